@@ -1,0 +1,213 @@
+"""CacheManager: pages, block tables and state slots of the live requests.
+
+Owns
+  * one PagePool per group of layers with the same need (all keys / a window);
+  * for each live request and group, the list of its pages by logical index
+    (the block table row; -1 where a window has passed and the page went back);
+  * one SlotPool for per-request state of fixed size;
+  * the device tensors behind all of it (when given a device).
+
+It replaces fastllm-py's two cache forms: the growable per-sequence buffer
+(`KVCache`, fastllm_py/model.py:76-123) and the preallocated
+(B, max_len, KVH, D) slot arrays of the batched decoder
+(fastllm_py/batched.py:118-121).  Unlike the latter it has bounds: a request
+cannot grow past `max_pages_per_request`, and asking for more pages than are
+free raises OutOfPages and changes nothing.
+
+Device layout of one layer's cache in a group:
+    [num_pages, 2 (keys, values), kv_heads, page_size, head_dim]
+so that the `page_size x head_dim` tile of one head of one page is contiguous.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from .needs import FixedState, PagedKV
+from .pages import OutOfPages, PagePool, SlotPool
+
+
+@dataclass
+class PageGroup:
+    need: PagedKV
+    cache_ids: list
+    pool: PagePool
+    tensors: dict = field(default_factory=dict)      # cache id -> device tensor
+
+    @property
+    def window(self):
+        return self.need.window
+
+
+@dataclass
+class RequestCache:
+    """What one live request holds."""
+    request_id: object
+    slot: int
+    seq_len: int = 0                                  # tokens whose keys/values are written
+    reserved: int = 0                                 # tokens that the pages taken so far can hold
+    pages: list = field(default_factory=list)         # per group: list of page ids by logical index (-1: given back)
+    released: list = field(default_factory=list)      # per group: logical pages below this index went back
+
+
+class CacheManager:
+    def __init__(self, needs: dict, page_size: int, num_pages: int, max_requests: int,
+                 max_pages_per_request: int):
+        """`needs`: cache id -> PagedKV | FixedState | None, one per run that has a cache."""
+        self.page_size = page_size
+        self.max_requests = max_requests
+        self.max_pages_per_request = max_pages_per_request
+        self.groups: list[PageGroup] = []
+        self.group_of: dict = {}                      # cache id -> index into groups
+        self.state_needs: dict = {}                   # cache id -> FixedState
+        self.state_tensors: dict = {}
+        by_need: dict = {}
+        for cid, need in needs.items():
+            if need is None:
+                continue
+            if isinstance(need, FixedState):
+                self.state_needs[cid] = need
+            elif isinstance(need, PagedKV):
+                if need not in by_need:
+                    by_need[need] = len(self.groups)
+                    self.groups.append(PageGroup(need, [], PagePool(num_pages)))
+                g = by_need[need]
+                self.groups[g].cache_ids.append(cid)
+                self.group_of[cid] = g
+            else:
+                raise TypeError(f"cache {cid}: unknown need {need!r}")
+        self.slots = SlotPool(max_requests)
+        self.live: dict = {}                          # request id -> RequestCache
+
+    # ------------------------------------------------------------ device side
+    def allocate(self, device, activation_dtype):
+        """Create the device tensors (pages of every layer, state rows)."""
+        import torch
+
+        for g in self.groups:
+            n = g.need
+            for cid in g.cache_ids:
+                g.tensors[cid] = torch.zeros(
+                    (g.pool.num_pages, 2, n.kv_heads, self.page_size, n.head_dim),
+                    dtype=activation_dtype, device=device)
+        for cid, need in self.state_needs.items():
+            dt = activation_dtype if need.dtype == "activation" else getattr(torch, need.dtype)
+            self.state_tensors[cid] = torch.zeros((self.max_requests,) + tuple(need.shape),
+                                                  dtype=dt, device=device)
+
+    @staticmethod
+    def bytes_per_token(needs: dict, itemsize: int) -> int:
+        """Cache bytes one token costs over all paged layers (for sizing the pools)."""
+        total = 0
+        for need in needs.values():
+            if isinstance(need, PagedKV):
+                total += 2 * need.kv_heads * need.head_dim * itemsize
+        return total
+
+    # ------------------------------------------------------------- requests
+    def admit(self, request_id) -> RequestCache:
+        if request_id in self.live:
+            raise RuntimeError(f"request {request_id!r} is already live")
+        slot = self.slots.take()
+        rc = RequestCache(request_id, slot, pages=[[] for _ in self.groups],
+                          released=[0] * len(self.groups))
+        self.live[request_id] = rc
+        return rc
+
+    def _pages_for(self, tokens: int) -> int:
+        return -(-tokens // self.page_size)
+
+    def pages_missing(self, rc: RequestCache, new_tokens: int) -> int:
+        """Pages each group must still take so that `new_tokens` more tokens fit."""
+        return max(0, self._pages_for(rc.seq_len + new_tokens) - self._pages_for(rc.reserved))
+
+    def can_extend(self, rc: RequestCache, new_tokens: int, spare: int = 0) -> bool:
+        """True if extend() would succeed and leave `spare` pages free in every group."""
+        if self._pages_for(rc.seq_len + new_tokens) > self.max_pages_per_request:
+            return False
+        missing = self.pages_missing(rc, new_tokens)
+        return all(g.pool.free_pages >= missing + spare for g in self.groups)
+
+    def extend(self, rc: RequestCache, new_tokens: int) -> None:
+        """Take the pages for `new_tokens` more tokens in every group, or raise
+        OutOfPages and take none."""
+        total = self._pages_for(rc.seq_len + new_tokens)
+        if total > self.max_pages_per_request:
+            raise OutOfPages(
+                f"request {rc.request_id!r} would hold {rc.seq_len + new_tokens} tokens; "
+                f"the most a request may hold is {self.max_pages_per_request * self.page_size}")
+        missing = self.pages_missing(rc, new_tokens)
+        if missing == 0:
+            return
+        for g in self.groups:
+            if g.pool.free_pages < missing:
+                raise OutOfPages(
+                    f"request {rc.request_id!r} needs {missing} more pages, "
+                    f"{g.pool.free_pages} free of {g.pool.num_pages}")
+        for gi, g in enumerate(self.groups):
+            rc.pages[gi].extend(g.pool.take(missing))
+        rc.reserved = total * self.page_size
+
+    def commit(self, rc: RequestCache, new_tokens: int) -> None:
+        """The step wrote `new_tokens` tokens.  Pages that a window has passed go back."""
+        rc.seq_len += new_tokens
+        if rc.seq_len > rc.reserved:
+            raise RuntimeError(f"request {rc.request_id!r}: {rc.seq_len} tokens written, "
+                               f"pages for {rc.reserved}")
+        for gi, g in enumerate(self.groups):
+            if g.window is None:
+                continue
+            # The next query sits at position seq_len and sees keys from
+            # seq_len - window + 1 on; pages wholly below that are dead.
+            first_needed = rc.seq_len - g.window + 1
+            row = rc.pages[gi]
+            dead_pages = min(max(0, first_needed) // self.page_size, len(row))
+            if dead_pages > rc.released[gi]:
+                g.pool.give_back(row[rc.released[gi]:dead_pages])
+                for i in range(rc.released[gi], dead_pages):
+                    row[i] = -1
+                rc.released[gi] = dead_pages
+
+    def release(self, request_id) -> None:
+        """The request ended (or is pushed out): everything it holds goes back."""
+        rc = self.live.pop(request_id)
+        for gi, g in enumerate(self.groups):
+            g.pool.give_back([p for p in rc.pages[gi] if p >= 0])
+            rc.pages[gi] = []
+        self.slots.give_back(rc.slot)
+
+    # ------------------------------------------------------ tables for a step
+    def block_table_row(self, group: int, rc: RequestCache, out: np.ndarray) -> None:
+        row = rc.pages[group]
+        out[:len(row)] = row
+        out[len(row):] = -1
+
+    def slot_mapping(self, group: int, rc: RequestCache, count: int, out: np.ndarray) -> None:
+        """Where the next `count` tokens of the request go: page * page_size + offset."""
+        row = rc.pages[group]
+        ps = self.page_size
+        pos = np.arange(rc.seq_len, rc.seq_len + count)
+        pages = np.asarray(row, dtype=np.int64)[pos // ps]
+        if (pages < 0).any():
+            raise RuntimeError(f"request {rc.request_id!r}: writing into a page that was given back")
+        out[:count] = pages * ps + pos % ps
+
+    # ------------------------------------------------------------ invariants
+    def check(self) -> None:
+        """No page lost, none held twice: the pools' books equal the requests'."""
+        for gi, g in enumerate(self.groups):
+            g.pool.check()
+            held = []
+            for rc in self.live.values():
+                held.extend(p for p in rc.pages[gi] if p >= 0)
+            if len(held) != len(set(held)):
+                raise AssertionError(f"group {gi}: a page is held by two requests")
+            if len(held) != g.pool.held_pages:
+                raise AssertionError(
+                    f"group {gi}: requests hold {len(held)} pages, pool says {g.pool.held_pages}")
+        slots = [rc.slot for rc in self.live.values()]
+        if len(slots) != len(set(slots)):
+            raise AssertionError("a slot is held by two requests")
+        if len(slots) != self.max_requests - self.slots.free_slots:
+            raise AssertionError("slot pool and live requests disagree")

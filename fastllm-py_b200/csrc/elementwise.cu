@@ -1,0 +1,148 @@
+// Embedding gather, RMSNorm (plain and fused with the residual add) and SwiGLU.
+//
+// fastllm-py's counterparts: the fancy-index gather `embed[ids]`
+// (fastllm_py/model.py:447), `rmsnorm_fused` (fastllm_py/kernels/ops.py:48-68),
+// `add_rmsnorm` (fastllm_py/graph_decode.py:300-324) and `swiglu_fused`
+// (ops.py:149-153).  As there, all arithmetic is float; sums of squares are
+// reduced in an order that depends on the block size only.
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+// out[t, :] = table[ids[t], :] as float (the residual stream is float in both
+// precisions).  An id outside [0, vocab) writes zeros and records 1 + t in
+// *status; it never reads outside the table.
+template <typename TT>
+__global__ void embed_kernel(const TT* __restrict__ table, long table_ld, const int* __restrict__ ids,
+                             float* __restrict__ out, long out_ld, int hidden, int vocab,
+                             int* __restrict__ status) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (long)t * out_ld;
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicCAS(status, 0, t + 1);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = 0.0f;
+        return;
+    }
+    const TT* row = table + (long)id * table_ld;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32<TT>(row[i]);
+}
+
+FL_API int fl_embed(const void* table, int table_dtype, long table_ld, const int* ids, float* out,
+                    long out_ld, int n_tokens, int hidden, int vocab, int* status,
+                    cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    FL_DISPATCH(table_dtype, TT,
+                embed_kernel<TT><<<n_tokens, 256, 0, stream>>>((const TT*)table, table_ld, ids, out,
+                                                               out_ld, hidden, vocab, status));
+    return fl_launch_status();
+}
+
+// -------------------------------------------------------------------- RMSNorm
+// out = x * (mean(x^2) + eps)^-1/2 * w.  With `delta`, first x += delta (x is
+// the float residual stream and is written back unless rows are gathered).
+// `rows`, when given, selects the input row of each output row.
+template <typename TX, typename TD, typename TW, typename TO, bool ADD>
+__global__ void rmsnorm_kernel(TX* __restrict__ x, long x_ld, const TD* __restrict__ delta,
+                               long delta_ld, const TW* __restrict__ w, TO* __restrict__ out,
+                               long out_ld, int dim, float eps, const int* __restrict__ rows,
+                               int write_back) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const long src = rows ? (long)rows[r] : (long)r;
+    TX* xr = x + src * x_ld;
+    TO* o = out + (long)r * out_ld;
+    float ss = 0.0f;
+    if (ADD) {
+        const TD* dr = delta + src * delta_ld;
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+            float v = to_f32<TX>(xr[i]) + to_f32<TD>(dr[i]);
+            if (write_back) xr[i] = from_f32<TX>(v);
+            ss += v * v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+            float v = to_f32<TX>(xr[i]);
+            ss += v * v;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+    if (ADD && !write_back) {
+        const TD* dr = delta + src * delta_ld;
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+            float v = to_f32<TX>(xr[i]) + to_f32<TD>(dr[i]);
+            o[i] = from_f32<TO>(v * inv * to_f32<TW>(w[i]));
+        }
+    } else {
+        // With write_back the sum is read again from x: each thread re-reads
+        // exactly the elements it wrote itself.
+        for (int i = threadIdx.x; i < dim; i += blockDim.x)
+            o[i] = from_f32<TO>(to_f32<TX>(xr[i]) * inv * to_f32<TW>(w[i]));
+    }
+}
+
+FL_API int fl_rmsnorm(const void* x, int x_dtype, long x_ld, const void* w, int w_dtype, void* out,
+                      int out_dtype, long out_ld, int n_rows, int dim, float eps, const int* rows,
+                      cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = dim >= 1024 ? 256 : 128;
+    FL_DISPATCH(x_dtype, TX, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,
+        (rmsnorm_kernel<TX, float, TW, TO, false><<<n_rows, threads, 0, stream>>>(
+            (TX*)x, x_ld, nullptr, 0, (const TW*)w, (TO*)out, out_ld, dim, eps, rows, 0)))));
+    return fl_launch_status();
+}
+
+FL_API int fl_add_rmsnorm(float* resid, long resid_ld, const void* delta, int delta_dtype,
+                          long delta_ld, const void* w, int w_dtype, void* out, int out_dtype,
+                          long out_ld, int n_rows, int dim, float eps, const int* rows,
+                          cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = dim >= 1024 ? 256 : 128;
+    const int write_back = rows ? 0 : 1;
+    FL_DISPATCH(delta_dtype, TD, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,
+        (rmsnorm_kernel<float, TD, TW, TO, true><<<n_rows, threads, 0, stream>>>(
+            resid, resid_ld, (const TD*)delta, delta_ld, (const TW*)w, (TO*)out, out_ld, dim, eps,
+            rows, write_back)))));
+    return fl_launch_status();
+}
+
+// resid += delta without a norm (the last pending sum of a stream that ends unnormed).
+template <typename TD>
+__global__ void add_kernel(float* __restrict__ resid, long resid_ld, const TD* __restrict__ delta,
+                           long delta_ld, int dim) {
+    float* xr = resid + (long)blockIdx.x * resid_ld;
+    const TD* dr = delta + (long)blockIdx.x * delta_ld;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) xr[i] += to_f32<TD>(dr[i]);
+}
+
+FL_API int fl_residual_add(float* resid, long resid_ld, const void* delta, int delta_dtype,
+                           long delta_ld, int n_rows, int dim, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    FL_DISPATCH(delta_dtype, TD, (add_kernel<TD><<<n_rows, 256, 0, stream>>>(
+        resid, resid_ld, (const TD*)delta, delta_ld, dim)));
+    return fl_launch_status();
+}
+
+// --------------------------------------------------------------------- SwiGLU
+// out[r, i] = silu(gu[r, i]) * gu[r, inter + i]: gate columns first, then up.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, long gu_ld, T* __restrict__ out, long out_ld,
+                              int inter) {
+    const T* g = gu + (long)blockIdx.y * gu_ld;
+    T* o = out + (long)blockIdx.y * out_ld;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < inter) {
+        const float gf = to_f32<T>(g[i]);
+        const float uf = to_f32<T>(g[inter + i]);
+        o[i] = from_f32<T>(gf / (1.0f + expf(-gf)) * uf);
+    }
+}
+
+FL_API int fl_swiglu(const void* gu, int dtype, long gu_ld, void* out, long out_ld, int n_rows,
+                     int inter, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    dim3 grid((inter + 255) / 256, n_rows);
+    FL_DISPATCH(dtype, T, (swiglu_kernel<T><<<grid, 256, 0, stream>>>((const T*)gu, gu_ld, (T*)out,
+                                                                      out_ld, inter)));
+    return fl_launch_status();
+}

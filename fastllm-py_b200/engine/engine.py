@@ -1,0 +1,174 @@
+"""Engine: the step function over a decoder and a cache manager.
+
+`step(entries)` runs exactly the tokens it is given, as one batch, against what
+earlier steps left in the cache, and returns the logits at the wanted places.
+It neither samples nor decides what to run: the scheduler above it does, and so
+does trace replay, through this same function.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, OutOfPages
+from ..config.engine import EngineConfig
+from ..parts import BuildContext, Decoder, Workspace
+from .batch import StepBuffers, StepContext, build_views
+
+
+@dataclass
+class StepEntry:
+    """A request's share of a step: its next tokens and the places (indices into
+    `tokens`) whose logits are wanted."""
+    request_id: object
+    tokens: list
+    want: list = field(default_factory=list)
+
+
+class Engine:
+    def __init__(self, decoder: Decoder, config: EngineConfig, max_model_len: int, num_pages: int):
+        self.decoder = decoder
+        self.config = config
+        self.device = decoder.ctx.device
+        self.dtype = decoder.ctx.dtype
+        self.page_size = config.page_size
+        self.max_model_len = max_model_len
+        self.max_tokens = min(config.max_batched_tokens, 65535)
+        bt_stride = -(-max_model_len // self.page_size)
+        self.cache = CacheManager(decoder.cache_needs(), self.page_size, num_pages,
+                                  config.max_requests, bt_stride)
+        self.cache.allocate(self.device, self.dtype)
+        self.workspace = Workspace(self.device, self.max_tokens)
+        self.buffers = StepBuffers(self.device, self.max_tokens, config.max_requests,
+                                   len(self.cache.groups), bt_stride)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.no_rotation = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.vocab = decoder.vocab
+        self.steps_run = 0
+
+    # -------------------------------------------------------------- requests
+    def begin(self, request_id):
+        """A request becomes live: it gets a state slot (pages come as it grows)."""
+        return self.cache.admit(request_id)
+
+    def end(self, request_id) -> None:
+        """A request is finished or pushed out: its pages and slot go back."""
+        self.cache.release(request_id)
+
+    def is_live(self, request_id) -> bool:
+        return request_id in self.cache.live
+
+    def tokens_held(self, request_id) -> int:
+        return self.cache.live[request_id].seq_len
+
+    # ------------------------------------------------------------------ step
+    def prepare(self, entries) -> StepContext:
+        """Check the batch, take its pages, fill and upload the step's tables."""
+        cache, buf = self.cache, self.buffers
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        if len(entries) > self.config.max_requests:
+            raise ValueError(f"{len(entries)} requests in one step; the engine allows "
+                             f"{self.config.max_requests}")
+        n_tokens = sum(len(e.tokens) for e in entries)
+        if n_tokens > self.max_tokens:
+            raise ValueError(f"{n_tokens} tokens in one step; the engine allows {self.max_tokens}")
+        seen = set()
+        need = 0
+        for e in entries:
+            if e.request_id in seen:
+                raise ValueError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            if e.request_id not in cache.live:
+                raise KeyError(f"request {e.request_id!r} is not live (call begin first)")
+            if len(e.tokens) == 0:
+                raise ValueError(f"request {e.request_id!r} brings no tokens")
+            rc = cache.live[e.request_id]
+            if rc.seq_len + len(e.tokens) > self.max_model_len:
+                raise ValueError(f"request {e.request_id!r} would reach {rc.seq_len + len(e.tokens)} "
+                                 f"tokens; the engine's longest sequence is {self.max_model_len}")
+            for t in e.tokens:
+                if not 0 <= int(t) < self.vocab:
+                    raise ValueError(f"request {e.request_id!r}: token id {t} is outside the "
+                                     f"vocabulary of {self.vocab}")
+            for w in e.want:
+                if not 0 <= int(w) < len(e.tokens):
+                    raise ValueError(f"request {e.request_id!r}: wanted place {w} is outside its "
+                                     f"{len(e.tokens)} tokens")
+            need += cache.pages_missing(rc, len(e.tokens))
+        for g in cache.groups:
+            if g.pool.free_pages < need:
+                raise OutOfPages(f"the step needs {need} more pages, {g.pool.free_pages} are free "
+                                 f"of {g.pool.num_pages}")
+        buf.wait_for_last_upload()
+        tok = buf.host_view("token_ids")
+        pos = buf.host_view("positions")
+        treq = buf.host_view("tok_req")
+        rows = buf.host_view("logit_rows")
+        rstart = buf.host_view("req_start")
+        rctx = buf.host_view("req_ctx")
+        rqlen = buf.host_view("req_qlen")
+        rslot = buf.host_view("req_slot")
+        slot_views = [buf.host_view(f"slots{g}") for g in range(len(cache.groups))]
+        bt_views = [buf.host_view(f"bt{g}").reshape(buf.max_requests, buf.bt_stride)
+                    for g in range(len(cache.groups))]
+        at, m = 0, 0
+        q_lens, ctx_lens, slots_host = [], [], []
+        for r, e in enumerate(entries):
+            rc = cache.live[e.request_id]
+            q = len(e.tokens)
+            cache.extend(rc, q)
+            tok[at:at + q] = e.tokens
+            pos[at:at + q] = np.arange(rc.seq_len, rc.seq_len + q)
+            treq[at:at + q] = r
+            for w in e.want:
+                rows[m] = at + int(w)
+                m += 1
+            for g in range(len(cache.groups)):
+                cache.slot_mapping(g, rc, q, slot_views[g][at:at + q])
+                cache.block_table_row(g, rc, bt_views[g][r])
+            rstart[r], rctx[r], rqlen[r], rslot[r] = at, rc.seq_len, q, rc.slot
+            q_lens.append(q)
+            ctx_lens.append(rc.seq_len)
+            slots_host.append(rc.slot)
+            at += q
+        rstart[len(entries)] = at
+        buf.upload(len(entries))
+        n = len(entries)
+        step = StepContext(
+            n_tokens=n_tokens, n_requests=n, n_wanted=m,
+            token_ids=buf.dev_view("token_ids")[:n_tokens],
+            positions=buf.dev_view("positions")[:n_tokens],
+            tok_req=buf.dev_view("tok_req")[:n_tokens],
+            logit_rows=buf.dev_view("logit_rows")[:m],
+            req_start=buf.dev_view("req_start")[:n + 1],
+            req_ctx=buf.dev_view("req_ctx")[:n],
+            req_qlen=buf.dev_view("req_qlen")[:n],
+            req_slot=buf.dev_view("req_slot")[:n],
+            status=self.status, workspace=self.workspace, no_rotation=self.no_rotation,
+            q_lens=q_lens, ctx_lens=ctx_lens, slots_host=slots_host,
+            max_q_len=max(q_lens), max_seq_len=max(c + q for c, q in zip(ctx_lens, q_lens)))
+        step._views = build_views(cache, buf, n_tokens, n)
+        return step
+
+    def step(self, entries) -> torch.Tensor:
+        """Run one step; returns float32 logits [wanted places, vocab] on the
+        device, ordered by entry and by `want`.  The tensor is a view of an
+        engine buffer and is overwritten by the next step."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        step = self.prepare(entries)
+        logits = self.decoder.forward(step)
+        for e in entries:
+            self.cache.commit(self.cache.live[e.request_id], len(e.tokens))
+        self.steps_run += 1
+        return logits
+
+    def check_status(self) -> None:
+        """Raise if a kernel reported a fault since the last check (synchronises)."""
+        code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise RuntimeError(f"a kernel reported error code {code} (a token id outside the "
+                               f"embedding table, or a wait that gave up)")

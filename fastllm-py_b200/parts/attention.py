@@ -1,0 +1,118 @@
+"""Attention mixer: grouped-query causal attention over a paged cache.
+
+Formulas (fastllm_py/model.py:399-430, :341-353): q, k, v = h Wq^T, h Wk^T,
+h Wv^T, split head-major; rotary encoding of q and k at the tokens' absolute
+positions; the rotated key and the value join the cache; scores
+q.k * head_dim^-1/2 over the visible keys (those at or before the query, within
+`window` if the layer has one), softmax in float, weighted sum of values, merged
+head-major; output projection Wo.  Query head h reads KV head
+h // (heads / kv_heads).
+
+One stacked matrix serves q|k|v.  A layer that reads another layer's cache
+(`shares_cache`) has no k/v matrices and writes nothing.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..cache.needs import PagedKV
+from ..native import ops
+from .base import Part
+from .linear import Linear
+from .registry import build_part, register_part
+
+
+@dataclass
+class PagedCacheView:
+    """What a paged mixer gets for one run: its layer's pages and this step's tables."""
+    tensor: torch.Tensor          # [pages, 2, kv_heads, page_size, head_dim]
+    block_table: torch.Tensor     # [requests in the step, max pages] int32
+    slots: torch.Tensor           # [tokens in the step] int32: page * page_size + offset
+    page_size: int
+    writes: bool                  # False when the run reads another run's cache
+
+
+@register_part("mixer", "attention")
+class Attention(Part):
+    """params: hidden_size, num_heads, num_kv_heads, head_dim, position (PartSpec | None),
+    window (None | int), shares_cache (bool), scale (None -> head_dim^-1/2).
+    tensors: q, o and, unless shares_cache, k, v."""
+    category = "mixer"
+
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.heads = int(p["num_heads"])
+        self.kv_heads = int(p["num_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.window = p.get("window")
+        self.shares_cache = bool(p.get("shares_cache", False))
+        self.scale = float(p["scale"]) if p.get("scale") is not None else self.head_dim ** -0.5
+        if self.heads % self.kv_heads:
+            raise ValueError(f"attention: {self.heads} heads are not a multiple of "
+                             f"{self.kv_heads} kv heads")
+        if self.head_dim % 16 or not 16 <= self.head_dim <= 256:
+            raise ValueError(f"attention: head_dim {self.head_dim} is not supported by the kernels "
+                             f"(multiples of 16 from 16 to 256)")
+        if self.heads > 65535:
+            raise ValueError(f"attention: {self.heads} heads exceed the kernels' limit of 65535")
+        self.position = build_part("position", p["position"], ctx) if p.get("position") else None
+        self.qkv = None
+        self.o = None
+
+    def children(self):
+        return [self.position] if self.position is not None else []
+
+    def cache_need(self):
+        if self.shares_cache:
+            return None
+        return PagedKV(self.kv_heads, self.head_dim, self.window)
+
+    def weight_shapes(self):
+        q_out, kv_out = self.heads * self.head_dim, self.kv_heads * self.head_dim
+        shapes = {"q": (q_out, self.hidden), "o": (self.hidden, q_out)}
+        if not self.shares_cache:
+            shapes["k"] = (kv_out, self.hidden)
+            shapes["v"] = (kv_out, self.hidden)
+        return shapes
+
+    def load(self, tensors):
+        mats = [tensors["q"]] if self.shares_cache else [tensors["q"], tensors["k"], tensors["v"]]
+        if len({m.dtype for m in mats}) != 1:
+            raise ValueError("attention: q, k and v matrices must be stored in one dtype")
+        self.qkv = Linear(mats)
+        self.o = Linear([tensors["o"]])
+
+    def forward(self, h, out, step, cache: PagedCacheView):
+        n = h.shape[0]
+        dt = self.ctx.dtype
+        q_cols = self.heads * self.head_dim
+        cols = q_cols if self.shares_cache else q_cols + 2 * self.kv_heads * self.head_dim
+        if cache.writes == self.shares_cache:
+            raise RuntimeError("attention: the run's cache and the layer's shares_cache disagree")
+        qkv = step.workspace.rows("qkv", n, cols, dt)
+        self.qkv.forward(h, qkv)
+        if self.position is not None:
+            cos, sin = self.position.tables()
+            rot = self.position.rot_dim
+        else:
+            cos, sin, rot = step.no_rotation, step.no_rotation, 0
+        ops.rope_kv_write(qkv, self.heads, self.kv_heads, self.head_dim, rot, cos, sin,
+                          step.positions, cache.slots, cache.tensor if cache.writes else None,
+                          cache.page_size)
+        ctx = step.workspace.rows("attn_ctx", n, q_cols, dt)
+        self.attend(qkv[:, :q_cols], ctx, step, cache)
+        self.o.forward(ctx, out)
+
+    def attend(self, q, ctx, step, cache):
+        from ..native import attention as fast
+        if fast.handles(q.dtype, self.head_dim):
+            fast.paged_attention(q, ctx, cache, step, self.heads, self.kv_heads, self.head_dim,
+                                 self.window, self.scale)
+        else:
+            ops.paged_attention_simt(q, ctx, cache.tensor, cache.block_table, step.tok_req,
+                                     step.positions, self.heads, self.kv_heads, self.head_dim,
+                                     self.window, self.scale, cache.page_size)

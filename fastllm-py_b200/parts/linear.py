@@ -1,0 +1,45 @@
+"""Linear: out = a @ W^T for an (out_features, in_features) weight, no bias.
+
+fastllm-py keeps every projection as its own (out, in) array and calls cuBLAS
+(`matmul_w`, fastllm_py/model.py:55-63).  Here a Linear may hold several
+checkpoint matrices stacked along the output axis (q|k|v, gate|up), so that one
+product serves them all, and picks the kernel by operand types:
+
+  * bfloat16 activations and bfloat16 weights: the tcgen05 tensor-core kernel;
+  * anything with a 32-bit operand: the CUDA-core kernel with float
+    accumulation (a weight stored in 32-bit stays 32-bit; the true 32-bit path
+    never touches a reduced-precision matrix mode).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..native import ops
+
+
+class Linear:
+    def __init__(self, weights: list):
+        """`weights`: matrices [out_i, in] of one dtype, stacked along out."""
+        w = weights[0] if len(weights) == 1 else torch.cat(weights, dim=0)
+        self.weight = w.contiguous()
+        self.out_features, self.in_features = self.weight.shape
+        self._tc = None
+
+    @classmethod
+    def sharing(cls, weight: torch.Tensor) -> "Linear":
+        """A Linear over an existing tensor without copying it (tied embeddings)."""
+        self = cls.__new__(cls)
+        self.weight = weight
+        self.out_features, self.in_features = weight.shape
+        self._tc = None
+        return self
+
+    def forward(self, a: torch.Tensor, out: torch.Tensor) -> None:
+        if a.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16:
+            from .. import native
+            if native.tensor_core_gemm_enabled():
+                if self._tc is None:
+                    self._tc = native.gemm_tc.TensorCoreLinear(self.weight)
+                self._tc.forward(a, out)
+                return
+        ops.gemm_simt(a, self.weight, out)
