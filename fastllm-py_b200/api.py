@@ -54,6 +54,9 @@ class Model:
         dev = _require_gpu(engine_config.device)
         torch.cuda.set_device(dev)
         dtype = getattr(torch, engine_config.dtype)
+        from .native import build as native_build
+        from .native.libraries import libraries_for
+        native_build.compile_many(libraries_for(engine_config.dtype))
         plan = arch.make_plan(config, set(store.names()) if store is not None else None)
         max_len = engine_config.max_model_len or plan.max_positions
         ctx = BuildContext(dev, dtype, engine_config.page_size, max_len)

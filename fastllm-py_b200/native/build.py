@@ -27,7 +27,7 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPI
                 "-Xcompiler", "-fvisibility=hidden"]
 
 _loaded: dict = {}
-_lock = threading.Lock()
+_lock = threading.RLock()
 
 
 class NativeBuildError(RuntimeError):
@@ -45,8 +45,19 @@ def _nvcc() -> str:
     return exe
 
 
+_build_dir_cache = None
+
+
 def _build_dir() -> Path:
     """In-tree when the tree is writable, else a per-user folder under the temp dir."""
+    global _build_dir_cache
+    with _lock:
+        if _build_dir_cache is None:
+            _build_dir_cache = _find_build_dir()
+        return _build_dir_cache
+
+
+def _find_build_dir() -> Path:
     cand = Path(os.environ["FASTLLM_B200_BUILD_DIR"]) if "FASTLLM_B200_BUILD_DIR" in os.environ \
         else Path(__file__).resolve().parent / "_build"
     try:

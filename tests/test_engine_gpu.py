@@ -1,0 +1,149 @@
+"""The engine against the plain implementation, for every way of cutting the work.
+
+Each tiny model runs the same requests whole, with the last 32 tokens one by
+one, in portions of changing size (down to two tokens) and mixed (up to four
+live requests, portions beside decoded tokens, a pool so small that pages are
+used again), in true 32-bit and in bfloat16.  Every (request, position) is
+compared with the plain whole-sequence logits.
+
+Tolerances, fixed before the first run:
+  * 32-bit vs plain: 1e-4 * max(1, largest |logit|);
+  * 32-bit, one cut vs another: equal bit for bit (every kernel of that path
+    sums in an order that depends on the token's own position only);
+  * bfloat16 vs the plain implementation with bfloat16 storage emulated:
+    twice the largest difference that bfloat16 storage itself makes to the plain
+    logits, plus 1e-3.
+"""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+import replay
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"tiny_a": [5, 17, 33, 70, 100], "tiny_b": [1, 9, 40, 64, 100, 150],
+           "tiny_c": [3, 47, 130, 64]}
+
+
+def make_requests(name):
+    cfg = tiny.CONFIGS[name]["config"]
+    rng = np.random.default_rng(sum(map(ord, name)) + 1)
+    return {f"r{i}": rng.integers(0, cfg.vocab_size, size=n).tolist()
+            for i, n in enumerate(LENGTHS[name])}
+
+
+_plain_cache = {}
+
+
+def plain_logits(name, folder, requests, bf16):
+    key = (name, bf16)
+    if key not in _plain_cache:
+        weights, config = plain.load_folder(folder)
+        store = plain.store_bf16 if bf16 else plain.identity
+        _plain_cache[key] = {rid: plain.forward(weights, config, toks, store=store)
+                             for rid, toks in requests.items()}
+    return _plain_cache[key]
+
+
+_engines = {}
+
+
+def engine_for(name, folder, dtype, max_tokens):
+    from fastllm_py_b200 import Model
+
+    key = (name, dtype, max_tokens)
+    if key not in _engines:
+        page = tiny.CONFIGS[name]["page_size"]
+        _engines[key] = Model.load(folder, dtype=dtype, page_size=page, max_tokens=max_tokens,
+                                   max_requests=8, max_batched_tokens=512, max_model_len=256,
+                                   cuda_graph=False).engine
+    return _engines[key]
+
+
+def tolerance(name, folder, requests, dtype):
+    ref = plain_logits(name, folder, requests, dtype == "bfloat16")
+    biggest = max(float(v.abs().max()) for v in ref.values())
+    if dtype == "float32":
+        return ref, 1e-4 * max(1.0, biggest)
+    exact = plain_logits(name, folder, requests, False)
+    storage = max(float((ref[r] - exact[r]).abs().max()) for r in ref)
+    return ref, 2.0 * storage + 1e-3
+
+
+def compare(got, ref, tol, what):
+    assert got, "no logits came back"
+    worst, where = 0.0, None
+    for (rid, pos), row in got.items():
+        d = float((row - ref[rid][pos]).abs().max())
+        if not d <= worst:                      # also catches NaN
+            worst, where = d, (rid, pos)
+    assert worst <= tol, f"{what}: largest difference {worst:.3e} at {where}, tolerance {tol:.3e}"
+
+
+CUTS = {
+    "whole": lambda reqs: replay.whole(reqs),
+    "tail": lambda reqs: replay.tail_decode(reqs, 32),
+    "portions": lambda reqs: replay.portions(reqs),
+    "mixed": lambda reqs: replay.mixed(reqs, live=4, seed=3),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cut", list(CUTS))
+@pytest.mark.parametrize("name", list(tiny.CONFIGS))
+def test_cut_matches_plain(name, cut, dtype, model_folders):
+    requests = make_requests(name)
+    steps = CUTS[cut](requests)
+    ref, tol = tolerance(name, model_folders[name], requests, dtype)
+    # the mixed cut gets a pool of exactly its peak, so that pages must be used again
+    pool = replay.peak_tokens(steps) if cut == "mixed" else 512
+    engine = engine_for(name, model_folders[name], dtype, pool)
+    got = replay.run_in_process(engine, steps)
+    assert len(got) == sum(len(t) for t in requests.values())
+    compare(got, ref, tol, f"{name} {cut} {dtype}")
+    assert not engine.cache.live
+    assert all(g.pool.free_pages == g.pool.num_pages for g in engine.cache.groups)
+
+
+@pytest.mark.parametrize("name", list(tiny.CONFIGS))
+def test_float32_cuts_agree_bit_for_bit(name, model_folders):
+    requests = make_requests(name)
+    engine = engine_for(name, model_folders[name], "float32", 512)
+    base = replay.run_in_process(engine, replay.whole(requests))
+    for cut in ("tail", "portions", "mixed"):
+        got = replay.run_in_process(engine, CUTS[cut](requests))
+        for key, row in got.items():
+            assert torch.equal(row, base[key]), f"{name} {cut}: {key} differs from the whole run"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype, model_folders, tmp_path):
+    """The program itself, as a subprocess, on a mixed trace with a tight pool."""
+    name = "tiny_b"
+    requests = make_requests(name)
+    steps = replay.mixed(requests, live=4, seed=5)
+    ref, tol = tolerance(name, model_folders[name], requests, dtype)
+    vocab = tiny.CONFIGS[name]["config"].vocab_size
+    got = replay.run_program(model_folders[name], dtype, steps, tmp_path / "out",
+                             replay.peak_tokens(steps), vocab)
+    compare(got, ref, tol, f"trace_run {dtype}")
+
+
+def test_long_decoding(model_folders):
+    """200 tokens decoded one by one after a short prompt, both precisions."""
+    name = "tiny_b"
+    cfg = tiny.CONFIGS[name]["config"]
+    rng = np.random.default_rng(9)
+    requests = {"long": rng.integers(0, cfg.vocab_size, size=230).tolist()}
+    for dtype in ("float32", "bfloat16"):
+        _plain_cache.pop((name, True), None)
+        _plain_cache.pop((name, False), None)
+        ref, tol = tolerance(name, model_folders[name], requests, dtype)
+        engine = engine_for(name, model_folders[name], dtype, 512)
+        got = replay.run_in_process(engine, replay.tail_decode(requests, 200))
+        compare(got, ref, tol, f"long decoding {dtype}")
+    _plain_cache.pop((name, True), None)
+    _plain_cache.pop((name, False), None)
