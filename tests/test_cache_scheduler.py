@@ -1,0 +1,298 @@
+"""The cache manager's books and the scheduler's decisions (no GPU).
+
+The scheduler runs here against the real CacheManager and a stand-in engine
+whose "model" emits a fixed function of the request's token count, so that its
+decisions (admission, portions under the budget, finishing, pushing out when
+pages run out) can be checked exactly.
+"""
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from fastllm_py_b200.cache import CacheManager, FixedState, OutOfPages, PagedKV, PagePool
+from fastllm_py_b200.engine.scheduler import Scheduler
+from fastllm_py_b200.sampling import SamplingParams
+
+
+# ------------------------------------------------------------------ page pool
+
+def test_pool_refuses_without_side_effects():
+    pool = PagePool(4)
+    a = pool.take(3)
+    with pytest.raises(OutOfPages):
+        pool.take(2)
+    assert pool.free_pages == 1
+    pool.give_back(a)
+    with pytest.raises(RuntimeError, match="twice"):
+        pool.give_back([a[0]])
+    pool.check()
+
+
+def manager(pages=16, page_size=4, window=None, max_requests=4, max_pages=64):
+    needs = {0: PagedKV(2, 16), 1: PagedKV(2, 16)}
+    if window:
+        needs[2] = PagedKV(2, 16, window)
+    needs[3] = FixedState((5,))
+    return CacheManager(needs, page_size, pages, max_requests, max_pages)
+
+
+def test_groups_by_need_and_state_slots():
+    m = manager(window=6)
+    assert [g.cache_ids for g in m.groups] == [[0, 1], [2]]
+    assert m.state_needs == {3: FixedState((5,))}
+    a, b = m.admit("a"), m.admit("b")
+    assert {a.slot, b.slot} == {0, 1}
+    with pytest.raises(RuntimeError):
+        m.admit("a")
+    m.release("a")
+    assert m.admit("c").slot == a.slot                     # a freed slot is used again
+    m.check()
+
+
+def test_extend_commit_tables():
+    m = manager(pages=8, page_size=4)
+    rc = m.admit("r")
+    m.extend(rc, 6)
+    assert len(rc.pages[0]) == 2 and m.groups[0].pool.free_pages == 6
+    slots = np.zeros(6, dtype=np.int32)
+    m.slot_mapping(0, rc, 6, slots)
+    p0, p1 = rc.pages[0]
+    assert slots.tolist() == [p0 * 4, p0 * 4 + 1, p0 * 4 + 2, p0 * 4 + 3, p1 * 4, p1 * 4 + 1]
+    m.commit(rc, 6)
+    m.extend(rc, 1)                                        # token 7 fits the second page
+    assert len(rc.pages[0]) == 2
+    m.commit(rc, 1)
+    m.extend(rc, 2)                                        # token 9 needs a third
+    assert len(rc.pages[0]) == 3
+    row = np.zeros(6, dtype=np.int32)
+    m.block_table_row(0, rc, row)
+    assert row.tolist() == rc.pages[0] + [-1, -1, -1]
+    with pytest.raises(RuntimeError):
+        m.commit(rc, 9)                                    # more tokens than pages were taken for
+    m.check()
+
+
+def test_out_of_pages_takes_nothing():
+    m = manager(pages=3, page_size=4)
+    a, b = m.admit("a"), m.admit("b")
+    m.extend(a, 8)
+    assert not m.can_extend(b, 8) and m.can_extend(b, 4)
+    with pytest.raises(OutOfPages):
+        m.extend(b, 8)
+    assert b.pages[0] == [] and m.groups[0].pool.free_pages == 1
+    m.release("a")
+    m.extend(b, 8)
+    m.check()
+
+
+def test_request_length_limit():
+    m = manager(pages=64, page_size=4, max_pages=3)
+    rc = m.admit("r")
+    assert not m.can_extend(rc, 13)
+    with pytest.raises(OutOfPages, match="most a request may hold"):
+        m.extend(rc, 13)
+
+
+def test_window_gives_pages_back():
+    m = manager(pages=8, page_size=4, window=6)
+    full, win = m.groups
+    rc = m.admit("r")
+    for _ in range(5):                                     # 20 tokens, 4 at a time
+        m.extend(rc, 4)
+        m.commit(rc, 4)
+    # next query at 20 sees keys 15..20: pages 0..2 (positions 0..11) are dead
+    assert rc.pages[1][:3] == [-1, -1, -1] and all(p >= 0 for p in rc.pages[1][3:])
+    assert win.pool.held_pages == 2 and full.pool.held_pages == 5
+    m.check()
+    m.release("r")
+    assert win.pool.free_pages == 8 and full.pool.free_pages == 8
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_random_orders_keep_the_books(seed):
+    rng = random.Random(seed)
+    m = manager(pages=24, page_size=4, window=9, max_requests=5)
+    live = {}
+    for step in range(400):
+        action = rng.random()
+        if action < 0.25 and len(live) < 5:
+            rid = f"r{step}"
+            live[rid] = m.admit(rid)
+        elif action < 0.8 and live:
+            rid = rng.choice(list(live))
+            n = rng.choice([1, 1, 1, 2, 5, 11])
+            if m.can_extend(live[rid], n):
+                m.extend(live[rid], n)
+                m.commit(live[rid], n)
+            else:
+                with pytest.raises(OutOfPages):
+                    m.extend(live[rid], n)
+        elif live:
+            rid = rng.choice(list(live))
+            m.release(rid)
+            del live[rid]
+        m.check()
+    for rid in list(live):
+        m.release(rid)
+    m.check()
+    assert all(g.pool.free_pages == 24 for g in m.groups) and m.slots.free_slots == 5
+
+
+# ------------------------------------------------------------------ scheduler
+
+class StandInEngine:
+    """Real cache manager, no model: the logits of a wanted row make argmax equal
+    (tokens the request holds after the step) mod vocab."""
+    vocab = 50
+
+    def __init__(self, pages, page_size=4, max_requests=4, max_model_len=64, max_tokens=16):
+        self.cache = CacheManager({0: PagedKV(1, 16)}, page_size, pages, max_requests,
+                                  -(-max_model_len // page_size))
+        self.max_model_len = max_model_len
+        self.max_tokens = max_tokens
+        self.steps = []
+
+    def begin(self, rid):
+        return self.cache.admit(rid)
+
+    def end(self, rid):
+        self.cache.release(rid)
+
+    def step(self, entries):
+        rows = []
+        self.steps.append([(e.request_id, len(e.tokens), list(e.want)) for e in entries])
+        assert sum(len(e.tokens) for e in entries) <= self.max_tokens
+        for e in entries:
+            rc = self.cache.live[e.request_id]
+            self.cache.extend(rc, len(e.tokens))
+            self.cache.commit(rc, len(e.tokens))
+            for _ in e.want:
+                row = torch.zeros(self.vocab)
+                row[rc.seq_len % self.vocab] = 1.0
+                rows.append(row)
+        self.cache.check()
+        return torch.stack(rows) if rows else torch.zeros(0, self.vocab)
+
+
+class ArgmaxSampler:
+    def sample(self, logits, states):
+        toks = logits.argmax(-1).tolist()
+        for s, t in zip(states, toks):
+            s.record(t)
+        return toks
+
+
+def test_portions_under_the_budget_and_first_token():
+    eng = StandInEngine(pages=32, max_tokens=8)
+    s = Scheduler(eng, ArgmaxSampler(), token_budget=8)
+    rid = s.add_request(list(range(19)), max_new_tokens=3)
+    out = s.run()
+    # 19 prompt tokens under a budget of 8: portions 8, 8, 3; only the last wants logits
+    assert eng.steps[:3] == [[(rid, 8, [])], [(rid, 8, [])], [(rid, 3, [2])]]
+    assert eng.steps[3:] == [[(rid, 1, [0])], [(rid, 1, [0])]]
+    assert out[rid] == [19, 20, 21]
+    assert not eng.cache.live and eng.cache.groups[0].pool.free_pages == 32
+
+
+def test_decodes_run_beside_a_prompt_portion():
+    eng = StandInEngine(pages=32, max_tokens=8)
+    s = Scheduler(eng, ArgmaxSampler(), token_budget=8)
+    a = s.add_request([1, 2, 3], max_new_tokens=4)
+    s.step()                                              # a: prompt whole, first token
+    b = s.add_request(list(range(12)), max_new_tokens=2)
+    s.step()
+    # a decodes one token, b gets the rest of the budget
+    assert eng.steps[1] == [(a, 1, [0]), (b, 7, [])]
+    s.step()
+    assert eng.steps[2] == [(a, 1, [0]), (b, 5, [4])]
+    s.run()
+    assert len(s.requests[a].output) == 4 and len(s.requests[b].output) == 2
+
+
+def test_stop_token_is_emitted_and_ends_the_request():
+    eng = StandInEngine(pages=32)
+    s = Scheduler(eng, ArgmaxSampler())
+    rid = s.add_request([7, 7, 7], max_new_tokens=10, stop_ids=[5])
+    out = s.run()
+    assert out[rid] == [3, 4, 5] and s.requests[rid].finish_reason == "stop"
+
+
+def test_requests_that_can_never_fit_are_refused():
+    eng = StandInEngine(pages=4, page_size=4, max_model_len=64)
+    s = Scheduler(eng, ArgmaxSampler())
+    with pytest.raises(ValueError, match="never finish"):
+        s.add_request(list(range(10)), max_new_tokens=8)      # 18 tokens > 16 in the pool
+    with pytest.raises(ValueError, match="longest sequence"):
+        s.add_request(list(range(60)), max_new_tokens=8)
+    with pytest.raises(ValueError):
+        s.add_request([], max_new_tokens=1)
+
+
+def test_admission_waits_for_slots_and_pages():
+    eng = StandInEngine(pages=6, page_size=4, max_requests=2)
+    s = Scheduler(eng, ArgmaxSampler())
+    ids = [s.add_request([1] * 6, max_new_tokens=2) for _ in range(3)]
+    s.step()
+    assert [r.request_id for r in s.running] == ids[:2] and len(s.waiting) == 1   # two slots only
+    s.run()
+    assert all(len(s.requests[i].output) == 2 for i in ids)
+    assert eng.cache.groups[0].pool.free_pages == 6
+
+
+def test_pages_run_out_last_admitted_is_pushed_out_and_recomputed():
+    # 6 pages of 4 tokens; two requests of 7 prompt tokens (2 pages each) that decode
+    # 8 more (up to 15 tokens = 4 pages each): together they need 8 pages, so one must go.
+    eng = StandInEngine(pages=6, page_size=4, max_requests=4)
+    s = Scheduler(eng, ArgmaxSampler())
+    a = s.add_request([1] * 7, max_new_tokens=8)
+    b = s.add_request([2] * 7, max_new_tokens=8)
+    out = s.run()
+    assert s.stats["pushed_out"] >= 1
+    assert s.requests[b].times_pushed_out >= 1 and s.requests[a].times_pushed_out == 0
+    # outputs are what an undisturbed run gives: token = tokens held after the step
+    assert out[a] == list(range(7, 15)) and out[b] == list(range(7, 15))
+    # b's comeback recomputed prompt + produced tokens as one prompt
+    regrown = [st for st in eng.steps if any(r == b and n > 7 for r, n, _ in st)]
+    assert regrown, "the pushed-out request did not come back with its produced tokens"
+    assert not eng.cache.live and eng.cache.groups[0].pool.free_pages == 6
+
+
+def test_no_admission_while_a_request_was_pushed_out():
+    eng = StandInEngine(pages=6, page_size=4, max_requests=4)
+    s = Scheduler(eng, ArgmaxSampler())
+    s.add_request([1] * 7, max_new_tokens=8)
+    s.add_request([2] * 7, max_new_tokens=8)
+    c = s.add_request([3] * 3, max_new_tokens=1)
+    seen_push = False
+    while s.has_work():
+        before = s.stats["pushed_out"]
+        running_before = {r.request_id for r in s.running}
+        s.step()
+        if s.stats["pushed_out"] > before:
+            seen_push = True
+            admitted = {r.request_id for r in s.running} - running_before
+            assert not admitted, "a request was admitted in a step that pushed one out"
+    assert seen_push and len(s.requests[c].output) == 1
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_workloads_finish_with_clean_books(seed):
+    rng = random.Random(seed)
+    eng = StandInEngine(pages=10, page_size=4, max_requests=3, max_model_len=40, max_tokens=12)
+    s = Scheduler(eng, ArgmaxSampler(), token_budget=12)
+    want = {}
+    for _ in range(12):
+        n, m = rng.randint(1, 20), rng.randint(1, 12)
+        rid = s.add_request([0] * n, max_new_tokens=m)
+        want[rid] = [(n + i) % 50 for i in range(m)]
+    out = s.run(max_steps=2000)
+    assert out == want
+    assert not s.has_work() and not eng.cache.live
+    assert eng.cache.groups[0].pool.free_pages == 10 and eng.cache.slots.free_slots == 3
+
+
+def test_sampling_params():
+    assert SamplingParams().greedy and not SamplingParams(temperature=0.5).greedy
+    assert SamplingParams(presence_penalty=0.1).penalized and not SamplingParams().penalized
