@@ -1,0 +1,437 @@
+// C[M, N] = A[M, K] * W[N, K]^T in bfloat16 with float accumulation on the
+// Blackwell tensor cores: TMA loads into 128-byte-swizzled shared memory,
+// tcgen05.mma issued by one thread, the accumulator in tensor memory, read back
+// with tcgen05.ld.
+//
+// fastllm-py leaves this product to cuBLAS (`x @ w.T`, fastllm_py/model.py:63)
+// and, for INT4, to Marlin; its own note on decoding is that M = 1 wants a
+// GEMV-shaped kernel and not a GEMM tile (fastllm_py/graph_decode.py:541-543).
+// This kernel covers both ends with one shape: the WEIGHTS are the 128-row
+// operand of the MMA and the TOKENS are its N dimension (16 to 256 wide), so a
+// decode step of a few tokens wastes no tensor-core rows and streams each weight
+// once, and a prompt portion uses 128 x 256 tiles.  When there are too few tiles
+// to keep every SM pulling bytes, K is split over CTAs; partial sums go to a
+// float workspace and a second kernel adds them in a fixed order.
+//
+// Roles in a CTA of 192 threads: warp 0 (one lane) issues the TMA loads, warp 1
+// owns the tensor memory and (one lane) issues the MMAs, warps 2-5 move the
+// accumulator from tensor memory to global memory.  Every wait on an mbarrier is
+// bounded: when a wait runs out the CTA records an error code in *status, all
+// roles leave their loops, the tensor memory is freed and the kernel returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define TC_BM 128            // weight rows (output features) per CTA tile
+#define TC_BK 64             // K elements per stage: 128 bytes of bfloat16, one swizzle row
+#define TC_THREADS 192
+#define TC_WAIT_LIMIT_NS 2000000000ull
+
+enum { TC_ERR_FULL_WAIT = 101, TC_ERR_EMPTY_WAIT = 102, TC_ERR_ACC_WAIT = 103 };
+
+// ------------------------------------------------------------------ PTX wraps
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Waits for the barrier's phase `parity` to complete.  Gives up (returns false)
+// when another role has already given up or after TC_WAIT_LIMIT_NS.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 255u) == 0) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > TC_WAIT_LIMIT_NS) return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x,
+                                            int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+        "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(dst_smem)),
+                 "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes
+// (64 bfloat16) in the 128-byte swizzle: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);   // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                     // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;           // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                     // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                     // SWIZZLE_128B
+    return d;
+}
+
+// kind::f16 instruction descriptor: float accumulator, bfloat16 A and B, both K-major.
+__host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+
+template <int BN, int STAGES>
+struct TcSmem {
+    static constexpr int A_BYTES = TC_BM * TC_BK * 2;
+    static constexpr int B_BYTES = BN * TC_BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int BAR_BYTES = (2 * STAGES + 1) * 8 + 16;
+    static constexpr int TOTAL = TILE_BYTES + BAR_BYTES + 1024;   // slack to align the tiles to 1024
+};
+
+// grid: (ceil(N / 128), ceil(M / BN), splits).  OutT: the type of C when
+// splits == 1; with splits > 1 float partial sums go to `partial[z][M][ld_partial]`.
+template <int BN, int STAGES, typename OutT>
+__global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
+    const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+    OutT* __restrict__ C, long ldc, float* __restrict__ partial, long ld_partial, int M, int N, int K,
+    int kb_per_split, int* __restrict__ status) {
+    using L = TcSmem<BN, STAGES>;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full_bar = (uint64_t*)(tiles + L::TILE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_bar = empty_bar + STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_bar + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_n = blockIdx.x;            // which 128 output features
+    const int tile_m = blockIdx.y;            // which BN tokens
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const int kb_begin = blockIdx.z * kb_per_split;
+    const int kb_end = min(num_kb, kb_begin + kb_per_split);
+    const int n_iters = kb_end - kb_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(acc_bar, 1);
+        // a fault recorded by an earlier CTA or kernel: do no work, so that a stuck
+        // launch drains quickly instead of every CTA waiting out its own limit
+        *abort_flag = (*(volatile int*)status != 0) ? 1 : 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_acc = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer: TMA loads of the weight tile and the token tile
+            for (int it = 0; it < n_iters && !*abort_flag; ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_EMPTY_WAIT); }
+                    break;
+                }
+                unsigned char* a_dst = tiles + s * L::STAGE_BYTES;
+                unsigned char* b_dst = a_dst + L::A_BYTES;
+                mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+                const int k0 = (kb_begin + it) * TC_BK;
+                tma_load_2d(a_dst, &map_w, &full_bar[s], k0, tile_n * TC_BM);
+                tma_load_2d(b_dst, &map_a, &full_bar[s], k0, tile_m * BN);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer
+            constexpr uint32_t idesc = instr_desc_bf16(TC_BM, BN);
+            bool ok = !*abort_flag;
+            for (int it = 0; it < n_iters && ok; ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                if (!mbar_wait(&full_bar[s], ph, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_FULL_WAIT); }
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(tiles + s * L::STAGE_BYTES);
+                const uint32_t b_addr = a_addr + L::A_BYTES;
+                const uint64_t adesc = smem_desc_sw128(a_addr);
+                const uint64_t bdesc = smem_desc_sw128(b_addr);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k) {
+                    // 16 bfloat16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
+                    umma_bf16(tmem_acc, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                              (it > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&empty_bar[s]);         // frees the stage once these MMAs have read it
+            }
+            if (ok) umma_commit(acc_bar);           // accumulator complete
+        }
+    } else {
+        // ---- epilogue: warps 2..5 own tensor-memory lanes 32 * (warp % 4) ..
+        const int quarter = warp & 3;
+        const int o = tile_n * TC_BM + quarter * 32 + lane;         // output feature of this thread
+        bool ok = !*abort_flag;
+        if (ok && n_iters > 0) {
+            ok = mbar_wait(acc_bar, 0, abort_flag);
+            if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_ACC_WAIT); }
+        }
+        tc_fence_after();
+        if (ok) {
+            const uint32_t t_base = tmem_acc + ((uint32_t)(quarter * 32) << 16);
+            const int t0 = tile_m * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                if (t0 + c >= M) break;                               // warp-uniform
+                uint32_t r[16];
+                if (n_iters > 0) {
+                    tmem_ld16(t_base + (uint32_t)c, r);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = 0u;
+                }
+                if (o < N) {
+                    if (gridDim.z == 1) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int t = t0 + c + j;
+                            if (t < M) C[(long)t * ldc + o] = from_f32<OutT>(__uint_as_float(r[j]));
+                        }
+                    } else {
+                        float* p = partial + (long)blockIdx.z * M * ld_partial;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int t = t0 + c + j;
+                            if (t < M) p[(long)t * ld_partial + o] = __uint_as_float(r[j]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_acc, TMEM_COLS);
+    }
+}
+
+// C[t, o] = sum over splits of partial[z][t][o], added in the order z = 0, 1, ...
+template <typename OutT>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, long ld_partial, int splits,
+                                     OutT* __restrict__ C, long ldc, int M, int N) {
+    const int o = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t = blockIdx.y;
+    if (o >= N) return;
+    float acc = 0.0f;
+    for (int z = 0; z < splits; ++z) acc += partial[((long)z * M + t) * ld_partial + o];
+    C[(long)t * ldc + o] = from_f32<OutT>(acc);
+}
+
+// ----------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// A [rows, cols] bfloat16 matrix with `ld` elements between rows, read in boxes
+// of box_rows x 64 elements with the 128-byte swizzle; out-of-range reads give zeros.
+static int make_map(CUtensorMap* map, const void* base, long rows, long cols, long ld, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    if (((uintptr_t)base & 15) || ((ld * 2) & 15)) return (int)cudaErrorMisalignedAddress;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                    box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+template <int BN, int STAGES, typename OutT>
+static int launch_tc(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C, long ldc,
+                     float* partial, long ld_partial, int M, int N, int K, int splits,
+                     int kb_per_split, int* status, cudaStream_t stream) {
+    using L = TcSmem<BN, STAGES>;
+    static bool configured = false;
+    auto kernel = gemm_tc_kernel<BN, STAGES, OutT>;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((N + TC_BM - 1) / TC_BM, (M + BN - 1) / BN, splits);
+    kernel<<<grid, TC_THREADS, L::TOTAL, stream>>>(map_w, map_a, (OutT*)C, ldc, partial, ld_partial, M,
+                                                   N, K, kb_per_split, status);
+    return fl_launch_status();
+}
+
+template <typename OutT>
+static int dispatch_tc(int bn, const CUtensorMap& map_w, const CUtensorMap& map_a, void* C, long ldc,
+                       float* partial, long ld_partial, int M, int N, int K, int splits,
+                       int kb_per_split, int* status, cudaStream_t stream) {
+    switch (bn) {
+        case 16: return launch_tc<16, 6, OutT>(map_w, map_a, C, ldc, partial, ld_partial, M, N, K, splits, kb_per_split, status, stream);
+        case 32: return launch_tc<32, 5, OutT>(map_w, map_a, C, ldc, partial, ld_partial, M, N, K, splits, kb_per_split, status, stream);
+        case 64: return launch_tc<64, 6, OutT>(map_w, map_a, C, ldc, partial, ld_partial, M, N, K, splits, kb_per_split, status, stream);
+        case 128: return launch_tc<128, 6, OutT>(map_w, map_a, C, ldc, partial, ld_partial, M, N, K, splits, kb_per_split, status, stream);
+        case 256: return launch_tc<256, 4, OutT>(map_w, map_a, C, ldc, partial, ld_partial, M, N, K, splits, kb_per_split, status, stream);
+    }
+    return (int)cudaErrorInvalidValue;
+}
+
+// Token-tile width and K splits for a problem: the smallest tile that holds the
+// tokens (up to 256), and as many splits as it takes to give every SM a CTA or two.
+FL_API void fl_gemm_tc_plan(int M, int N, int K, int num_sms, int* bn_out, int* splits_out) {
+    int bn = 16;
+    while (bn < 256 && bn < M) bn *= 2;
+    const int tiles = ((N + TC_BM - 1) / TC_BM) * ((M + bn - 1) / bn);
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const int target = bn <= 32 ? 2 * num_sms : num_sms;
+    int splits = 1;
+    if (tiles < target) {
+        splits = (target + tiles / 2) / tiles;
+        const int most = num_kb / 4 > 0 ? num_kb / 4 : 1;       // at least 4 k-blocks per split
+        if (splits > most) splits = most;
+        if (splits > 16) splits = 16;
+        if (splits < 1) splits = 1;
+    }
+    const int per = (num_kb + splits - 1) / splits;
+    splits = (num_kb + per - 1) / per;                          // no empty split
+    *bn_out = bn;
+    *splits_out = splits;
+}
+
+// A: [M, K] bfloat16 with lda elements between rows; W: [N, K] bfloat16 with ldw;
+// C: [M, N] bfloat16 or float with ldc.  lda and ldw must be multiples of 8 and
+// the bases 16-byte aligned (what a TMA descriptor wants).  `workspace` holds
+// splits * M * round_up(N, 4) floats when the plan splits K (bn and splits come
+// from fl_gemm_tc_plan, or 0 to plan here).
+FL_API int fl_gemm_tc(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc,
+                      int M, int N, int K, int bn, int splits, float* workspace, long workspace_floats,
+                      int num_sms, int* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0) return (int)cudaErrorInvalidValue;
+    if (bn == 0) fl_gemm_tc_plan(M, N, K, num_sms, &bn, &splits);
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    if (splits < 1 || splits > num_kb) return (int)cudaErrorInvalidValue;
+    const int kb_per_split = (num_kb + splits - 1) / splits;
+    if ((long)(splits - 1) * kb_per_split >= num_kb) return (int)cudaErrorInvalidValue;
+    const long ld_partial = ((long)N + 3) / 4 * 4;
+    if (splits > 1 && (workspace == nullptr || workspace_floats < (long)splits * M * ld_partial))
+        return (int)cudaErrorMemoryAllocation;
+    if ((M + bn - 1) / bn > 65535) return (int)cudaErrorInvalidValue;
+    CUtensorMap map_w, map_a;
+    int rc = make_map(&map_w, W, N, K, ldw, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&map_a, A, M, K, lda, bn);
+    if (rc) return rc;
+    if (c_dtype == FL_BF16)
+        rc = dispatch_tc<bf16>(bn, map_w, map_a, C, ldc, workspace, ld_partial, M, N, K, splits, kb_per_split, status, stream);
+    else if (c_dtype == FL_F32)
+        rc = dispatch_tc<float>(bn, map_w, map_a, C, ldc, workspace, ld_partial, M, N, K, splits, kb_per_split, status, stream);
+    else
+        return (int)cudaErrorInvalidValue;
+    if (rc || splits == 1) return rc;
+    dim3 grid((N + 255) / 256, M);
+    if (c_dtype == FL_BF16)
+        splitk_reduce_kernel<bf16><<<grid, 256, 0, stream>>>(workspace, ld_partial, splits, (bf16*)C, ldc, M, N);
+    else
+        splitk_reduce_kernel<float><<<grid, 256, 0, stream>>>(workspace, ld_partial, splits, (float*)C, ldc, M, N);
+    return fl_launch_status();
+}

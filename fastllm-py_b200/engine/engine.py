@@ -43,7 +43,8 @@ class Engine:
         self.workspace = Workspace(self.device, self.max_tokens)
         self.buffers = StepBuffers(self.device, self.max_tokens, config.max_requests,
                                    len(self.cache.groups), bt_stride)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        from ..native.gemm_tc import status_word
+        self.status = status_word(self.device)
         self.no_rotation = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.vocab = decoder.vocab
         self.steps_run = 0

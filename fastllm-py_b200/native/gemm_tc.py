@@ -1,0 +1,115 @@
+"""The tcgen05 tensor-core product behind `Linear` for bfloat16 operands."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_long, c_void_p
+
+import torch
+
+from . import ops
+from .build import load_library
+
+_state: dict = {}
+
+
+def _lib():
+    lib = _state.get("lib")
+    if lib is None:
+        lib = load_library("gemm_tcgen05")
+        lib.fl_gemm_tc.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_long, c_int,
+                                   c_int, c_int, c_int, c_int, c_void_p, c_long, c_int, c_void_p,
+                                   c_void_p]
+        lib.fl_gemm_tc.restype = c_int
+        lib.fl_gemm_tc_plan.argtypes = [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int),
+                                        ctypes.POINTER(c_int)]
+        lib.fl_gemm_tc_plan.restype = None
+        _state["lib"] = lib
+    return lib
+
+
+def status_word(device) -> torch.Tensor:
+    """The int32 word in which kernels of this process record a fault (0 = none)."""
+    key = ("status", str(device))
+    if key not in _state:
+        _state[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _state[key]
+
+
+def _num_sms(device) -> int:
+    key = ("sms", str(device))
+    if key not in _state:
+        _state[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _state[key]
+
+
+_plans: dict = {}
+
+
+def plan(m: int, n: int, k: int, num_sms: int):
+    """(token-tile width, K splits) the kernel will use for this problem."""
+    key = (m, n, k, num_sms)
+    p = _plans.get(key)
+    if p is None:
+        bn, splits = c_int(0), c_int(0)
+        _lib().fl_gemm_tc_plan(m, n, k, num_sms, ctypes.byref(bn), ctypes.byref(splits))
+        p = _plans[key] = (bn.value, splits.value)
+    return p
+
+
+def _workspace(device, floats: int) -> torch.Tensor:
+    """Float scratch for split-K partial sums; grows on demand, never inside a graph capture."""
+    key = ("ws", str(device))
+    ws = _state.get(key)
+    if ws is None or ws.numel() < floats:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("the split-K workspace would have to grow during graph capture; "
+                               "run the step once before capturing it")
+        ws = torch.empty(max(floats, 4 << 20), dtype=torch.float32, device=device)
+        _state[key] = ws
+    return ws
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int = 0, splits: int = 0) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T; a and w bfloat16 (row pitch a multiple of 8
+    elements, base 16-byte aligned), out bfloat16 or float32."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise ops.KernelError("tensor-core gemm takes bfloat16 operands")
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape[0] != m or out.shape[1] != n:
+        raise ops.KernelError(f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    if m == 0:
+        return
+    lda, ldw, ldc = ops._ld(a), ops._ld(w), ops._ld(out)
+    if lda % 8 or ldw % 8 or a.data_ptr() % 16 or w.data_ptr() % 16:
+        raise ops.KernelError("tensor-core gemm: operands must be 16-byte aligned with a row pitch "
+                              "that is a multiple of 8 elements")
+    sms = _num_sms(a.device)
+    if bn == 0:
+        bn, splits = plan(m, n, k, sms)
+    ws, ws_floats = None, 0
+    if splits > 1:
+        ws_floats = splits * m * (-(-n // 4) * 4)
+        ws = _workspace(a.device, ws_floats)
+        ws_floats = ws.numel()
+    rc = _lib().fl_gemm_tc(ops._ptr(a), lda, ops._ptr(w), ldw, ops._ptr(out), ops.dtype_code(out), ldc,
+                           m, n, k, bn, splits, ops._ptr(ws), ws_floats, sms,
+                           ops._ptr(status_word(a.device)), ops._stream())
+    ops._check(rc, "gemm_tcgen05")
+
+
+class TensorCoreLinear:
+    """A weight made ready for the tensor-core kernel: a row pitch that is not a
+    multiple of 16 bytes (K not a multiple of 8) is padded once, at load."""
+
+    def __init__(self, weight: torch.Tensor):
+        n, k = weight.shape
+        if k % 8 or weight.data_ptr() % 16 or not weight.is_contiguous():
+            pitch = -(-k // 8) * 8
+            padded = torch.zeros((n, pitch), dtype=weight.dtype, device=weight.device)
+            padded[:, :k] = weight
+            weight = padded[:, :k]
+        self.weight = weight
+
+    def forward(self, a: torch.Tensor, out: torch.Tensor) -> None:
+        gemm(a, self.weight, out)

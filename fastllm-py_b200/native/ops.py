@@ -215,3 +215,4 @@ def apply_penalties(logits, rows, tokens, counts, repetition, frequency, presenc
 # ---------------------------------------------------------------------- build
 
 BASE_LIBRARIES = ["elementwise", "rope_kv", "attention_simt", "gemm_simt", "sampling"]
+BF16_LIBRARIES = ["gemm_tcgen05"]
