@@ -1,0 +1,321 @@
+#!/usr/bin/env python
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
+
+The default run is the DeepSeek-LLM-7B sized model (30 layers, hidden 4096,
+32 heads, head size 128, feed-forward 11008, vocabulary 102400) with random
+bfloat16 weights: a batch of 8 requests, each with a 2048-token context already
+in the cache, decoding one token per step.  A "step" is one decode step.  It
+prints ONE line of JSON:
+
+  value      decoded tokens per second, K steps timed on the device with CUDA
+             events (the step function plus the sampling kernel, tokens given);
+  e2e        the same through the public scheduler API: every step builds its
+             batch on the host, copies it from pinned memory, runs, samples and
+             reads the token ids back;
+  prefill    one 2048-token prompt in one step: tokens/s, ms and the fraction
+             of the bfloat16 tensor-core peak that its FLOPs / time reach;
+  roofline   the decode step against HBM: bytes it has to read (every weight
+             once, the cache of the live requests) / time / peak bandwidth;
+  points     decode tokens/s at batch 1 and 64.
+
+Weights (13.8 GB) and cache are far larger than the 126 MB L2, so no flush is
+needed between steps.  Peaks come from MEASURED_PEAKS.json when the driver
+wrote it, else from the fallback figures 6650 GB/s and 1590 TFLOP/s.
+
+fastllm-py's counterpart is scripts/bench_one.py:27-100 (128-token prefill, 64
+decode steps, wall-clock per token); its lesson kept here is to time steady
+steps only (docs/handoff-4090-ktransformers.md:45-48).
+"""
+import argparse
+import json
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+MODEL_7B = dict(num_layers=30, hidden_size=4096, num_heads=32, num_kv_heads=32, head_dim=128,
+                intermediate_size=11008, vocab_size=102400, rope_theta=10000.0, rms_norm_eps=1e-6,
+                max_position_embeddings=4096)
+CONTEXT = 2048
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            raw = json.loads(path.read_text())
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(raw.get(k), (int, float)):
+                    out[k] = float(raw[k])
+            out["source"] = "measured"
+            return out
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6 and parts[0].isdigit():
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
+        return {"sm_mhz": int(statistics.median(int(s[0]) for s in self.samples)),
+                "sm_max_mhz": int(self.samples[0][1]), "reasons": reasons,
+                "samples": len(self.samples)}
+
+
+def decode_bytes(cfg, batch, mean_context):
+    """Bytes one decode step has to read: every weight it uses once (bf16), the
+    embedding rows of its tokens, and the cached keys and values of its requests."""
+    h, inter, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    qkv = (cfg.num_heads + 2 * cfg.num_kv_heads) * cfg.head_dim
+    per_layer = h * qkv + cfg.num_heads * cfg.head_dim * h + 3 * h * inter + 2 * h
+    weights = 2 * (cfg.num_layers * per_layer + h + v * h) + 2 * batch * h
+    kv = batch * mean_context * cfg.num_layers * 2 * cfg.num_kv_heads * cfg.head_dim * 2
+    return weights + kv
+
+
+def prefill_flops(cfg, tokens):
+    h, inter = cfg.hidden_size, cfg.intermediate_size
+    qkv = (cfg.num_heads + 2 * cfg.num_kv_heads) * cfg.head_dim
+    linear = 2 * tokens * (h * qkv + cfg.num_heads * cfg.head_dim * h + 3 * h * inter)
+    attention = 2 * cfg.head_dim * cfg.num_heads * tokens * (tokens + 1)       # QK^T and PV, causal
+    return cfg.num_layers * (linear + attention) + 2 * h * cfg.vocab_size
+
+
+def fill_context(engine, rids, context, vocab, gen):
+    """Put `context` random tokens of every request into the cache, in steps under the token budget."""
+    import torch
+
+    from fastllm_py_b200 import StepEntry
+
+    for rid in rids:
+        engine.begin(rid)
+        at = 0
+        while at < context:
+            n = min(engine.max_tokens, context - at)
+            toks = torch.randint(0, vocab, (n,), generator=gen).tolist()
+            engine.step([StepEntry(rid, toks, [])])
+            at += n
+
+
+def time_decode(model, batch, steps, warmup, context, sample_clocks=False):
+    """(tokens/s, ms per step, launches in the timed region, clocks) of device-timed decode steps."""
+    import torch
+
+    from fastllm_py_b200 import StepEntry
+    from fastllm_py_b200.native import ops
+
+    engine = model.engine
+    vocab = engine.vocab
+    gen = torch.Generator().manual_seed(batch)
+    rids = [f"b{batch}_{i}" for i in range(batch)]
+    fill_context(engine, rids, context, vocab, gen)
+    tokens = torch.randint(0, vocab, (warmup + steps, batch), generator=gen).tolist()
+    out = torch.zeros(batch, dtype=torch.int32, device=engine.device)
+
+    def one(i):
+        logits = engine.step([StepEntry(r, [tokens[i][j]], [0]) for j, r in enumerate(rids)])
+        ops.sample(logits, out)
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler() if sample_clocks else None
+    if sampler:
+        sampler.__enter__()
+    before = ops.counter.launches
+    start.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    stop.record()
+    torch.cuda.synchronize()
+    launches = ops.counter.launches - before
+    if sampler:
+        sampler.__exit__()
+    ms = start.elapsed_time(stop) / steps
+    engine.check_status()
+    for r in rids:
+        engine.end(r)
+    return batch * 1000.0 / ms, ms, launches, (sampler.summary() if sampler else None)
+
+
+def time_e2e(model, batch, steps, warmup, context):
+    """Decode tokens/s through the scheduler: host batch building, pinned upload, step, sampling, token read-back."""
+    import torch
+
+    sched = model.scheduler()
+    gen = torch.Generator().manual_seed(1000 + batch)
+    for i in range(batch):
+        prompt = torch.randint(0, model.engine.vocab, (context,), generator=gen).tolist()
+        sched.add_request(prompt, max_new_tokens=warmup + steps + 8)
+    while any(r.remaining > 1 or not r.output for r in sched.requests.values()):
+        sched.step()                                   # prompts in; every request now decodes
+    for _ in range(warmup):
+        sched.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    produced = 0
+    for _ in range(steps):
+        produced += len(sched.step())
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    buf = model.engine.buffers
+    h2d = 4 * (buf.small_size + batch * buf.bt_stride * buf.n_groups)
+    for r in list(sched.running):
+        model.engine.end(r.request_id)
+    return produced / dt, h2d, 4 * batch
+
+
+def time_prefill(model, tokens, repeats, warmup):
+    import torch
+
+    from fastllm_py_b200 import StepEntry
+
+    engine = model.engine
+    gen = torch.Generator().manual_seed(7)
+    toks = torch.randint(0, engine.vocab, (tokens,), generator=gen).tolist()
+    times = []
+    for i in range(warmup + repeats):
+        rid = f"p{i}"
+        engine.begin(rid)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        engine.step([StepEntry(rid, toks, [tokens - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(start.elapsed_time(stop))
+        engine.end(rid)
+    return statistics.median(times)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=MODEL_7B["num_layers"],
+                    help="run fewer layers of the same sizes (the line names both numbers)")
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "fastllm-py's GPU path needs CuPy (cupy-cuda12x), which is not installed and "
+                          "not in the offline wheelhouse; the package itself installs with --no-deps"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(3, args.warmup)
+
+    import torch
+
+    from fastllm_py_b200 import LlamaConfig, Model
+
+    cfg = LlamaConfig(architecture="LlamaForCausalLM", rope_scaling=None, tie_word_embeddings=False,
+                      **dict(MODEL_7B, num_layers=args.layers))
+    pk = peaks()
+    t_load = time.time()
+    biggest = max(args.batch, 1 if args.no_points else 64)
+    pool = biggest * (CONTEXT + warmup + args.steps + 64)
+    model = Model.from_config(cfg, seed=0, dtype="bfloat16", page_size=16, max_tokens=pool,
+                              max_requests=biggest, max_batched_tokens=PREFILL_TOKENS,
+                              max_model_len=4096, cuda_graph=not args.no_graph)
+    torch.cuda.synchronize()
+    load_s = time.time() - t_load
+
+    value, ms, launches, clocks = time_decode(model, args.batch, args.steps, warmup, CONTEXT, True)
+    mean_ctx = CONTEXT + warmup + (args.steps + 1) / 2
+    nbytes = decode_bytes(cfg, args.batch, mean_ctx)
+    achieved = nbytes / (ms * 1e-3) / 1e9
+    e2e, h2d, d2h = time_e2e(model, args.batch, args.steps, warmup, CONTEXT)
+    line = {
+        "metric": "decode tok/s @ batch 8, 2048-token context, DeepSeek-LLM-7B bf16",
+        "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": "DeepSeek-LLM-7B size, random weights", "global_batch": args.batch,
+                   "seq_len": CONTEXT, "parallelism": "single GPU", "layers": args.layers,
+                   "layers_of_config": MODEL_7B["num_layers"], "hidden": cfg.hidden_size,
+                   "heads": cfg.num_heads, "kv_heads": cfg.num_kv_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "page_size": 16, "context_limit": 4096, "prefill_tokens": PREFILL_TOKENS,
+                   "l2": "weights and cache exceed L2; no flush", "cuda_graph": not args.no_graph,
+                   "peaks": pk["source"], "load_s": round(load_s, 1)},
+        "e2e": {"value": round(e2e, 2), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
+    }
+    if not args.no_points:
+        pms = time_prefill(model, PREFILL_TOKENS, 5, 3)
+        flops = prefill_flops(cfg, PREFILL_TOKENS)
+        line["prefill"] = {"value": round(PREFILL_TOKENS * 1000.0 / pms, 1), "tokens": PREFILL_TOKENS,
+                           "ms": round(pms, 3),
+                           "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        points = {}
+        for b in (1, 64):
+            v, _, _, _ = time_decode(model, b, max(8, args.steps // 2), warmup, CONTEXT)
+            points[f"decode_b{b}"] = round(v, 2)
+        line["points"] = points
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -57,7 +57,8 @@ class Model:
         from .native import build as native_build
         from .native.libraries import libraries_for
         native_build.compile_many(libraries_for(engine_config.dtype))
-        plan = arch.make_plan(config, set(store.names()) if store is not None else None)
+        names = None if isinstance(store, _RandomSpec) else set(store.names())
+        plan = arch.make_plan(config, names)
         max_len = engine_config.max_model_len or plan.max_positions
         ctx = BuildContext(dev, dtype, engine_config.page_size, max_len)
         decoder = Decoder(plan, ctx)

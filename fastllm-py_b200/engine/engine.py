@@ -48,6 +48,9 @@ class Engine:
         self.no_rotation = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.vocab = decoder.vocab
         self.steps_run = 0
+        self.use_graph = bool(config.cuda_graph)
+        self._graphs: dict = {}          # step shape -> (graph, logits view, kernels in it)
+        self._warmed: set = set()
 
     # -------------------------------------------------------------- requests
     def begin(self, request_id):
@@ -160,10 +163,40 @@ class Engine:
         engine buffer and is overwritten by the next step."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         step = self.prepare(entries)
-        logits = self.decoder.forward(step)
+        if self.use_graph and step.max_q_len == 1 and step.n_wanted == step.n_tokens:
+            logits = self._decode_with_graph(step)
+        else:
+            logits = self.decoder.forward(step)
         for e in entries:
             self.cache.commit(self.cache.live[e.request_id], len(e.tokens))
         self.steps_run += 1
+        return logits
+
+    def _decode_with_graph(self, step: StepContext) -> torch.Tensor:
+        """A decode-only step (one token per request, every row wanted) replays a
+        CUDA graph captured for its shape.  The first step of a shape runs
+        eagerly (it sizes every buffer), the second is captured, later ones are
+        replayed: the step's inputs already sit in fixed device buffers, so a
+        replay needs nothing but the upload that `prepare` did.  This is the
+        captured decode step of fastllm_py/batched.py:230-275 with the LM head
+        inside the graph."""
+        from ..native import ops
+
+        key = (step.n_tokens, self.decoder.graph_key(step))
+        entry = self._graphs.get(key)
+        if entry is None:
+            if key not in self._warmed:
+                self._warmed.add(key)
+                return self.decoder.forward(step)
+            graph = torch.cuda.CUDAGraph()
+            before = ops.counter.launches
+            with torch.cuda.graph(graph):
+                logits = self.decoder.forward(step)
+            entry = self._graphs[key] = (graph, logits, ops.counter.launches - before)
+            ops.counter.launches = before
+        graph, logits, kernels = entry
+        graph.replay()
+        ops.counter.launches += kernels
         return logits
 
     def check_status(self) -> None:

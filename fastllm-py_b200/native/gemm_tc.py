@@ -95,7 +95,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int = 0, split
     rc = _lib().fl_gemm_tc(ops._ptr(a), lda, ops._ptr(w), ldw, ops._ptr(out), ops.dtype_code(out), ldc,
                            m, n, k, bn, splits, ops._ptr(ws), ws_floats, sms,
                            ops._ptr(status_word(a.device)), ops._stream())
-    ops._check(rc, "gemm_tcgen05")
+    ops._check(rc, "gemm_tcgen05", 2 if splits > 1 else 1)
 
 
 class TensorCoreLinear:

@@ -48,9 +48,19 @@ def _ld(t: torch.Tensor) -> int:
     return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
 
 
-def _check(rc: int, what: str) -> None:
+class _Counter:
+    """Kernels launched by this process through these wrappers (a graph replay
+    adds the number of kernels captured in it)."""
+    launches = 0
+
+
+counter = _Counter()
+
+
+def _check(rc: int, what: str, kernels: int = 1) -> None:
     if rc != 0:
         raise KernelError(f"{what}: CUDA error {rc} at launch")
+    counter.launches += kernels
 
 
 def _require_cuda(*tensors):

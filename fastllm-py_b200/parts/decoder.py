@@ -94,6 +94,16 @@ class Decoder:
                     needs[i] = need
         return needs
 
+    def graph_key(self, step):
+        """What, beside the number of tokens, fixes the launch shapes of a
+        decode-only step: each mixer may add its own (a bucket of the longest
+        sequence, say).  Steps with equal keys may replay one captured graph."""
+        key = []
+        for block in self.blocks:
+            fn = getattr(block.mixer, "graph_key", None)
+            key.append(fn(step) if fn is not None else None)
+        return tuple(key)
+
     # ------------------------------------------------------------------- pass
     def forward(self, step) -> torch.Tensor:
         """Logits [wanted rows, vocab] in float32 for the step's tokens."""
