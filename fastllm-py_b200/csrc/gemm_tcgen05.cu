@@ -435,3 +435,56 @@ FL_API int fl_gemm_tc(const void* A, long lda, const void* W, long ldw, void* C,
         splitk_reduce_kernel<float><<<grid, 256, 0, stream>>>(workspace, ld_partial, splits, (float*)C, ldc, M, N);
     return fl_launch_status();
 }
+
+// ------------------------------------------- entry point that allocates nothing
+// See gemm_tcgen05_static.h: the split-K workspace is this file-scope array, so
+// a caller that cannot allocate can still use the split-K product.
+#include <stdio.h>
+
+#include "gemm_tcgen05_static.h"
+
+#define FL_TC_MAX_DEVICES 64
+
+static __device__ __align__(256) float tc_static_scratch[FL_TC_STATIC_SCRATCH_FLOATS];
+// Device address of the array on each device; found at the first call there.
+// `tc_static_scratch` itself is only a host-side handle in host code.
+static float* tc_static_scratch_addr[FL_TC_MAX_DEVICES];
+
+static void tc_say(char* text, int bytes, const char* fmt, long a, long b) {
+    if (text != nullptr && bytes > 0) snprintf(text, (size_t)bytes, fmt, a, b);
+}
+
+FL_API int fl_gemm_tc_static_scratch(const void* A, long lda, const void* W, long ldw, void* C,
+                                     int c_dtype, long ldc, int M, int N, int K, int bn, int splits,
+                                     int num_sms, int* status, cudaStream_t stream, char* error_text,
+                                     int error_text_bytes) {
+    if (error_text != nullptr && error_text_bytes > 0) error_text[0] = '\0';
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0) return (int)cudaErrorInvalidValue;
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= FL_TC_MAX_DEVICES) {
+        tc_say(error_text, error_text_bytes, "device %ld is beyond the %ld devices this entry point tracks",
+               (long)device, (long)FL_TC_MAX_DEVICES);
+        return FL_TC_ERR_BAD_DEVICE;
+    }
+    if (tc_static_scratch_addr[device] == nullptr) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, tc_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        tc_static_scratch_addr[device] = p;
+    }
+    if (bn == 0 || splits == 0) fl_gemm_tc_plan(M, N, K, num_sms, &bn, &splits);
+    const long ld_partial = ((long)N + 3) / 4 * 4;
+    const long needed = splits > 1 ? (long)splits * M * ld_partial : 0;
+    if (needed > FL_TC_STATIC_SCRATCH_FLOATS) {
+        tc_say(error_text, error_text_bytes,
+               "this product needs %ld floats of split-K scratch; the built-in array holds %ld "
+               "(use fewer splits, fewer tokens per call, or fl_gemm_tc with a workspace of your own)",
+               needed, (long)FL_TC_STATIC_SCRATCH_FLOATS);
+        return FL_TC_ERR_SCRATCH_TOO_SMALL;
+    }
+    return fl_gemm_tc(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, bn, splits, tc_static_scratch_addr[device],
+                      FL_TC_STATIC_SCRATCH_FLOATS, num_sms, status, stream);
+}
