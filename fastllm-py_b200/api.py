@@ -54,14 +54,15 @@ class Model:
         dev = _require_gpu(engine_config.device)
         torch.cuda.set_device(dev)
         dtype = getattr(torch, engine_config.dtype)
-        from .native import build as native_build
-        from .native.libraries import libraries_for
-        native_build.compile_many(libraries_for(engine_config.dtype))
         names = None if isinstance(store, _RandomSpec) else set(store.names())
         plan = arch.make_plan(config, names)
         max_len = engine_config.max_model_len or plan.max_positions
         ctx = BuildContext(dev, dtype, engine_config.page_size, max_len)
         decoder = Decoder(plan, ctx)
+        from .native import build as native_build
+        from .native.libraries import libraries_for
+        head_dims = [p.head_dim for p in decoder.all_parts() if hasattr(p, "head_dim")]
+        native_build.compile_many(libraries_for(engine_config.dtype, head_dims))
         expected = decoder.expected_tensors()
         if isinstance(store, _RandomSpec):
             store = RandomStore(expected, store.seed, store.std, store.norm_std,

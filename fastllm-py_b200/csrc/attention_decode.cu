@@ -1,0 +1,271 @@
+// Split-key paged attention for single decoded tokens, bfloat16, float math.
+//
+// One query token per request attends to hundreds or thousands of cached keys:
+// the work is reading the cache, so the kernel is built to keep many 16-byte
+// loads in flight on every SM.  The keys of a token are cut at fixed absolute
+// positions (every ATD_SPLIT keys); one CTA of four warps handles one
+// (token, query head, split), each warp a quarter of the split.  Inside a warp a
+// key row is spread over HEAD_DIM / 8 lanes (8 bfloat16 = 16 bytes each), so a
+// warp covers 32 / lanes-per-key keys per load and eight loads (four keys' worth
+// of K and of V per lane group) are issued before any is used.  Scores, the running
+// maximum and sum, and the weighted values are float; exp2f on scores pre-scaled
+// by log2(e).  Partial (values, maximum, sum) per split go to a float workspace;
+// a second kernel merges the splits in ascending order.  Split boundaries and
+// the merge order depend on positions only, so a token's result does not depend
+// on what else is in the batch.
+//
+// fastllm-py's counterparts are `attn_decode` (fastllm_py/graph_decode.py:378-420:
+// one block per head, all scores in shared memory, hence a context limit) and
+// `battn` (fastllm_py/batched.py:48-92: one block per (head, sequence), a block
+// reduction per key).  This kernel has no context limit and no per-key barrier.
+//
+// HEAD_DIM is a compile-time constant (-DHEAD_DIM=...), a multiple of 8 up to 256.
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 128
+#endif
+#define ATD_SPLIT 256                      // keys per split
+#define ATD_WARPS 4
+#define ATD_KEYS_PER_WARP (ATD_SPLIT / ATD_WARPS)
+#define ATD_UNROLL 4
+
+static_assert(HEAD_DIM % 8 == 0 && HEAD_DIM >= 8 && HEAD_DIM <= 256, "HEAD_DIM: multiple of 8, at most 256");
+
+constexpr int atd_lanes_per_key() {
+    int l = 1;
+    while (l * 8 < HEAD_DIM) l *= 2;
+    return l;
+}
+constexpr int LPK = atd_lanes_per_key();   // lanes that share one key row (power of two)
+constexpr int KPW = 32 / LPK;              // keys a warp reads per load
+
+struct __align__(16) Bf16x8 { __nv_bfloat162 v[4]; };
+
+__device__ __forceinline__ void unpack8(const Bf16x8& p, float* f) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __bfloat1622float2(p.v[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+// exp2f(a - b) with the conventions of a running softmax: an empty state (-inf) weighs nothing.
+__device__ __forceinline__ float weight_of(float a, float b) {
+    return (a == -CUDART_INF_F) ? 0.0f : exp2f(a - b);
+}
+
+// workspace rows: [HEAD_DIM values | maximum | sum], one row per (token index, head, split)
+#define ATD_ROW (HEAD_DIM + 2)
+
+__global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_kernel(
+    const bf16* __restrict__ q, long q_ld, bf16* __restrict__ out, long out_ld,
+    const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, long page_stride, int page_size,
+    int page_shift, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req,
+    const int* __restrict__ positions, const int* __restrict__ tok_list, int n_heads, int n_kv_heads,
+    int window, float scale_log2e, int n_splits, float* __restrict__ partial) {
+    const int li = blockIdx.x;                              // index into the list of decode tokens
+    const int t = tok_list ? tok_list[li] : li;
+    const int h = blockIdx.y, split = blockIdx.z;
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int split_begin = split * ATD_SPLIT;
+    if (split_begin > pos || split_begin + ATD_SPLIT <= lo) return;       // nothing of this split is visible
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int group = lane / LPK;                           // which of the warp's KPW keys per load
+    const int d0 = (lane % LPK) * 8;                        // this lane's 8 dimensions
+    const bool dim_ok = d0 < HEAD_DIM;
+    const int kvh = h / (n_heads / n_kv_heads);
+    const int* bt = block_table + (long)tok_req[t] * bt_stride;
+    const long head_off = (long)kvh * page_size * HEAD_DIM + d0;
+
+    float qf[8];
+    {
+        Bf16x8 qv;
+        if (dim_ok) qv = *reinterpret_cast<const Bf16x8*>(q + (long)t * q_ld + (long)h * HEAD_DIM + d0);
+        else
+#pragma unroll
+            for (int i = 0; i < 4; ++i) qv.v[i] = __floats2bfloat162_rn(0.0f, 0.0f);
+        unpack8(qv, qf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) qf[i] *= scale_log2e;
+    }
+
+    float m = -CUDART_INF_F, l = 0.0f, o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = 0.0f;
+
+    const int warp_begin = split_begin + warp * ATD_KEYS_PER_WARP;
+#pragma unroll 1
+    for (int base = warp_begin; base < warp_begin + ATD_KEYS_PER_WARP; base += KPW * ATD_UNROLL) {
+        if (base > pos) break;
+        Bf16x8 kv[ATD_UNROLL], vv[ATD_UNROLL];
+        bool valid[ATD_UNROLL];
+#pragma unroll
+        for (int u = 0; u < ATD_UNROLL; ++u) {
+            const int j = base + u * KPW + group;
+            valid[u] = (j >= lo) && (j <= pos);
+            if (valid[u] && dim_ok) {
+                const int pg = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
+                const int off = page_shift >= 0 ? (j & (page_size - 1)) : (j - pg * page_size);
+                const long a = (long)bt[pg] * page_stride + head_off + (long)off * HEAD_DIM;
+                kv[u] = *reinterpret_cast<const Bf16x8*>(k_cache + a);
+                vv[u] = *reinterpret_cast<const Bf16x8*>(v_cache + a);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    kv[u].v[i] = __floats2bfloat162_rn(0.0f, 0.0f);
+                    vv[u].v[i] = kv[u].v[i];
+                }
+            }
+        }
+        float s[ATD_UNROLL];
+        float m_new = m;
+#pragma unroll
+        for (int u = 0; u < ATD_UNROLL; ++u) {
+            float kf[8];
+            unpack8(kv[u], kf);
+            float dot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dot += qf[i] * kf[i];
+#pragma unroll
+            for (int x = LPK / 2; x > 0; x >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, x);
+            s[u] = valid[u] ? dot : -CUDART_INF_F;
+            m_new = fmaxf(m_new, s[u]);
+        }
+        if (m_new != -CUDART_INF_F) {
+            const float corr = weight_of(m, m_new);
+            l *= corr;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] *= corr;
+#pragma unroll
+            for (int u = 0; u < ATD_UNROLL; ++u) {
+                const float p = weight_of(s[u], m_new);
+                l += p;
+                float vf[8];
+                unpack8(vv[u], vf);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] += p * vf[i];
+            }
+            m = m_new;
+        }
+    }
+
+    // merge the warp's key groups (they saw different keys), in a fixed order
+#pragma unroll
+    for (int x = LPK; x < 32; x <<= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, x);
+        const float l2 = __shfl_xor_sync(0xffffffffu, l, x);
+        const float mm = fmaxf(m, m2);
+        const float a1 = weight_of(m, mm), a2 = weight_of(m2, mm);
+        l = l * a1 + l2 * a2;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float o2 = __shfl_xor_sync(0xffffffffu, o[i], x);
+            o[i] = o[i] * a1 + o2 * a2;
+        }
+        m = mm;
+    }
+    // merge the four warps through shared memory, warp 0 first
+    __shared__ float s_o[ATD_WARPS][LPK * 8];
+    __shared__ float s_m[ATD_WARPS], s_l[ATD_WARPS];
+    if (lane < LPK) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s_o[warp][lane * 8 + i] = o[i];
+        if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+    }
+    __syncthreads();
+    if (warp == 0 && lane < LPK && dim_ok) {
+        float mm = s_m[0];
+#pragma unroll
+        for (int w = 1; w < ATD_WARPS; ++w) mm = fmaxf(mm, s_m[w]);
+        float ll = 0.0f, acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+#pragma unroll
+        for (int w = 0; w < ATD_WARPS; ++w) {
+            const float a = weight_of(s_m[w], mm);
+            ll += s_l[w] * a;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += s_o[w][lane * 8 + i] * a;
+        }
+        if (n_splits == 1) {
+            const float inv = 1.0f / ll;
+            bf16* dst = out + (long)t * out_ld + (long)h * HEAD_DIM + d0;
+            Bf16x8 r;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) r.v[i] = __floats2bfloat162_rn(acc[2 * i] * inv, acc[2 * i + 1] * inv);
+            *reinterpret_cast<Bf16x8*>(dst) = r;
+        } else {
+            float* row = partial + (((long)li * n_heads + h) * n_splits + split) * ATD_ROW;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) row[d0 + i] = acc[i];
+            if (lane == 0) { row[HEAD_DIM] = mm; row[HEAD_DIM + 1] = ll; }
+        }
+    }
+}
+
+// out[t, h, :] = sum_s values_s * 2^(m_s - M) / sum_s sum_s * 2^(m_s - M) over the splits the token sees
+__global__ void attention_decode_merge_kernel(const float* __restrict__ partial, bf16* __restrict__ out,
+                                              long out_ld, const int* __restrict__ positions,
+                                              const int* __restrict__ tok_list, int n_heads, int window,
+                                              int n_splits) {
+    const int li = blockIdx.x, h = blockIdx.y;
+    const int t = tok_list ? tok_list[li] : li;
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int s_lo = lo / ATD_SPLIT, s_hi = pos / ATD_SPLIT;
+    const float* rows = partial + ((long)li * n_heads + h) * n_splits * ATD_ROW;
+    float mm = -CUDART_INF_F;
+    for (int s = s_lo; s <= s_hi; ++s) mm = fmaxf(mm, rows[(long)s * ATD_ROW + HEAD_DIM]);
+    float ll = 0.0f;
+    for (int s = s_lo; s <= s_hi; ++s)
+        ll += rows[(long)s * ATD_ROW + HEAD_DIM + 1] * weight_of(rows[(long)s * ATD_ROW + HEAD_DIM], mm);
+    const float inv = 1.0f / ll;
+    for (int d = threadIdx.x; d < HEAD_DIM; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = s_lo; s <= s_hi; ++s)
+            acc += rows[(long)s * ATD_ROW + d] * weight_of(rows[(long)s * ATD_ROW + HEAD_DIM], mm);
+        out[(long)t * out_ld + (long)h * HEAD_DIM + d] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+FL_API int fl_attention_decode_head_dim() { return HEAD_DIM; }
+FL_API int fl_attention_decode_split() { return ATD_SPLIT; }
+FL_API long fl_attention_decode_workspace_floats(int n_list, int n_heads, int n_splits) {
+    return n_splits > 1 ? (long)n_list * n_heads * n_splits * ATD_ROW : 0;
+}
+
+// Tokens tok_list[0..n_list) (or 0..n_list when tok_list is null) of q attend to
+// their requests' cached keys.  n_splits must cover the longest sequence among
+// them: n_splits * ATD_SPLIT > largest position.  `partial` holds
+// fl_attention_decode_workspace_floats(...) floats when n_splits > 1.
+FL_API int fl_attention_decode(const void* q, long q_ld, void* out, long out_ld, const void* k_cache,
+                               const void* v_cache, long page_stride, int page_size,
+                               const int* block_table, int bt_stride, const int* tok_req,
+                               const int* positions, const int* tok_list, int n_list, int n_heads,
+                               int n_kv_heads, int window, float scale, int n_splits, float* partial,
+                               cudaStream_t stream) {
+    if (n_list <= 0) return 0;
+    if (n_heads > 65535 || n_splits < 1 || n_splits > 65535 || n_heads % n_kv_heads) return (int)cudaErrorInvalidValue;
+    if ((q_ld % 8) || (out_ld % 8) || (page_stride % 8)) return (int)cudaErrorMisalignedAddress;
+    if (n_splits > 1 && partial == nullptr) return (int)cudaErrorInvalidValue;
+    int page_shift = -1;
+    if ((page_size & (page_size - 1)) == 0) {
+        page_shift = 0;
+        while ((1 << page_shift) < page_size) ++page_shift;
+    }
+    dim3 grid(n_list, n_heads, n_splits);
+    attention_decode_kernel<<<grid, ATD_WARPS * 32, 0, stream>>>(
+        (const bf16*)q, q_ld, (bf16*)out, out_ld, (const bf16*)k_cache, (const bf16*)v_cache, page_stride,
+        page_size, page_shift, block_table, bt_stride, tok_req, positions, tok_list, n_heads, n_kv_heads,
+        window, scale * 1.4426950408889634f, n_splits, partial);
+    int rc = fl_launch_status();
+    if (rc || n_splits == 1) return rc;
+    dim3 mgrid(n_list, n_heads);
+    attention_decode_merge_kernel<<<mgrid, 128, 0, stream>>>(partial, (bf16*)out, out_ld, positions, tok_list,
+                                                           n_heads, window, n_splits);
+    return fl_launch_status();
+}

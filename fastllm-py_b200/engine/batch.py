@@ -40,7 +40,8 @@ class StepBuffers:
         self.max_tokens, self.max_requests = max_tokens, max_requests
         self.n_groups, self.bt_stride = n_groups, bt_stride
         T, R = max_tokens, max_requests
-        layout = [("token_ids", T), ("positions", T), ("tok_req", T), ("logit_rows", T)]
+        layout = [("token_ids", T), ("positions", T), ("tok_req", T), ("logit_rows", T),
+                  ("decode_tokens", T)]
         layout += [(f"slots{g}", T) for g in range(n_groups)]
         layout += [("req_start", R + 1), ("req_ctx", R), ("req_qlen", R), ("req_slot", R)]
         self.offsets = {}
@@ -97,6 +98,7 @@ class StepContext:
     req_ctx: torch.Tensor          # [n] int32 tokens already cached before the step
     req_qlen: torch.Tensor         # [n] int32 tokens of the request in this step
     req_slot: torch.Tensor         # [n] int32 state slot of each request
+    decode_tokens: torch.Tensor    # [n_decode_tokens] int32 rows of requests that bring exactly one token
     status: torch.Tensor           # [1] int32 device-side error word (0 = fine)
     workspace: object
     no_rotation: torch.Tensor      # stand-in table for mixers without position encoding
@@ -106,6 +108,8 @@ class StepContext:
     slots_host: list = field(default_factory=list)
     max_q_len: int = 0
     max_seq_len: int = 0
+    n_decode_tokens: int = 0       # tokens of requests that bring exactly one token
+    decode_splits: int = 1         # key splits the decode attention kernel is launched with
     _views: dict = field(default_factory=dict)
 
     def cache_view(self, cache_id: int, writes: bool):

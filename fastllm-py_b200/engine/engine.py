@@ -115,6 +115,8 @@ class Engine:
         rctx = buf.host_view("req_ctx")
         rqlen = buf.host_view("req_qlen")
         rslot = buf.host_view("req_slot")
+        dec = buf.host_view("decode_tokens")
+        n_dec = 0
         slot_views = [buf.host_view(f"slots{g}") for g in range(len(cache.groups))]
         bt_views = [buf.host_view(f"bt{g}").reshape(buf.max_requests, buf.bt_stride)
                     for g in range(len(cache.groups))]
@@ -134,6 +136,9 @@ class Engine:
                 cache.slot_mapping(g, rc, q, slot_views[g][at:at + q])
                 cache.block_table_row(g, rc, bt_views[g][r])
             rstart[r], rctx[r], rqlen[r], rslot[r] = at, rc.seq_len, q, rc.slot
+            if q == 1:
+                dec[n_dec] = at
+                n_dec += 1
             q_lens.append(q)
             ctx_lens.append(rc.seq_len)
             slots_host.append(rc.slot)
@@ -151,11 +156,25 @@ class Engine:
             req_ctx=buf.dev_view("req_ctx")[:n],
             req_qlen=buf.dev_view("req_qlen")[:n],
             req_slot=buf.dev_view("req_slot")[:n],
+            decode_tokens=buf.dev_view("decode_tokens")[:n_dec],
             status=self.status, workspace=self.workspace, no_rotation=self.no_rotation,
             q_lens=q_lens, ctx_lens=ctx_lens, slots_host=slots_host,
-            max_q_len=max(q_lens), max_seq_len=max(c + q for c, q in zip(ctx_lens, q_lens)))
+            max_q_len=max(q_lens), max_seq_len=max(c + q for c, q in zip(ctx_lens, q_lens)),
+            n_decode_tokens=n_dec)
+        step.decode_splits = self._decode_splits(step)
         step._views = build_views(cache, buf, n_tokens, n)
         return step
+
+    def _decode_splits(self, step: StepContext) -> int:
+        """Key splits for the decode attention kernel: enough for the longest
+        sequence of the step.  Under graph replay the count is part of the
+        graph's key, so it moves in buckets of 1024 keys instead of every 256."""
+        from ..native.attention import DECODE_SPLIT, decode_splits
+
+        longest = step.max_seq_len
+        if self.use_graph and step.max_q_len == 1:
+            longest = -(-longest // 1024) * 1024
+        return decode_splits(longest)
 
     def step(self, entries) -> torch.Tensor:
         """Run one step; returns float32 logits [wanted places, vocab] on the
@@ -182,7 +201,7 @@ class Engine:
         inside the graph."""
         from ..native import ops
 
-        key = (step.n_tokens, self.decoder.graph_key(step))
+        key = (step.n_tokens, step.decode_splits, self.decoder.graph_key(step))
         entry = self._graphs.get(key)
         if entry is None:
             if key not in self._warmed:

@@ -1,17 +1,120 @@
-"""Choice of the attention kernel for a step.
+"""Choice and launch of the attention kernels for a step.
 
-The CUDA-core kernel (csrc/attention_simt.cu) serves the true 32-bit path and
-is the reference for the others.  bfloat16 steps go to the tensor-core prefill
-kernel and the split-key decode kernel once those are built for the head size.
+bfloat16 steps use the tensor-core prefill kernel for requests that bring more
+than one token and the split-key decode kernel for requests that bring exactly
+one; both are compiled for the model's head size at first use.  Everything else
+(the true 32-bit path) goes to the CUDA-core kernel, which is also the reference
+the other two are tested against.
 """
 from __future__ import annotations
 
+from ctypes import c_float, c_int, c_long, c_void_p
+
 import torch
+
+from . import ops
+from .build import load_library
+
+DECODE_SPLIT = 256          # keys per split of the decode kernel (ATD_SPLIT in attention_decode.cu)
+_libs: dict = {}
+_state: dict = {}
 
 
 def handles(dtype, head_dim: int) -> bool:
-    return False
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
+
+
+def libraries(head_dim: int) -> list:
+    return [("attention_decode", {"HEAD_DIM": head_dim}), ("attention_prefill", {"HEAD_DIM": head_dim})]
+
+
+def _decode_lib(head_dim: int):
+    key = ("decode", head_dim)
+    lib = _libs.get(key)
+    if lib is None:
+        lib = load_library("attention_decode", {"HEAD_DIM": head_dim})
+        lib.fl_attention_decode.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_long,
+                                            c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                            c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]
+        lib.fl_attention_decode.restype = c_int
+        assert lib.fl_attention_decode_head_dim() == head_dim
+        assert lib.fl_attention_decode_split() == DECODE_SPLIT
+        _libs[key] = lib
+    return lib
+
+
+def _prefill_lib(head_dim: int):
+    key = ("prefill", head_dim)
+    lib = _libs.get(key)
+    if lib is None:
+        lib = load_library("attention_prefill", {"HEAD_DIM": head_dim})
+        lib.fl_attention_prefill.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_long,
+                                             c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+        lib.fl_attention_prefill.restype = c_int
+        assert lib.fl_attention_prefill_head_dim() == head_dim
+        _libs[key] = lib
+    return lib
+
+
+def _partials(device, floats: int) -> torch.Tensor:
+    """Float scratch for the decode kernel's per-split results; grows on demand,
+    never inside a graph capture."""
+    key = ("partials", str(device))
+    ws = _state.get(key)
+    if ws is None or ws.numel() < floats:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("the decode-attention workspace would have to grow during graph capture")
+        ws = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        _state[key] = ws
+    return ws
+
+
+def decode_splits(max_seq_len: int) -> int:
+    return max(1, -(-max_seq_len // DECODE_SPLIT))
+
+
+def decode_attention(q, out, cache_tensor, block_table, tok_req, positions, tok_list, n_list, heads,
+                     kv_heads, head_dim, window, scale, page_size, n_splits):
+    """Split-key attention for the tokens in tok_list (None: tokens 0..n_list)."""
+    lib = _decode_lib(head_dim)
+    ws = None
+    if n_splits > 1:
+        ws = _partials(q.device, n_list * heads * n_splits * (head_dim + 2))
+    k_ptr = c_void_p(cache_tensor.data_ptr())
+    v_ptr = c_void_p(cache_tensor.data_ptr() + cache_tensor.stride(1) * cache_tensor.element_size())
+    rc = lib.fl_attention_decode(ops._ptr(q), ops._ld(q), ops._ptr(out), ops._ld(out), k_ptr, v_ptr,
+                                 cache_tensor.stride(0), page_size, ops._ptr(block_table),
+                                 block_table.stride(0), ops._ptr(tok_req), ops._ptr(positions),
+                                 ops._ptr(tok_list), n_list, heads, kv_heads, int(window or 0),
+                                 float(scale), n_splits, ops._ptr(ws), ops._stream())
+    ops._check(rc, "attention_decode", 2 if n_splits > 1 else 1)
+
+
+def prefill_attention(q, out, cache_tensor, block_table, req_start, req_ctx, req_qlen, n_requests,
+                      n_tokens, include_single, heads, kv_heads, head_dim, window, scale, page_size):
+    """Tensor-core attention for the requests of the step that bring several tokens."""
+    lib = _prefill_lib(head_dim)
+    k_ptr = c_void_p(cache_tensor.data_ptr())
+    v_ptr = c_void_p(cache_tensor.data_ptr() + cache_tensor.stride(1) * cache_tensor.element_size())
+    rc = lib.fl_attention_prefill(ops._ptr(q), ops._ld(q), ops._ptr(out), ops._ld(out), k_ptr, v_ptr,
+                                  cache_tensor.stride(0), page_size, ops._ptr(block_table),
+                                  block_table.stride(0), ops._ptr(req_start), ops._ptr(req_ctx),
+                                  ops._ptr(req_qlen), n_requests, n_tokens, 1 if include_single else 0,
+                                  heads, kv_heads, int(window or 0), float(scale), ops._stream())
+    ops._check(rc, "attention_prefill")
 
 
 def paged_attention(q, out, cache, step, heads, kv_heads, head_dim, window, scale):
-    raise NotImplementedError
+    """Attention for every token of a bfloat16 step: the decode kernel for
+    requests with one token, the prefill kernel for the others."""
+    n_dec = step.n_decode_tokens
+    if n_dec:
+        tok_list = None if n_dec == step.n_tokens else step.decode_tokens
+        decode_attention(q, out, cache.tensor, cache.block_table, step.tok_req, step.positions, tok_list,
+                         n_dec, heads, kv_heads, head_dim, window, scale, cache.page_size,
+                         step.decode_splits)
+    if n_dec < step.n_tokens:
+        prefill_attention(q, out, cache.tensor, cache.block_table, step.req_start, step.req_ctx,
+                          step.req_qlen, step.n_requests, step.n_tokens, False, heads, kv_heads,
+                          head_dim, window, scale, cache.page_size)

@@ -76,3 +76,169 @@ def test_cuda_core_gemm(a_dt, w_dt, c_dt):
         ops.gemm_simt(a.to(DEV), w.to(DEV), out)
         tol = 1e-5 * math.sqrt(k) * 4 if c_dt == torch.float32 else 2 ** -8 * float(ref.abs().max()) + 1e-3
         assert float((out.double().cpu() - ref).abs().max()) <= tol
+
+
+# ------------------------------------------------------------------ attention
+
+class AttentionCase:
+    """Requests with cached context and new query tokens, their keys and values
+    scattered over randomly chosen pages, plus a plain float reference."""
+
+    def __init__(self, q_lens, ctx_lens, heads, kv_heads, head_dim, page_size, dtype, seed=0,
+                 spikes=()):
+        g = torch.Generator().manual_seed(seed)
+        self.heads, self.kv_heads, self.head_dim, self.page_size = heads, kv_heads, head_dim, page_size
+        self.q_lens, self.ctx_lens = q_lens, ctx_lens
+        n = len(q_lens)
+        totals = [c + q for c, q in zip(ctx_lens, q_lens)]
+        pages_per = [-(-t // page_size) for t in totals]
+        n_pages = sum(pages_per) + 3
+        perm = torch.randperm(n_pages, generator=g).tolist()
+        self.k_full = [torch.randn(t, kv_heads, head_dim, generator=g) for t in totals]
+        self.v_full = [torch.randn(t, kv_heads, head_dim, generator=g) for t in totals]
+        q_rows = [torch.randn(ql, heads, head_dim, generator=g) for ql in q_lens]
+        # spikes: (request, query row, key position, query head): that key's score stands out
+        for (r, row, key_pos, h) in spikes:
+            direction = torch.randn(head_dim, generator=g)
+            direction = direction / direction.norm()
+            self.k_full[r][key_pos, h // (heads // kv_heads)] = direction * 12.0
+            q_rows[r][row, h] = direction * 12.0
+        rt = lambda x: x.to(dtype).to(torch.float32)            # what the device will hold
+        self.k_full = [rt(k) for k in self.k_full]
+        self.v_full = [rt(v) for v in self.v_full]
+        q_rows = [rt(x) for x in q_rows]
+        self.q_rows = q_rows
+        cache = torch.zeros(n_pages, 2, kv_heads, page_size, head_dim)
+        cache[:] = float("nan") if dtype == torch.float32 else 1e4   # unowned pages hold poison
+        bt = torch.full((n, max(pages_per)), -1, dtype=torch.int32)
+        at = 0
+        for r in range(n):
+            for lp in range(pages_per[r]):
+                pg = perm[at]
+                at += 1
+                bt[r, lp] = pg
+                lo, hi = lp * page_size, min((lp + 1) * page_size, totals[r])
+                cache[pg, 0, :, :hi - lo] = self.k_full[r][lo:hi].transpose(0, 1)
+                cache[pg, 1, :, :hi - lo] = self.v_full[r][lo:hi].transpose(0, 1)
+                cache[pg, :, :, hi - lo:] = 0.0
+        self.cache = cache.to(dtype).to(DEV)
+        self.block_table = bt.to(DEV)
+        self.q = torch.cat([x.reshape(x.shape[0], heads * head_dim) for x in q_rows]).to(dtype).to(DEV)
+        starts = [0]
+        for ql in q_lens:
+            starts.append(starts[-1] + ql)
+        self.n_tokens = starts[-1]
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        self.req_start, self.req_ctx, self.req_qlen = i32(starts), i32(ctx_lens), i32(q_lens)
+        self.tok_req = i32([r for r, ql in enumerate(q_lens) for _ in range(ql)])
+        self.positions = i32([c + i for c, ql in zip(ctx_lens, q_lens) for i in range(ql)])
+        self.decode_tokens = i32([starts[r] for r, ql in enumerate(q_lens) if ql == 1])
+        self.dtype = dtype
+
+    def reference(self, window=None):
+        outs = []
+        rep = self.heads // self.kv_heads
+        for r, (ql, c) in enumerate(zip(self.q_lens, self.ctx_lens)):
+            k = self.k_full[r].repeat_interleave(rep, dim=1)
+            v = self.v_full[r].repeat_interleave(rep, dim=1)
+            for i in range(ql):
+                p = c + i
+                lo = max(0, p - window + 1) if window else 0
+                s = torch.einsum("hd,shd->hs", self.q_rows[r][i], k[lo:p + 1]) * self.head_dim ** -0.5
+                w = torch.softmax(s.double(), dim=-1).float()
+                outs.append(torch.einsum("hs,shd->hd", w, v[lo:p + 1]).reshape(-1))
+        return torch.stack(outs)
+
+    def tolerance(self):
+        biggest = max(float(v.abs().max()) for v in self.v_full)
+        return 1e-5 * biggest if self.dtype == torch.float32 else 2 ** -7 * biggest
+
+
+def run_simt(case, window=None):
+    from fastllm_py_b200.native import ops
+
+    out = torch.zeros_like(case.q)
+    ops.paged_attention_simt(case.q, out, case.cache, case.block_table, case.tok_req, case.positions,
+                             case.heads, case.kv_heads, case.head_dim, window, case.head_dim ** -0.5,
+                             case.page_size)
+    return out.float().cpu()
+
+
+def run_fast(case, window=None):
+    from fastllm_py_b200.native import attention as fast
+
+    out = torch.zeros_like(case.q)
+    scale = case.head_dim ** -0.5
+    n_dec = int(case.decode_tokens.numel())
+    if n_dec:
+        longest = max(c + q for c, q in zip(case.ctx_lens, case.q_lens) if q == 1)
+        fast.decode_attention(case.q, out, case.cache, case.block_table, case.tok_req, case.positions,
+                              None if n_dec == case.n_tokens else case.decode_tokens, n_dec, case.heads,
+                              case.kv_heads, case.head_dim, window, scale, case.page_size,
+                              fast.decode_splits(longest))
+    if n_dec < case.n_tokens:
+        fast.prefill_attention(case.q, out, case.cache, case.block_table, case.req_start, case.req_ctx,
+                               case.req_qlen, len(case.q_lens), case.n_tokens, False, case.heads,
+                               case.kv_heads, case.head_dim, window, scale, case.page_size)
+    return out.float().cpu()
+
+
+ATT_SHAPES = [
+    # q_lens, ctx_lens, heads, kv_heads, head_dim, page_size
+    ([1, 1, 1], [0, 17, 300], 4, 4, 16, 16),
+    ([5, 1, 33, 1], [0, 40, 7, 129], 6, 2, 48, 8),
+    ([70, 2, 1], [0, 130, 600], 4, 2, 80, 32),
+    ([130], [257], 8, 1, 128, 16),
+    ([1, 1], [1023, 1024], 2, 2, 256, 64),
+    ([64, 65, 63], [0, 64, 1], 3, 3, 112, 12),
+]
+
+
+@pytest.mark.parametrize("shape", ATT_SHAPES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 37])
+def test_cuda_core_attention(shape, dtype, window):
+    case = AttentionCase(*shape, dtype, seed=1)
+    diff = (run_simt(case, window) - case.reference(window)).abs().max()
+    assert float(diff) <= case.tolerance()
+
+
+@pytest.mark.parametrize("shape", ATT_SHAPES)
+@pytest.mark.parametrize("window", [None, 37, 200])
+def test_tensor_core_and_split_key_attention(shape, window):
+    case = AttentionCase(*shape, torch.bfloat16, seed=2)
+    diff = (run_fast(case, window) - case.reference(window)).abs().max()
+    assert float(diff) <= case.tolerance()
+
+
+@pytest.mark.parametrize("runner", [run_simt, run_fast])
+def test_a_far_key_among_hundreds_is_found(runner):
+    """One key far back (and one right at a page edge, one at a split edge) gets
+    nearly all the weight: the output must be that key's value."""
+    ctx = 700
+    spikes = [(0, 0, 3, 0), (0, 0, 15, 1), (0, 0, 16, 2), (0, 0, 255, 3), (0, 0, 256, 4),
+              (0, 0, 511, 5), (1, 9, 64, 0), (1, 9, 63, 1), (1, 9, 700, 2), (1, 9, 0, 3)]
+    case = AttentionCase([1, 10], [ctx, ctx], 6, 6, 64, 16, torch.bfloat16, seed=3, spikes=spikes)
+    got = runner(case)
+    ref = case.reference()
+    assert float((got - ref).abs().max()) <= case.tolerance()
+    for (r, row, key_pos, h) in spikes:
+        t = row if r == 0 else 1 + row
+        want = case.v_full[r][key_pos, h]
+        assert float((got[t].reshape(6, 64)[h] - want).abs().max()) < 0.05, (r, row, key_pos, h)
+
+
+@pytest.mark.parametrize("runner", [run_simt, run_fast])
+def test_window_edge(runner):
+    """A dominant key just outside the window must be ignored, one just inside must win."""
+    window, ctx = 50, 300
+    pos = ctx                                   # the single query token's position
+    inside, outside = pos - window + 1, pos - window
+    case = AttentionCase([1, 4], [ctx, ctx], 2, 2, 32, 16, torch.bfloat16, seed=4,
+                         spikes=[(0, 0, outside, 0), (0, 0, inside, 1),
+                                 (1, 3, ctx + 3 - window, 0), (1, 3, ctx + 3 - window + 1, 1)])
+    got = runner(case, window)
+    ref = case.reference(window)
+    assert float((got - ref).abs().max()) <= case.tolerance()
+    assert float((got[0].reshape(2, 32)[1] - case.v_full[0][inside, 1]).abs().max()) < 0.05
+    assert float((got[0].reshape(2, 32)[0] - case.v_full[0][outside, 0]).abs().max()) > 0.5
