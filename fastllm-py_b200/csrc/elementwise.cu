@@ -7,6 +7,27 @@
 // reduced in an order that depends on the block size only.
 #include "common.cuh"
 
+// Four consecutive elements as floats (16-byte loads for float, 8-byte for bfloat16).
+__device__ __forceinline__ void load4(const float* p, float4& v) { v = *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ void load4(const bf16* p, float4& v) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    v = make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, const float4& v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, const float4& v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&a);
+    raw.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+// Can rows of `dim` elements of `elem` bytes be read four at a time?
+static inline bool vec4_ok(int dim, const void* base, long ld, size_t elem) {
+    return base == nullptr || (dim % 4 == 0 && ((uintptr_t)base % (4 * elem)) == 0 && (ld % 4) == 0);
+}
+
 // ------------------------------------------------------------------ embedding
 // out[t, :] = table[ids[t], :] as float (the residual stream is float in both
 // precisions).  An id outside [0, vocab) writes zeros and records 1 + t in
@@ -14,7 +35,7 @@
 template <typename TT>
 __global__ void embed_kernel(const TT* __restrict__ table, long table_ld, const int* __restrict__ ids,
                              float* __restrict__ out, long out_ld, int hidden, int vocab,
-                             int* __restrict__ status) {
+                             int* __restrict__ status, int vec_ok) {
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (long)t * out_ld;
@@ -24,7 +45,15 @@ __global__ void embed_kernel(const TT* __restrict__ table, long table_ld, const 
         return;
     }
     const TT* row = table + (long)id * table_ld;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32<TT>(row[i]);
+    if (vec_ok) {                                   // hidden % 4 == 0, rows 16-byte aligned
+        for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+            float4 v;
+            load4(row + i, v);
+            *reinterpret_cast<float4*>(o + i) = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32<TT>(row[i]);
+    }
 }
 
 FL_API int fl_embed(const void* table, int table_dtype, long table_ld, const int* ids, float* out,
@@ -32,8 +61,9 @@ FL_API int fl_embed(const void* table, int table_dtype, long table_ld, const int
                     cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     FL_DISPATCH(table_dtype, TT,
-                embed_kernel<TT><<<n_tokens, 256, 0, stream>>>((const TT*)table, table_ld, ids, out,
-                                                               out_ld, hidden, vocab, status));
+                embed_kernel<TT><<<n_tokens, 256, 0, stream>>>(
+                    (const TT*)table, table_ld, ids, out, out_ld, hidden, vocab, status,
+                    vec4_ok(hidden, table, table_ld, sizeof(TT)) && vec4_ok(hidden, out, out_ld, 4)));
     return fl_launch_status();
 }
 
@@ -41,7 +71,7 @@ FL_API int fl_embed(const void* table, int table_dtype, long table_ld, const int
 // out = x * (mean(x^2) + eps)^-1/2 * w.  With `delta`, first x += delta (x is
 // the float residual stream and is written back unless rows are gathered).
 // `rows`, when given, selects the input row of each output row.
-template <typename TX, typename TD, typename TW, typename TO, bool ADD>
+template <typename TX, typename TD, typename TW, typename TO, bool ADD, bool VEC>
 __global__ void rmsnorm_kernel(TX* __restrict__ x, long x_ld, const TD* __restrict__ delta,
                                long delta_ld, const TW* __restrict__ w, TO* __restrict__ out,
                                long out_ld, int dim, float eps, const int* __restrict__ rows,
@@ -50,45 +80,73 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, long x_ld, const TD* __restri
     const int r = blockIdx.x;
     const long src = rows ? (long)rows[r] : (long)r;
     TX* xr = x + src * x_ld;
+    const TD* dr = ADD ? delta + src * delta_ld : nullptr;
     TO* o = out + (long)r * out_ld;
+    constexpr int STEP = VEC ? 4 : 1;
     float ss = 0.0f;
-    if (ADD) {
-        const TD* dr = delta + src * delta_ld;
-        for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-            float v = to_f32<TX>(xr[i]) + to_f32<TD>(dr[i]);
-            if (write_back) xr[i] = from_f32<TX>(v);
-            ss += v * v;
-        }
-    } else {
-        for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    for (int i = threadIdx.x * STEP; i < dim; i += blockDim.x * STEP) {
+        if (VEC) {
+            float4 v;
+            load4(xr + i, v);
+            if (ADD) {
+                float4 d;
+                load4(dr + i, d);
+                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+                if (write_back) store4(xr + i, v);
+            }
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        } else {
             float v = to_f32<TX>(xr[i]);
+            if (ADD) {
+                v += to_f32<TD>(dr[i]);
+                if (write_back) xr[i] = from_f32<TX>(v);
+            }
             ss += v * v;
         }
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
-    if (ADD && !write_back) {
-        const TD* dr = delta + src * delta_ld;
-        for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-            float v = to_f32<TX>(xr[i]) + to_f32<TD>(dr[i]);
+    // Second pass.  With write_back each thread re-reads exactly what it wrote
+    // itself; without it the sum is formed again from x and delta.
+    const bool readd = ADD && !write_back;
+    for (int i = threadIdx.x * STEP; i < dim; i += blockDim.x * STEP) {
+        if (VEC) {
+            float4 v, g;
+            load4(xr + i, v);
+            if (readd) {
+                float4 d;
+                load4(dr + i, d);
+                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+            }
+            load4(w + i, g);
+            store4(o + i, make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w));
+        } else {
+            float v = to_f32<TX>(xr[i]);
+            if (readd) v += to_f32<TD>(dr[i]);
             o[i] = from_f32<TO>(v * inv * to_f32<TW>(w[i]));
         }
-    } else {
-        // With write_back the sum is read again from x: each thread re-reads
-        // exactly the elements it wrote itself.
-        for (int i = threadIdx.x; i < dim; i += blockDim.x)
-            o[i] = from_f32<TO>(to_f32<TX>(xr[i]) * inv * to_f32<TW>(w[i]));
     }
+}
+
+static inline int norm_threads(int dim, bool vec) {
+    int t = vec ? (dim + 3) / 4 : dim;
+    t = (t + 31) / 32 * 32;
+    return t < 32 ? 32 : (t > 1024 ? 1024 : t);
 }
 
 FL_API int fl_rmsnorm(const void* x, int x_dtype, long x_ld, const void* w, int w_dtype, void* out,
                       int out_dtype, long out_ld, int n_rows, int dim, float eps, const int* rows,
                       cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    const int threads = dim >= 1024 ? 256 : 128;
-    FL_DISPATCH(x_dtype, TX, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,
-        (rmsnorm_kernel<TX, float, TW, TO, false><<<n_rows, threads, 0, stream>>>(
-            (TX*)x, x_ld, nullptr, 0, (const TW*)w, (TO*)out, out_ld, dim, eps, rows, 0)))));
+    const bool vec = vec4_ok(dim, x, x_ld, x_dtype == FL_F32 ? 4 : 2) && vec4_ok(dim, w, 4, w_dtype == FL_F32 ? 4 : 2) &&
+                     vec4_ok(dim, out, out_ld, out_dtype == FL_F32 ? 4 : 2);
+    const int threads = norm_threads(dim, vec);
+#define FL_NORM_LAUNCH(VEC)                                                                          \
+    FL_DISPATCH(x_dtype, TX, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,                      \
+        (rmsnorm_kernel<TX, float, TW, TO, false, VEC><<<n_rows, threads, 0, stream>>>(               \
+            (TX*)x, x_ld, nullptr, 0, (const TW*)w, (TO*)out, out_ld, dim, eps, rows, 0)))))
+    if (vec) { FL_NORM_LAUNCH(true); } else { FL_NORM_LAUNCH(false); }
+#undef FL_NORM_LAUNCH
     return fl_launch_status();
 }
 
@@ -97,12 +155,17 @@ FL_API int fl_add_rmsnorm(float* resid, long resid_ld, const void* delta, int de
                           long out_ld, int n_rows, int dim, float eps, const int* rows,
                           cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    const int threads = dim >= 1024 ? 256 : 128;
     const int write_back = rows ? 0 : 1;
-    FL_DISPATCH(delta_dtype, TD, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,
-        (rmsnorm_kernel<float, TD, TW, TO, true><<<n_rows, threads, 0, stream>>>(
-            resid, resid_ld, (const TD*)delta, delta_ld, (const TW*)w, (TO*)out, out_ld, dim, eps,
-            rows, write_back)))));
+    const bool vec = vec4_ok(dim, resid, resid_ld, 4) && vec4_ok(dim, delta, delta_ld, delta_dtype == FL_F32 ? 4 : 2) &&
+                     vec4_ok(dim, w, 4, w_dtype == FL_F32 ? 4 : 2) && vec4_ok(dim, out, out_ld, out_dtype == FL_F32 ? 4 : 2);
+    const int threads = norm_threads(dim, vec);
+#define FL_NORM_LAUNCH(VEC)                                                                          \
+    FL_DISPATCH(delta_dtype, TD, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,                  \
+        (rmsnorm_kernel<float, TD, TW, TO, true, VEC><<<n_rows, threads, 0, stream>>>(                \
+            resid, resid_ld, (const TD*)delta, delta_ld, (const TW*)w, (TO*)out, out_ld, dim, eps,   \
+            rows, write_back)))))
+    if (vec) { FL_NORM_LAUNCH(true); } else { FL_NORM_LAUNCH(false); }
+#undef FL_NORM_LAUNCH
     return fl_launch_status();
 }
 

@@ -13,59 +13,51 @@
 // and beyond rot_dim pass through.
 #include "common.cuh"
 
+// One block per (token, head): heads 0 .. n_heads-1 are queries (rotated in
+// place), the next n_kv_heads are keys (rotated into the cache), the last
+// n_kv_heads are values (copied into the cache).
 template <typename T>
 __global__ void rope_kv_kernel(T* __restrict__ qkv, long ld, int n_heads, int n_kv_heads,
                                int head_dim, int rot_dim, const float* __restrict__ cos_table,
                                const float* __restrict__ sin_table, const int* __restrict__ positions,
                                const int* __restrict__ slots, T* __restrict__ k_cache,
-                               T* __restrict__ v_cache, long page_stride, int page_size,
-                               int has_kv) {
-    const int t = blockIdx.x;
-    const int pos = positions[t];
+                               T* __restrict__ v_cache, long page_stride, int page_size) {
+    const int t = blockIdx.x, head = blockIdx.y;
     const int half = rot_dim >> 1;
-    T* row = qkv + (long)t * ld;
-    const float* cs = cos_table + (long)pos * half;
-    const float* sn = sin_table + (long)pos * half;
-
-    // queries: rotated in place
-    for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
-        const int h = idx / half, j = idx - h * half;
-        T* x = row + (long)h * head_dim;
-        const float x1 = to_f32<T>(x[j]), x2 = to_f32<T>(x[j + half]);
-        const float c = cs[j], s = sn[j];
-        x[j] = from_f32<T>(x1 * c - x2 * s);
-        x[j + half] = from_f32<T>(x2 * c + x1 * s);
+    T* x = qkv + (long)t * ld + (long)head * head_dim;
+    if (head < n_heads) {
+        const long pos = positions[t];
+        const float* cs = cos_table + pos * half;
+        const float* sn = sin_table + pos * half;
+        for (int j = threadIdx.x; j < half; j += blockDim.x) {
+            const float x1 = to_f32<T>(x[j]), x2 = to_f32<T>(x[j + half]);
+            const float c = cs[j], s = sn[j];
+            x[j] = from_f32<T>(x1 * c - x2 * s);
+            x[j + half] = from_f32<T>(x2 * c + x1 * s);
+        }
+        return;
     }
-    if (!has_kv) return;
     const int slot = slots[t];
     if (slot < 0) return;
     const long page = slot / page_size;
     const int off = slot - (int)page * page_size;
-    const T* k_in = row + (long)n_heads * head_dim;
-    const T* v_in = k_in + (long)n_kv_heads * head_dim;
-    T* k_out = k_cache + page * page_stride + (long)off * head_dim;
-    T* v_out = v_cache + page * page_stride + (long)off * head_dim;
-    const long head_stride = (long)page_size * head_dim;
-
-    // keys: rotated pairs, then the dimensions that are not rotated
-    for (int idx = threadIdx.x; idx < n_kv_heads * half; idx += blockDim.x) {
-        const int h = idx / half, j = idx - h * half;
-        const T* x = k_in + (long)h * head_dim;
-        const float x1 = to_f32<T>(x[j]), x2 = to_f32<T>(x[j + half]);
-        const float c = cs[j], s = sn[j];
-        T* o = k_out + h * head_stride;
-        o[j] = from_f32<T>(x1 * c - x2 * s);
-        o[j + half] = from_f32<T>(x2 * c + x1 * s);
-    }
-    const int rest = head_dim - rot_dim;
-    for (int idx = threadIdx.x; idx < n_kv_heads * rest; idx += blockDim.x) {
-        const int h = idx / rest, j = rot_dim + (idx - h * rest);
-        k_out[h * head_stride + j] = k_in[(long)h * head_dim + j];
-    }
-    // values: copied
-    for (int idx = threadIdx.x; idx < n_kv_heads * head_dim; idx += blockDim.x) {
-        const int h = idx / head_dim, j = idx - h * head_dim;
-        v_out[h * head_stride + j] = v_in[idx];
+    const bool is_key = head < n_heads + n_kv_heads;
+    const int kvh = is_key ? head - n_heads : head - n_heads - n_kv_heads;
+    T* dst = (is_key ? k_cache : v_cache) + page * page_stride + (long)kvh * page_size * head_dim +
+             (long)off * head_dim;
+    if (is_key) {
+        const long pos = positions[t];
+        const float* cs = cos_table + pos * half;
+        const float* sn = sin_table + pos * half;
+        for (int j = threadIdx.x; j < half; j += blockDim.x) {
+            const float x1 = to_f32<T>(x[j]), x2 = to_f32<T>(x[j + half]);
+            const float c = cs[j], s = sn[j];
+            dst[j] = from_f32<T>(x1 * c - x2 * s);
+            dst[j + half] = from_f32<T>(x2 * c + x1 * s);
+        }
+        for (int j = rot_dim + threadIdx.x; j < head_dim; j += blockDim.x) dst[j] = x[j];
+    } else {
+        for (int j = threadIdx.x; j < head_dim; j += blockDim.x) dst[j] = x[j];
     }
 }
 
@@ -80,8 +72,12 @@ FL_API int fl_rope_kv_write(void* qkv, int dtype, long ld, int n_tokens, int n_h
                             int has_kv, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rot_dim < 0 || rot_dim > head_dim || (rot_dim & 1)) return (int)cudaErrorInvalidValue;
-    FL_DISPATCH(dtype, T, (rope_kv_kernel<T><<<n_tokens, 256, 0, stream>>>(
+    const int heads = n_heads + (has_kv ? 2 * n_kv_heads : 0);
+    if (heads > 65535) return (int)cudaErrorInvalidValue;
+    dim3 grid(n_tokens, heads);
+    const int threads = head_dim >= 128 ? 64 : 32;
+    FL_DISPATCH(dtype, T, (rope_kv_kernel<T><<<grid, threads, 0, stream>>>(
         (T*)qkv, ld, n_heads, n_kv_heads, head_dim, rot_dim, cos_table, sin_table, positions, slots,
-        (T*)k_cache, (T*)v_cache, page_stride, page_size, has_kv)));
+        (T*)k_cache, (T*)v_cache, page_stride, page_size)));
     return fl_launch_status();
 }

@@ -34,7 +34,18 @@ __device__ void block_argmax(const float* __restrict__ x, int vocab, float* best
     __shared__ int s_idx[32];
     float v = -CUDART_INF_F;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    // four independent loads per round, so that a row of 100 000 logits does not
+    // cost a hundred dependent memory round trips per thread
+    int i = threadIdx.x;
+    const int stride = blockDim.x;
+    for (; i + 3 * stride < vocab; i += 4 * stride) {
+        const float a = x[i], b = x[i + stride], c = x[i + 2 * stride], d = x[i + 3 * stride];
+        if (a > v || idx == 0x7fffffff) { v = a; idx = i; }
+        if (b > v) { v = b; idx = i + stride; }
+        if (c > v) { v = c; idx = i + 2 * stride; }
+        if (d > v) { v = d; idx = i + 3 * stride; }
+    }
+    for (; i < vocab; i += stride) {
         const float xi = x[i];
         if (xi > v || idx == 0x7fffffff) { v = xi; idx = i; }
     }
