@@ -1,0 +1,234 @@
+"""Generation through the Python entry point and the scheduler, and the sampler on the device."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+import tiny
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+_models = {}
+
+
+def model_for(name, folder, dtype, **opts):
+    from fastllm_py_b200 import Model
+
+    key = (name, dtype, tuple(sorted(opts.items())))
+    if key not in _models:
+        page = tiny.CONFIGS[name]["page_size"]
+        base = dict(page_size=page, max_tokens=1024, max_requests=8, max_batched_tokens=64,
+                    max_model_len=256)
+        base.update(opts)
+        _models[key] = Model.load(folder, dtype=dtype, **base)
+    return _models[key]
+
+
+def prompts_of(name, lengths, seed=4):
+    cfg = tiny.CONFIGS[name]["config"]
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in lengths]
+
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_greedy_generation_matches_plain_float32(name, model_folders):
+    weights, config = plain.load_folder(model_folders[name])
+    model = model_for(name, model_folders[name], "float32")
+    for prompt in prompts_of(name, [5, 17, 33]):
+        want = plain.generate(weights, config, prompt, 16)
+        assert model.generate(prompt, max_new_tokens=16) == want
+        assert model.generate(prompt, max_new_tokens=16, use_graph=False) == want
+
+
+def test_greedy_generation_bfloat16(model_folders):
+    """bfloat16 greedy follows the plain bfloat16-storage model; where the two part
+    ways the plain model's two best logits must be nearly tied."""
+    name = "tiny_c"
+    weights, config = plain.load_folder(model_folders[name])
+    model = model_for(name, model_folders[name], "bfloat16")
+    for prompt in prompts_of(name, [9, 40]):
+        got = model.generate(prompt, max_new_tokens=12)
+        ids = list(prompt)
+        for tok in got:
+            row = plain.forward(weights, config, ids, store=plain.store_bf16)[-1]
+            best = int(row.argmax())
+            if tok != best:
+                exact = plain.forward(weights, config, ids)[-1]
+                spread = float((row - exact).abs().max())
+                assert float(row[best] - row[tok]) <= 2 * spread + 1e-3
+            ids.append(tok)
+
+
+def test_batch_of_prompts_equals_single_requests(model_folders):
+    name = "tiny_b"
+    model = model_for(name, model_folders[name], "float32")
+    prompts = prompts_of(name, [1, 9, 40, 64, 100])
+    together = model.generate(prompts, max_new_tokens=24)
+    for p, out in zip(prompts, together):
+        assert out == model.generate(p, max_new_tokens=24)
+
+
+def test_temperature_with_seed_matches_plain(model_folders):
+    name = "tiny_b"
+    weights, config = plain.load_folder(model_folders[name])
+    model = model_for(name, model_folders[name], "float32")
+    for i, prompt in enumerate(prompts_of(name, [9, 40])):
+        want = plain.generate(weights, config, prompt, 24, temperature=0.7, seed=11 + i)
+        got = model.generate(prompt, max_new_tokens=24, temperature=0.7, seed=11 + i)
+        assert got == want
+        again = model.generate(prompt, max_new_tokens=24, temperature=0.7, seed=11 + i)
+        assert again == got                                   # the same seed, the same stream
+    assert model.generate(prompt, max_new_tokens=24, temperature=0.7, seed=99) != got
+
+
+def test_stop_token_is_emitted_and_ends(model_folders):
+    name = "tiny_a"
+    model = model_for(name, model_folders[name], "float32")
+    prompt = prompts_of(name, [17])[0]
+    free_run = model.generate(prompt, max_new_tokens=16)
+    stop = free_run[5]
+    first = free_run.index(stop)
+    assert model.generate(prompt, max_new_tokens=16, stop_ids=[stop]) == free_run[:first + 1]
+
+
+def test_page_pressure_changes_no_output(model_folders):
+    """A pool so small that running requests are pushed out and recomputed."""
+    name = "tiny_a"
+    roomy = model_for(name, model_folders[name], "float32")
+    tight = model_for(name, model_folders[name], "float32", max_tokens=112, max_requests=4)
+    prompts = prompts_of(name, [30, 28, 33, 25], seed=8)
+    want = [roomy.generate(p, max_new_tokens=20) for p in prompts]
+    sched = tight.scheduler()
+    ids = [sched.add_request(p, 20) for p in prompts]
+    out = sched.run()
+    assert sched.stats["pushed_out"] >= 1
+    assert [out[i] for i in ids] == want
+    tight.engine.cache.check()
+    assert not tight.engine.cache.live
+
+
+def test_graph_replay_equals_eager_bit_for_bit(model_folders):
+    """The captured decode step against the same step run eagerly
+    (the idea of fastllm_py/graph_decode.py:994-1032)."""
+    from fastllm_py_b200 import StepEntry
+
+    name = "tiny_b"
+    rows = {}
+    for use_graph in (False, True):
+        model = model_for(name, model_folders[name], "bfloat16", cuda_graph=use_graph)
+        eng = model.engine
+        eng.use_graph = use_graph
+        prompts = prompts_of(name, [7, 19, 3], seed=6)
+        for i, p in enumerate(prompts):
+            eng.begin(i)
+            eng.step([StepEntry(i, p, [])])
+        got = []
+        for k in range(6):                                  # steps 0 (eager warm-up), 1 (capture), 2.. (replay)
+            logits = eng.step([StepEntry(i, [(k * 7 + i) % 300], [0]) for i in range(3)])
+            got.append(logits.to("cpu", copy=True))
+        for i in range(3):
+            eng.end(i)
+        rows[use_graph] = got
+    if True in rows and False in rows:
+        for a, b in zip(rows[False], rows[True]):
+            assert torch.equal(a, b)
+
+
+# ------------------------------------------------------------------- sampler
+
+def test_sampler_matches_plain_sampler():
+    from fastllm_py_b200.native import ops
+
+    g = torch.Generator().manual_seed(0)
+    vocab, rows = 1000, 64
+    logits = (torch.randn(rows, vocab, generator=g) * 2.5)
+    combos = [dict(), dict(top_k=7), dict(top_p=0.6), dict(min_p=0.15), dict(top_k=40, top_p=0.8, min_p=0.02),
+              dict(top_k=1), dict(top_p=0.999)]
+    rng = np.random.default_rng(1)
+    for combo in combos:
+        temp = 0.3 + 1.5 * rng.random(rows)
+        uni = rng.random(rows)
+        dev = lambda a, dt: torch.tensor(a, dtype=dt, device=DEV)
+        out = torch.zeros(rows, dtype=torch.int32, device=DEV)
+        ops.sample(logits.to(DEV), out, dev(temp, torch.float32),
+                   dev([combo.get("top_k", 0)] * rows, torch.int32),
+                   dev([combo.get("top_p", 1.0)] * rows, torch.float32),
+                   dev([combo.get("min_p", 0.0)] * rows, torch.float32), dev(uni, torch.float64))
+        got = out.cpu().tolist()
+        for r in range(rows):
+            want = plain.sample(logits[r], float(np.float32(temp[r])), uniform=float(uni[r]), **combo)
+            if got[r] != want:
+                # only a draw that falls on the edge between two tokens may differ
+                p = plain.probabilities(logits[r], float(np.float32(temp[r])), **combo)
+                cdf = torch.cumsum(p, 0)
+                assert p[got[r]] > 0, f"{combo}: token {got[r]} was filtered out"
+                edge = cdf[min(got[r], want)]
+                assert abs(float(edge) - uni[r]) < 1e-5, (combo, r, got[r], want)
+
+
+def test_greedy_is_first_argmax_and_ignores_filters():
+    from fastllm_py_b200.native import ops
+
+    logits = torch.zeros(3, 500)
+    logits[0, 77] = logits[0, 300] = 5.0                     # a tie: the first index wins
+    logits[1, 499] = 1.0
+    logits[2, 0] = 1.0
+    out = torch.zeros(3, dtype=torch.int32, device=DEV)
+    ops.sample(logits.to(DEV), out)
+    assert out.cpu().tolist() == [77, 499, 0]
+    zero = torch.zeros(3, dtype=torch.float32, device=DEV)
+    ops.sample(logits.to(DEV), out, zero, torch.full((3,), 5, dtype=torch.int32, device=DEV),
+               torch.full((3,), 0.1, device=DEV), zero, torch.zeros(3, dtype=torch.float64, device=DEV))
+    assert out.cpu().tolist() == [77, 499, 0]
+
+
+def test_sampled_frequencies_follow_softmax():
+    from fastllm_py_b200.native import ops
+
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5, 1.5]])
+    n = 20000
+    big = logits.repeat(n, 1).to(DEV)
+    uni = torch.tensor(np.random.default_rng(3).random(n), dtype=torch.float64, device=DEV)
+    out = torch.zeros(n, dtype=torch.int32, device=DEV)
+    ops.sample(big, out, torch.full((n,), 0.9, device=DEV), None, None, None, uni)
+    freq = torch.bincount(out.cpu().long(), minlength=6).float() / n
+    assert float((freq - torch.softmax(logits[0] / 0.9, 0)).abs().max()) < 0.02
+
+
+def test_penalties_kernel():
+    from fastllm_py_b200.native import ops
+
+    g = torch.Generator().manual_seed(5)
+    logits = torch.randn(2, 50, generator=g) * 3
+    counts = [{3: 2, 7: 1, 49: 4}, {0: 1}]
+    rep, freq, pres = [1.3, 1.0], [0.2, 0.0], [0.1, 0.5]
+    items = [(r, t, c) for r, d in enumerate(counts) for t, c in d.items()]
+    arr = torch.tensor(items, dtype=torch.int32).t().contiguous().to(DEV)
+    dev = logits.to(DEV)
+    f = lambda v: torch.tensor(v, dtype=torch.float32, device=DEV)
+    ops.apply_penalties(dev, arr[0], arr[1], arr[2], f(rep), f(freq), f(pres))
+    for r in range(2):
+        want = plain.apply_penalties(logits[r], counts[r], rep[r], freq[r], pres[r])
+        assert float((dev[r].cpu().double() - want).abs().max()) < 1e-5
+
+
+def test_sampling_options_through_generate(model_folders):
+    name = "tiny_a"
+    weights, config = plain.load_folder(model_folders[name])
+    model = model_for(name, model_folders[name], "float32")
+    prompt = prompts_of(name, [12])[0]
+    opts = dict(temperature=0.9, top_k=20, top_p=0.9, min_p=0.01, repetition_penalty=1.2,
+                frequency_penalty=0.1, presence_penalty=0.1)
+    got = model.generate(prompt, max_new_tokens=12, seed=3, **opts)
+    # the plain loop with the same penalties and uniforms
+    rng = np.random.default_rng(3)
+    ids, counts, want = list(prompt), {}, []
+    for _ in range(12):
+        row = plain.forward(weights, config, ids)[-1]
+        row = plain.apply_penalties(row, counts, 1.2, 0.1, 0.1)
+        tok = plain.sample(row, 0.9, top_p=0.9, top_k=20, min_p=0.01, uniform=float(rng.random()))
+        counts[tok] = counts.get(tok, 0) + 1
+        want.append(tok)
+        ids.append(tok)
+    assert got == want
