@@ -55,13 +55,16 @@ def rope_tables(positions, head_dim, theta, scaling_factor=None):
     (fastllm_py/kernels/ops.py:79); linear scaling divides the integer
     positions by the factor in float64 before the float32 cast
     (fastllm_py/model.py:337-338, ops.py:80)."""
-    exponent = torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim
-    inv_freq = 1.0 / (torch.tensor(theta, dtype=torch.float32) ** exponent)
-    pos = positions.to(torch.float64)
+    import numpy as np
+
+    # NumPy, as in the reference: its float32 power differs from torch's in the last bit,
+    # and that bit times a position of a few hundred is visible in the angles.
+    inv_freq = 1.0 / (theta ** (np.arange(0, head_dim, 2, dtype=np.float32) / head_dim))
+    pos = np.asarray(positions)
     if scaling_factor is not None:
         pos = pos / float(scaling_factor)
-    ang = pos.to(torch.float32)[:, None] * inv_freq[None, :]
-    return torch.cos(ang), torch.sin(ang)
+    ang = pos.astype(np.float32)[:, None] * inv_freq[None, :]
+    return torch.from_numpy(np.cos(ang)), torch.from_numpy(np.sin(ang))
 
 
 def apply_rope(x, cos, sin):

@@ -1,0 +1,343 @@
+"""Each part alone against the plain function of the same name, and toy parts
+defined here that the framework has never heard of.
+
+The toy architecture below registers, without a change to the package's files:
+  * a mixer with state of its own (a running mean of its inputs per request,
+    kept in a fixed-size state slot);
+  * attention layers with a window, a layer that runs twice, and a layer that
+    reads another layer's cache;
+and is built, loaded with random weights and stepped through the engine in
+portions, then compared with a plain whole-sequence implementation.
+"""
+import types
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def harness(needs, dtype, page_size=8, max_tokens=256):
+    """An Engine around a stand-in decoder, to obtain real StepContexts for single parts."""
+    from fastllm_py_b200.config import EngineConfig
+    from fastllm_py_b200.engine import Engine
+    from fastllm_py_b200.parts import BuildContext
+
+    ctx = BuildContext(torch.device(DEV), dtype, page_size, 256)
+    decoder = types.SimpleNamespace(ctx=ctx, vocab=100, cache_needs=lambda: needs,
+                                    graph_key=lambda step: ())
+    cfg = EngineConfig(dtype="float32" if dtype == torch.float32 else "bfloat16", page_size=page_size,
+                       max_tokens=max_tokens, max_requests=4, max_batched_tokens=128, cuda_graph=False)
+    return Engine(decoder, cfg, 256, max_tokens // page_size), ctx
+
+
+def tol_for(dtype, scale=1.0):
+    return 2e-5 * scale if dtype == torch.float32 else 2 ** -7 * scale
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part(dtype):
+    from fastllm_py_b200.parts import PartSpec, ResidualStream, build_part
+
+    _, ctx = harness({}, dtype)
+    size, eps = 200, 3e-6
+    part = build_part("norm", PartSpec("rmsnorm", dict(size=size, eps=eps), {"weight": "w"}), ctx)
+    w = (1 + 0.1 * torch.randn(size)).to(torch.bfloat16)
+    part.load({"weight": w.to(DEV)})
+    x = torch.randn(9, size)
+    delta = torch.randn(9, size).to(dtype)
+    stream = ResidualStream(x.clone().to(DEV))
+    out = torch.zeros(9, size, dtype=dtype, device=DEV)
+    part.apply(stream, out)
+    want = plain.rms_norm(x, w.float(), eps)
+    assert float((out.float().cpu() - want).abs().max()) <= tol_for(dtype, float(want.abs().max()))
+    stream.pending = delta.to(DEV)
+    part.apply(stream, out)
+    summed = x + delta.float()
+    want = plain.rms_norm(summed, w.float(), eps)
+    assert float((out.float().cpu() - want).abs().max()) <= tol_for(dtype, float(want.abs().max()))
+    assert float((stream.x.cpu() - summed).abs().max()) < 1e-6 and stream.pending is None
+    rows = torch.tensor([7, 0, 3], dtype=torch.int32, device=DEV)
+    picked = torch.zeros(3, size, dtype=dtype, device=DEV)
+    part.apply(stream, picked, rows=rows)
+    assert float((picked.float().cpu() - want[[7, 0, 3]]).abs().max()) <= tol_for(dtype, float(want.abs().max()))
+
+
+def test_rotary_tables_match_plain():
+    from fastllm_py_b200.parts import PartSpec, build_part
+
+    _, ctx = harness({}, torch.float32)
+    for rot, theta, factor in [(16, 10000.0, None), (48, 100000.0, 4.0), (128, 50000.0, 2.0)]:
+        scaling = ("linear", factor) if factor else None
+        part = build_part("position", PartSpec("rotary", dict(rot_dim=rot, theta=theta, scaling=scaling)), ctx)
+        cos, sin = part.tables()
+        pcos, psin = plain.rope_tables(torch.arange(256), rot, theta, factor)
+        assert float((cos.cpu() - pcos).abs().max()) < 2e-6 and float((sin.cpu() - psin).abs().max()) < 2e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_and_io_parts(dtype):
+    from fastllm_py_b200 import StepEntry
+    from fastllm_py_b200.parts import PartSpec, build_part
+
+    eng, ctx = harness({}, dtype)
+    hidden, inter, vocab = 72, 172, 100
+    rt = lambda t: t.to(torch.bfloat16)
+    wg, wu, wd = rt(torch.randn(inter, hidden) * 0.1), rt(torch.randn(inter, hidden) * 0.1), rt(torch.randn(hidden, inter) * 0.1)
+    ffn = build_part("feed_forward", PartSpec("swiglu", dict(hidden_size=hidden, intermediate_size=inter),
+                                              dict(gate="g", up="u", down="d")), ctx)
+    ffn.load({"gate": wg.to(DEV), "up": wu.to(DEV), "down": wd.to(DEV)})
+    eng.begin("r")
+    step = eng.prepare([StepEntry("r", list(range(11)), [10])])
+    h = torch.randn(11, hidden).to(dtype)
+    out = torch.zeros(11, hidden, dtype=dtype, device=DEV)
+    ffn.forward(h.to(DEV), out, step)
+    store = plain.store_bf16 if dtype == torch.bfloat16 else plain.identity
+    hf = h.float()
+    want = plain.linear(store(plain.swiglu(store(plain.linear(hf, wg.float())), store(plain.linear(hf, wu.float())))), wd.float())
+    assert float((out.float().cpu() - want).abs().max()) <= tol_for(dtype, float(want.abs().max()) + 1)
+
+    table = rt(torch.randn(vocab, hidden))
+    emb = build_part("embedding", PartSpec("table", dict(vocab_size=vocab, hidden_size=hidden), {"weight": "e"}), ctx)
+    emb.load({"weight": table.to(DEV)})
+    x = torch.zeros(11, hidden, device=DEV)
+    emb.forward(step, x)
+    assert torch.equal(x.cpu(), plain.embedding(table.float(), torch.arange(11)))
+    head = build_part("head", PartSpec("linear", dict(vocab_size=vocab, hidden_size=hidden), {"weight": "e"}), ctx)
+    head.load({"weight": table.to(DEV)})
+    logits = torch.zeros(11, vocab, device=DEV)
+    head.forward(h.to(DEV), logits)
+    want = plain.linear(hf, table.float())
+    assert float((logits.cpu() - want).abs().max()) <= tol_for(torch.float32 if dtype == torch.float32 else dtype,
+                                                               float(want.abs().max()))
+    eng.end("r")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 13])
+def test_attention_part_in_portions(dtype, window):
+    """The attention mixer alone: a sequence fed in portions equals plain attention of the whole."""
+    from fastllm_py_b200 import StepEntry
+    from fastllm_py_b200.cache import PagedKV
+    from fastllm_py_b200.parts import PartSpec, build_part
+
+    hidden, heads, kv_heads, hd, T = 72, 6, 2, 32, 61
+    eng, ctx = harness({0: PagedKV(kv_heads, hd, window)}, dtype)
+    spec = PartSpec("attention", dict(hidden_size=hidden, num_heads=heads, num_kv_heads=kv_heads, head_dim=hd,
+                                      window=window,
+                                      position=PartSpec("rotary", dict(rot_dim=hd, theta=10000.0, scaling=None))),
+                    dict(q="q", k="k", v="v", o="o"))
+    att = build_part("mixer", spec, ctx)
+    rt = lambda t: t.to(torch.bfloat16)
+    w = {n: rt(torch.randn(s) * 0.15) for n, s in
+         dict(q=(heads * hd, hidden), k=(kv_heads * hd, hidden), v=(kv_heads * hd, hidden), o=(hidden, heads * hd)).items()}
+    att.load({n: t.to(DEV) for n, t in w.items()})
+    h = torch.randn(T, hidden).to(dtype)
+    got = torch.zeros(T, hidden, dtype=dtype, device=DEV)
+    eng.begin("r")
+    at = 0
+    for n in [7, 2, 19, 1, 1, 30, 1]:
+        step = eng.prepare([StepEntry("r", [0] * n, [])])
+        att.forward(h[at:at + n].to(DEV), got[at:at + n], step, step.cache_view(0, True))
+        eng.cache.commit(eng.cache.live["r"], n)
+        at += n
+    assert at == T
+    store = plain.store_bf16 if dtype == torch.bfloat16 else plain.identity
+    hf = h.float()
+    q = store(plain.linear(hf, w["q"].float())).reshape(T, heads, hd)
+    k = store(plain.linear(hf, w["k"].float())).reshape(T, kv_heads, hd)
+    v = store(plain.linear(hf, w["v"].float())).reshape(T, kv_heads, hd)
+    cos, sin = plain.rope_tables(torch.arange(T), hd, 10000.0)
+    ctxv = store(plain.attention(store(plain.apply_rope(q, cos, sin)), store(plain.apply_rope(k, cos, sin)), v, window))
+    want = plain.linear(ctxv, w["o"].float())
+    assert float((got.float().cpu() - want).abs().max()) <= tol_for(dtype, float(want.abs().max()) + 1)
+    eng.cache.check()
+    eng.end("r")
+
+
+# ------------------------------------------------------- a toy architecture
+
+@dataclass(frozen=True)
+class ToyConfig:
+    hidden_size: int = 48
+    vocab_size: int = 97
+    num_heads: int = 3
+    head_dim: int = 16
+    window: int = 11
+    eps: float = 2e-6
+
+    @classmethod
+    def from_hf(cls, raw):
+        return cls(raw["hidden_size"], raw["vocab_size"], raw["num_heads"], raw["head_dim"], raw["window"], raw["eps"])
+
+    def to_hf(self):
+        return dict(architectures=["ToyForCausalLM"], **self.__dict__)
+
+
+def register_toy():
+    from fastllm_py_b200.cache import FixedState
+    from fastllm_py_b200.config import register_architecture
+    from fastllm_py_b200.parts import LayerRun, LayerSpec, ModelPlan, Part, PartSpec, register_part
+    from fastllm_py_b200.parts.linear import Linear
+
+    @register_part("mixer", "toy_running_mean")
+    class RunningMean(Part):
+        """out_t = W . mean(h_0 .. h_t) over the request's own tokens.  The state
+        (sum of inputs, count) lives in the request's fixed-size state slot."""
+        category = "mixer"
+
+        def __init__(self, spec, ctx):
+            super().__init__(spec, ctx)
+            self.hidden = spec.params["hidden_size"]
+            self.proj = None
+
+        def cache_need(self):
+            return FixedState((self.hidden + 1,), "float32")
+
+        def weight_shapes(self):
+            return {"w": (self.hidden, self.hidden)}
+
+        def load(self, tensors):
+            self.proj = Linear([tensors["w"]])
+
+        def forward(self, h, out, step, cache):
+            state = cache.tensor
+            means = torch.empty_like(h)
+            at = 0
+            for q, ctx_len, slot in zip(step.q_lens, step.ctx_lens, step.slots_host):
+                if ctx_len == 0:
+                    state[slot].zero_()                       # a new request: reset its state
+                rows = h[at:at + q].float()
+                sums = state[slot, :self.hidden] + torch.cumsum(rows, dim=0)
+                counts = state[slot, self.hidden] + torch.arange(1, q + 1, device=h.device)
+                means[at:at + q] = (sums / counts[:, None]).to(h.dtype)
+                state[slot, :self.hidden] = sums[-1]
+                state[slot, self.hidden] = counts[-1]
+                at += q
+            self.proj.forward(means, out)
+
+    def make_plan(cfg, names=None):
+        def norm(n):
+            return PartSpec("rmsnorm", dict(size=cfg.hidden_size, eps=cfg.eps), {"weight": n})
+
+        def ffn(i):
+            return PartSpec("swiglu", dict(hidden_size=cfg.hidden_size, intermediate_size=2 * cfg.hidden_size),
+                            {s: f"l{i}.ffn.{s}" for s in ("gate", "up", "down")})
+
+        def attn(i, window, shares):
+            names_ = {"q": f"l{i}.q", "o": f"l{i}.o"}
+            if not shares:
+                names_.update(k=f"l{i}.k", v=f"l{i}.v")
+            return PartSpec("attention", dict(
+                hidden_size=cfg.hidden_size, num_heads=cfg.num_heads, num_kv_heads=cfg.num_heads,
+                head_dim=cfg.head_dim, window=window, shares_cache=shares,
+                position=PartSpec("rotary", dict(rot_dim=cfg.head_dim, theta=10000.0, scaling=None))), names_)
+
+        mixers = [attn(0, None, False), attn(1, cfg.window, False),
+                  PartSpec("toy_running_mean", dict(hidden_size=cfg.hidden_size), {"w": "l2.w"}),
+                  attn(3, None, True)]
+        layers = [LayerSpec("prenorm", m, ffn(i), {"mixer": norm(f"l{i}.n1"), "feed_forward": norm(f"l{i}.n2")})
+                  for i, m in enumerate(mixers)]
+        # order: full attention, windowed, state mixer, windowed AGAIN (its own second cache),
+        # then a layer that reads the first run's cache
+        order = [LayerRun(0), LayerRun(1), LayerRun(2), LayerRun(1), LayerRun(3, cache=0)]
+        io = dict(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size)
+        return ModelPlan(cfg.hidden_size, cfg.vocab_size, 256, PartSpec("table", io, {"weight": "emb"}), layers,
+                         order, norm("final"), PartSpec("linear", io, {"weight": "emb"}))
+
+    register_architecture("ToyForCausalLM", ToyConfig, make_plan)
+    return make_plan
+
+
+def toy_plain(w, cfg, ids, store):
+    """Whole-sequence plain forward of the toy architecture."""
+    T = len(ids)
+    x = plain.embedding(w["emb"], torch.as_tensor(ids))
+    cos, sin = plain.rope_tables(torch.arange(T), cfg.head_dim, 10000.0)
+    H, D = cfg.num_heads, cfg.head_dim
+    kv0 = None
+    for run, (layer, kind) in enumerate([(0, "full"), (1, "window"), (2, "mean"), (1, "window"), (3, "shared")]):
+        p = f"l{layer}."
+        h = store(plain.rms_norm(x, w[p + "n1"], cfg.eps))
+        if kind == "mean":
+            mean = store(torch.cumsum(h, 0) / torch.arange(1, T + 1)[:, None])
+            delta = store(plain.linear(mean, w[p + "w"]))
+        else:
+            q = store(plain.apply_rope(store(plain.linear(h, w[p + "q"])).reshape(T, H, D), cos, sin))
+            if kind == "shared":
+                k, v = kv0
+            else:
+                k = store(plain.apply_rope(store(plain.linear(h, w[p + "k"])).reshape(T, H, D), cos, sin))
+                v = store(plain.linear(h, w[p + "v"])).reshape(T, H, D)
+                if run == 0:
+                    kv0 = (k, v)
+            ctxv = store(plain.attention(q, k, v, cfg.window if kind == "window" else None))
+            delta = store(plain.linear(ctxv, w[p + "o"]))
+        x = x + delta
+        h = store(plain.rms_norm(x, w[p + "n2"], cfg.eps))
+        a = store(plain.swiglu(store(plain.linear(h, w[p + "ffn.gate"])), store(plain.linear(h, w[p + "ffn.up"]))))
+        x = x + store(plain.linear(a, w[p + "ffn.down"]))
+    return plain.linear(store(plain.rms_norm(x, w["final"], cfg.eps)), w["emb"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_with_state_window_repeat_and_shared_cache(dtype, tmp_path):
+    import json
+
+    from safetensors.torch import load_file
+
+    from fastllm_py_b200 import Model, StepEntry
+    from fastllm_py_b200.weights import write_model_folder
+
+    register_toy()
+    cfg = ToyConfig()
+    folder = write_model_folder(cfg, tmp_path / "toy", seed=5, std=0.12, norm_std=0.1)
+    assert json.loads((folder / "config.json").read_text())["architectures"] == ["ToyForCausalLM"]
+    model = Model.load(folder, dtype=dtype, page_size=4, max_tokens=256, max_requests=4,
+                       max_batched_tokens=64, max_model_len=128, cuda_graph=False)
+    eng = model.engine
+    # three cache groups: full attention (run 0), window (runs 1 and 3), and state for run 2
+    assert len(eng.cache.groups) == 2 and list(eng.cache.state_tensors) == [2]
+    assert sorted(eng.cache.groups[1].cache_ids) == [1, 3]
+    weights = {k: v.float() for k, v in load_file(str(folder / "model.safetensors")).items()}
+    store = plain.store_bf16 if dtype == "bfloat16" else plain.identity
+    rng = np.random.default_rng(2)
+    seqs = {"a": rng.integers(0, cfg.vocab_size, 50).tolist(), "b": rng.integers(0, cfg.vocab_size, 37).tolist()}
+    want = {r: toy_plain(weights, cfg, ids, store) for r, ids in seqs.items()}
+    exact = {r: toy_plain(weights, cfg, ids, plain.identity) for r, ids in seqs.items()}
+    tol = 1e-4 if dtype == "float32" else \
+        2 * max(float((want[r] - exact[r]).abs().max()) for r in seqs) + 1e-3
+    fed = {"a": 0, "b": 0}
+    plan = [("a", 9), ("b", 2), ("a", 1), ("a", 1), ("b", 20), ("a", 17), ("b", 1), ("a", 22), ("b", 14)]
+    eng.begin("a")
+    eng.begin("b")
+    k = 0
+    while k < len(plan):
+        # two requests in one step where the plan allows it
+        batch = [plan[k]]
+        if k + 1 < len(plan) and plan[k + 1][0] != plan[k][0]:
+            batch.append(plan[k + 1])
+        k += len(batch)
+        entries = [StepEntry(r, seqs[r][fed[r]:fed[r] + n], list(range(n))) for r, n in batch]
+        logits = eng.step(entries).cpu()
+        row = 0
+        for r, n in batch:
+            diff = float((logits[row:row + n] - want[r][fed[r]:fed[r] + n]).abs().max())
+            assert diff <= tol, f"{r} tokens {fed[r]}..{fed[r] + n}: {diff:.3e} > {tol:.3e}"
+            row += n
+            fed[r] += n
+    assert fed == {r: len(s) for r, s in seqs.items()}
+    # the window group gave pages back while the requests were still running
+    win = eng.cache.groups[1]
+    held = sum(1 for rc in eng.cache.live.values() for p in rc.pages[1] if p >= 0)
+    assert held < sum(-(-len(s) // 4) for s in seqs.values())
+    eng.cache.check()
+    eng.end("a")
+    eng.end("b")
+    assert all(g.pool.free_pages == g.pool.num_pages for g in eng.cache.groups)
