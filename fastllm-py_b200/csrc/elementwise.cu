@@ -209,3 +209,78 @@ FL_API int fl_swiglu(const void* gu, int dtype, long gu_ld, void* out, long out_
                                                                       out_ld, inter)));
     return fl_launch_status();
 }
+
+// ------------------------------------------- consumers of split-K partial sums
+// A product whose K was split over CTAs leaves `splits` float slabs
+// partial[z][row][col] (slab stride `split_stride`, row pitch `ld`).  Instead of
+// a kernel that only adds the slabs, the kernel that consumes the product adds
+// them as it reads: in the order z = 0, 1, ..., so the sum is the same as the
+// separate reduction's.
+
+__device__ __forceinline__ float sum_splits(const float* __restrict__ p, long idx, int splits,
+                                            long split_stride) {
+    float acc = 0.0f;
+    for (int z = 0; z < splits; ++z) acc += p[idx + (long)z * split_stride];
+    return acc;
+}
+
+// resid[r] += sum_z partial[z][r]; out[r] = rmsnorm(resid[r]) * w
+template <typename TW, typename TO>
+__global__ void add_rmsnorm_partial_kernel(float* __restrict__ resid, long resid_ld,
+                                           const float* __restrict__ partial, int splits,
+                                           long split_stride, long ld, const TW* __restrict__ w,
+                                           TO* __restrict__ out, long out_ld, int dim, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    float* xr = resid + (long)r * resid_ld;
+    const float* pr = partial + (long)r * ld;
+    TO* o = out + (long)r * out_ld;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        // the sum is rounded to the activation type first, as the separate reduction stores it
+        const float v = xr[i] + to_f32<TO>(from_f32<TO>(sum_splits(pr, i, splits, split_stride)));
+        xr[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+        o[i] = from_f32<TO>(xr[i] * inv * to_f32<TW>(w[i]));
+}
+
+FL_API int fl_add_rmsnorm_partial(float* resid, long resid_ld, const float* partial, int splits,
+                                  long split_stride, long ld, const void* w, int w_dtype, void* out,
+                                  int out_dtype, long out_ld, int n_rows, int dim, float eps,
+                                  cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = norm_threads(dim, false);
+    FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,
+        (add_rmsnorm_partial_kernel<TW, TO><<<n_rows, threads, 0, stream>>>(
+            resid, resid_ld, partial, splits, split_stride, ld, (const TW*)w, (TO*)out, out_ld, dim,
+            eps))));
+    return fl_launch_status();
+}
+
+// out[r, i] = silu(sum_z partial[z][r][i]) * sum_z partial[z][r][inter + i]
+template <typename TO>
+__global__ void swiglu_partial_kernel(const float* __restrict__ partial, int splits, long split_stride,
+                                      long ld, TO* __restrict__ out, long out_ld, int inter) {
+    const float* g = partial + (long)blockIdx.y * ld;
+    TO* o = out + (long)blockIdx.y * out_ld;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < inter) {
+        // what the separate reduction would have stored, so that both routes agree
+        const float gf = to_f32<TO>(from_f32<TO>(sum_splits(g, i, splits, split_stride)));
+        const float uf = to_f32<TO>(from_f32<TO>(sum_splits(g, inter + i, splits, split_stride)));
+        o[i] = from_f32<TO>(gf / (1.0f + expf(-gf)) * uf);
+    }
+}
+
+FL_API int fl_swiglu_partial(const float* partial, int splits, long split_stride, long ld, void* out,
+                             int out_dtype, long out_ld, int n_rows, int inter, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    dim3 grid((inter + 255) / 256, n_rows);
+    FL_DISPATCH(out_dtype, TO, (swiglu_partial_kernel<TO><<<grid, 256, 0, stream>>>(
+        partial, splits, split_stride, ld, (TO*)out, out_ld, inter)));
+    return fl_launch_status();
+}

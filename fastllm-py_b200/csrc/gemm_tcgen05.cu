@@ -402,9 +402,9 @@ FL_API void fl_gemm_tc_plan(int M, int N, int K, int num_sms, int* bn_out, int* 
 // the bases 16-byte aligned (what a TMA descriptor wants).  `workspace` holds
 // splits * M * round_up(N, 4) floats when the plan splits K (bn and splits come
 // from fl_gemm_tc_plan, or 0 to plan here).
-FL_API int fl_gemm_tc(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc,
-                      int M, int N, int K, int bn, int splits, float* workspace, long workspace_floats,
-                      int num_sms, int* status, cudaStream_t stream) {
+static int gemm_tc_impl(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc,
+                        int M, int N, int K, int bn, int splits, float* workspace, long workspace_floats,
+                        int num_sms, int* status, cudaStream_t stream, int skip_reduce) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return (int)cudaErrorInvalidValue;
     if (bn == 0) fl_gemm_tc_plan(M, N, K, num_sms, &bn, &splits);
@@ -427,13 +427,30 @@ FL_API int fl_gemm_tc(const void* A, long lda, const void* W, long ldw, void* C,
         rc = dispatch_tc<float>(bn, map_w, map_a, C, ldc, workspace, ld_partial, M, N, K, splits, kb_per_split, status, stream);
     else
         return (int)cudaErrorInvalidValue;
-    if (rc || splits == 1) return rc;
+    if (rc || splits == 1 || skip_reduce) return rc;
     dim3 grid((N + 255) / 256, M);
     if (c_dtype == FL_BF16)
         splitk_reduce_kernel<bf16><<<grid, 256, 0, stream>>>(workspace, ld_partial, splits, (bf16*)C, ldc, M, N);
     else
         splitk_reduce_kernel<float><<<grid, 256, 0, stream>>>(workspace, ld_partial, splits, (float*)C, ldc, M, N);
     return fl_launch_status();
+}
+
+FL_API int fl_gemm_tc(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc,
+                      int M, int N, int K, int bn, int splits, float* workspace, long workspace_floats,
+                      int num_sms, int* status, cudaStream_t stream) {
+    return gemm_tc_impl(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, bn, splits, workspace, workspace_floats,
+                        num_sms, status, stream, 0);
+}
+
+// The same, but with splits > 1 the partial sums stay in the workspace
+// ([splits][M][round_up(N, 4)] floats) for a consumer kernel that adds them as
+// it reads; C is not written then.
+FL_API int fl_gemm_tc_partial(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype,
+                              long ldc, int M, int N, int K, int bn, int splits, float* workspace,
+                              long workspace_floats, int num_sms, int* status, cudaStream_t stream) {
+    return gemm_tc_impl(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, bn, splits, workspace, workspace_floats,
+                        num_sms, status, stream, 1);
 }
 
 // ------------------------------------------- entry point that allocates nothing

@@ -81,3 +81,74 @@ FL_API int fl_rope_kv_write(void* qkv, int dtype, long ld, int n_tokens, int n_h
         (T*)k_cache, (T*)v_cache, page_stride, page_size)));
     return fl_launch_status();
 }
+
+// The same, reading q|k|v as split-K partial sums (float slabs partial[z][t][col],
+// added in the order z = 0, 1, ...) and writing the rotated queries to a buffer
+// of the activation type: the product's reduction, the rotation and the cache
+// write in one pass.  Each sum is first rounded to the activation type, as the
+// separate reduction would have stored it, so both routes give the same bits.
+template <typename T>
+__global__ void rope_kv_partial_kernel(const float* __restrict__ partial, int splits, long split_stride,
+                                       long ld, T* __restrict__ q_out, long q_ld, int n_heads,
+                                       int n_kv_heads, int head_dim, int rot_dim,
+                                       const float* __restrict__ cos_table,
+                                       const float* __restrict__ sin_table,
+                                       const int* __restrict__ positions, const int* __restrict__ slots,
+                                       T* __restrict__ k_cache, T* __restrict__ v_cache, long page_stride,
+                                       int page_size) {
+    const int t = blockIdx.x, head = blockIdx.y;
+    const int half = rot_dim >> 1;
+    const float* x = partial + (long)t * ld + (long)head * head_dim;
+    auto in = [&](int j) {
+        float acc = 0.0f;
+        for (int z = 0; z < splits; ++z) acc += x[j + (long)z * split_stride];
+        return to_f32<T>(from_f32<T>(acc));
+    };
+    T* dst;
+    bool rotate = true;
+    if (head < n_heads) {
+        dst = q_out + (long)t * q_ld + (long)head * head_dim;
+    } else {
+        const int slot = slots[t];
+        if (slot < 0) return;
+        const long page = slot / page_size;
+        const int off = slot - (int)page * page_size;
+        const bool is_key = head < n_heads + n_kv_heads;
+        const int kvh = is_key ? head - n_heads : head - n_heads - n_kv_heads;
+        dst = (is_key ? k_cache : v_cache) + page * page_stride + (long)kvh * page_size * head_dim +
+              (long)off * head_dim;
+        rotate = is_key;
+    }
+    if (rotate) {
+        const long pos = positions[t];
+        const float* cs = cos_table + pos * half;
+        const float* sn = sin_table + pos * half;
+        for (int j = threadIdx.x; j < half; j += blockDim.x) {
+            const float x1 = in(j), x2 = in(j + half);
+            const float c = cs[j], s = sn[j];
+            dst[j] = from_f32<T>(x1 * c - x2 * s);
+            dst[j + half] = from_f32<T>(x2 * c + x1 * s);
+        }
+        for (int j = rot_dim + threadIdx.x; j < head_dim; j += blockDim.x) dst[j] = from_f32<T>(in(j));
+    } else {
+        for (int j = threadIdx.x; j < head_dim; j += blockDim.x) dst[j] = from_f32<T>(in(j));
+    }
+}
+
+FL_API int fl_rope_kv_write_partial(const float* partial, int splits, long split_stride, long ld,
+                                    void* q_out, int dtype, long q_ld, int n_tokens, int n_heads,
+                                    int n_kv_heads, int head_dim, int rot_dim, const float* cos_table,
+                                    const float* sin_table, const int* positions, const int* slots,
+                                    void* k_cache, void* v_cache, long page_stride, int page_size,
+                                    int has_kv, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (rot_dim < 0 || rot_dim > head_dim || (rot_dim & 1)) return (int)cudaErrorInvalidValue;
+    const int heads = n_heads + (has_kv ? 2 * n_kv_heads : 0);
+    if (heads > 65535) return (int)cudaErrorInvalidValue;
+    dim3 grid(n_tokens, heads);
+    const int threads = head_dim >= 128 ? 64 : 32;
+    FL_DISPATCH(dtype, T, (rope_kv_partial_kernel<T><<<grid, threads, 0, stream>>>(
+        partial, splits, split_stride, ld, (T*)q_out, q_ld, n_heads, n_kv_heads, head_dim, rot_dim,
+        cos_table, sin_table, positions, slots, (T*)k_cache, (T*)v_cache, page_stride, page_size)));
+    return fl_launch_status();
+}

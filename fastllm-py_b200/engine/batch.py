@@ -108,6 +108,7 @@ class StepContext:
     slots_host: list = field(default_factory=list)
     max_q_len: int = 0
     max_seq_len: int = 0
+    rows_identity: bool = False    # the wanted rows are all rows, in order
     n_decode_tokens: int = 0       # tokens of requests that bring exactly one token
     decode_splits: int = 1         # key splits the decode attention kernel is launched with
     _views: dict = field(default_factory=dict)

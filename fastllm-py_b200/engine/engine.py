@@ -160,7 +160,8 @@ class Engine:
             status=self.status, workspace=self.workspace, no_rotation=self.no_rotation,
             q_lens=q_lens, ctx_lens=ctx_lens, slots_host=slots_host,
             max_q_len=max(q_lens), max_seq_len=max(c + q for c, q in zip(ctx_lens, q_lens)),
-            n_decode_tokens=n_dec)
+            n_decode_tokens=n_dec,
+            rows_identity=(m == n_tokens and bool((rows[:m] == np.arange(m)).all())))
         step.decode_splits = self._decode_splits(step)
         step._views = build_views(cache, buf, n_tokens, n)
         return step

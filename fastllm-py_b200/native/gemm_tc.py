@@ -20,6 +20,8 @@ def _lib():
                                    c_int, c_int, c_int, c_int, c_void_p, c_long, c_int, c_void_p,
                                    c_void_p]
         lib.fl_gemm_tc.restype = c_int
+        lib.fl_gemm_tc_partial.argtypes = lib.fl_gemm_tc.argtypes
+        lib.fl_gemm_tc_partial.restype = c_int
         lib.fl_gemm_tc_plan.argtypes = [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int),
                                         ctypes.POINTER(c_int)]
         lib.fl_gemm_tc_plan.restype = None
@@ -69,9 +71,30 @@ def _workspace(device, floats: int) -> torch.Tensor:
     return ws
 
 
-def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int = 0, splits: int = 0) -> None:
+class Partial:
+    """A product left as split-K partial sums: `splits` float slabs [rows, ld] in
+    the shared workspace, to be added (in slab order) by the kernel that reads
+    them.  The workspace is reused by the next split-K product, so a Partial must
+    be consumed before that; `check()` raises if it was not."""
+
+    def __init__(self, data, splits, rows, cols, ld, device):
+        self.data, self.splits, self.rows, self.cols, self.ld = data, splits, rows, cols, ld
+        self.split_stride = rows * ld
+        self.device = device
+        self.generation = _state.get(("gen", str(device)), 0)
+
+    def check(self):
+        if self.generation != _state.get(("gen", str(self.device)), 0):
+            raise RuntimeError("split-K partial sums were overwritten by a later product before use")
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int = 0, splits: int = 0,
+         defer: bool = False):
     """out[M, N] = a[M, K] @ w[N, K]^T; a and w bfloat16 (row pitch a multiple of 8
-    elements, base 16-byte aligned), out bfloat16 or float32."""
+    elements, base 16-byte aligned), out bfloat16 or float32.
+
+    With `defer`, a product whose K is split returns a Partial instead of
+    writing `out`: its consumer adds the slabs while it reads them."""
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise ops.KernelError("tensor-core gemm takes bfloat16 operands")
     m, k = a.shape
@@ -92,10 +115,18 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int = 0, split
         ws_floats = splits * m * (-(-n // 4) * 4)
         ws = _workspace(a.device, ws_floats)
         ws_floats = ws.numel()
-    rc = _lib().fl_gemm_tc(ops._ptr(a), lda, ops._ptr(w), ldw, ops._ptr(out), ops.dtype_code(out), ldc,
-                           m, n, k, bn, splits, ops._ptr(ws), ws_floats, sms,
-                           ops._ptr(status_word(a.device)), ops._stream())
-    ops._check(rc, "gemm_tcgen05", 2 if splits > 1 else 1)
+    deferred = defer and splits > 1
+    fn = _lib().fl_gemm_tc_partial if deferred else _lib().fl_gemm_tc
+    if splits > 1:
+        gen_key = ("gen", str(a.device))
+        _state[gen_key] = _state.get(gen_key, 0) + 1          # earlier Partials are now stale
+    rc = fn(ops._ptr(a), lda, ops._ptr(w), ldw, ops._ptr(out), ops.dtype_code(out), ldc,
+            m, n, k, bn, splits, ops._ptr(ws), ws_floats, sms,
+            ops._ptr(status_word(a.device)), ops._stream())
+    ops._check(rc, "gemm_tcgen05", 2 if (splits > 1 and not deferred) else 1)
+    if deferred:
+        return Partial(ws, splits, m, n, -(-n // 4) * 4, a.device)
+    return None
 
 
 class TensorCoreLinear:
@@ -111,5 +142,5 @@ class TensorCoreLinear:
             weight = padded[:, :k]
         self.weight = weight
 
-    def forward(self, a: torch.Tensor, out: torch.Tensor) -> None:
-        gemm(a, self.weight, out)
+    def forward(self, a: torch.Tensor, out: torch.Tensor, defer: bool = False):
+        return gemm(a, self.weight, out, defer=defer)

@@ -119,6 +119,51 @@ def add_rmsnorm(resid, delta, weight, out, eps, rows=None):
               float(eps), _ptr(rows), _stream()), "add_rmsnorm")
 
 
+def add_rmsnorm_partial(resid, partial, weight, out, eps):
+    """resid += (split-K partial sums, added in slab order); out = rmsnorm(resid) * weight."""
+    _require_cuda(resid, weight, out)
+    partial.check()
+    fn = _fn("elementwise", "fl_add_rmsnorm_partial", [c_void_p, c_long, c_void_p, c_int, c_long, c_long,
+                                                       c_void_p, c_int, c_void_p, c_int, c_long, c_int,
+                                                       c_int, c_float, c_void_p])
+    _check(fn(_ptr(resid), _ld(resid), _ptr(partial.data), partial.splits, partial.split_stride,
+              partial.ld, _ptr(weight), dtype_code(weight), _ptr(out), dtype_code(out), _ld(out),
+              out.shape[0], resid.shape[1], float(eps), _stream()), "add_rmsnorm_partial")
+
+
+def swiglu_partial(partial, out):
+    """swiglu over gate|up columns given as split-K partial sums."""
+    _require_cuda(out)
+    partial.check()
+    fn = _fn("elementwise", "fl_swiglu_partial", [c_void_p, c_int, c_long, c_long, c_void_p, c_int, c_long,
+                                                  c_int, c_int, c_void_p])
+    _check(fn(_ptr(partial.data), partial.splits, partial.split_stride, partial.ld, _ptr(out),
+              dtype_code(out), _ld(out), out.shape[0], out.shape[1], _stream()), "swiglu_partial")
+
+
+def rope_kv_write_partial(partial, q_out, n_heads, n_kv_heads, head_dim, rot_dim, cos, sin, positions,
+                          slots, cache, page_size):
+    """rope_kv_write reading q|k|v as split-K partial sums; rotated queries go to q_out."""
+    _require_cuda(q_out, cos, sin, positions, slots, cache)
+    partial.check()
+    fn = _fn("rope_kv", "fl_rope_kv_write_partial",
+             [c_void_p, c_int, c_long, c_long, c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int,
+              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p])
+    if cache is not None:
+        if cache.dtype != q_out.dtype:
+            raise KernelError("rope_kv_write: cache and activations must have one dtype")
+        k_ptr = c_void_p(cache.data_ptr())
+        v_ptr = c_void_p(cache.data_ptr() + cache.stride(1) * cache.element_size())
+        page_stride = cache.stride(0)
+    else:
+        k_ptr = v_ptr = None
+        page_stride = 0
+    _check(fn(_ptr(partial.data), partial.splits, partial.split_stride, partial.ld, _ptr(q_out),
+              dtype_code(q_out), _ld(q_out), q_out.shape[0], n_heads, n_kv_heads, head_dim, rot_dim,
+              _ptr(cos), _ptr(sin), _ptr(positions), _ptr(slots), k_ptr, v_ptr, page_stride, page_size,
+              0 if cache is None else 1, _stream()), "rope_kv_write_partial")
+
+
 def residual_add(resid, delta):
     _require_cuda(resid, delta)
     if resid.dtype != torch.float32:

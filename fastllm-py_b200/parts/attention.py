@@ -94,18 +94,23 @@ class Attention(Part):
         if cache.writes == self.shares_cache:
             raise RuntimeError("attention: the run's cache and the layer's shares_cache disagree")
         qkv = step.workspace.rows("qkv", n, cols, dt)
-        self.qkv.forward(h, qkv)
+        partial = self.qkv.forward(h, qkv, defer=True)
         if self.position is not None:
             cos, sin = self.position.tables()
             rot = self.position.rot_dim
         else:
             cos, sin, rot = step.no_rotation, step.no_rotation, 0
-        ops.rope_kv_write(qkv, self.heads, self.kv_heads, self.head_dim, rot, cos, sin,
-                          step.positions, cache.slots, cache.tensor if cache.writes else None,
-                          cache.page_size)
+        kv_cache = cache.tensor if cache.writes else None
+        if partial is None:
+            ops.rope_kv_write(qkv, self.heads, self.kv_heads, self.head_dim, rot, cos, sin,
+                              step.positions, cache.slots, kv_cache, cache.page_size)
+        else:
+            ops.rope_kv_write_partial(partial, qkv[:, :q_cols], self.heads, self.kv_heads, self.head_dim,
+                                      rot, cos, sin, step.positions, cache.slots, kv_cache,
+                                      cache.page_size)
         ctx = step.workspace.rows("attn_ctx", n, q_cols, dt)
         self.attend(qkv[:, :q_cols], ctx, step, cache)
-        self.o.forward(ctx, out)
+        return self.o.forward(ctx, out, defer=True)
 
     def attend(self, q, ctx, step, cache):
         from ..native import attention as fast

@@ -31,9 +31,11 @@ class PreNormBlock(Part):
         dt = self.ctx.dtype
         h = step.workspace.rows("normed", n, self.hidden, dt)
         delta = step.workspace.rows("delta", n, self.hidden, dt)
+        # a mixer or feed-forward returns None when it wrote `delta`, or the
+        # split-K partial sums of its last product, which the next norm adds up
         self.norm_mixer.apply(stream, h)
-        self.mixer.forward(h, delta, step, cache)
-        stream.pending = delta
+        left = self.mixer.forward(h, delta, step, cache)
+        stream.pending = delta if left is None else left
         self.norm_ff.apply(stream, h)
-        self.feed_forward.forward(h, delta, step)
-        stream.pending = delta
+        left = self.feed_forward.forward(h, delta, step)
+        stream.pending = delta if left is None else left

@@ -118,6 +118,11 @@ class Decoder:
         logits = ws.rows("logits", m, self.vocab, torch.float32, initial=64)
         if m > 0:
             picked = ws.rows("picked", m, self.hidden, self.ctx.dtype, initial=64)
-            self.final_norm.apply(stream, picked, rows=step.logit_rows)
+            rows = None if step.rows_identity else step.logit_rows
+            if rows is not None and stream.pending is not None and \
+                    not isinstance(stream.pending, torch.Tensor):
+                # partial sums cannot be gathered by row: fold them into the stream first
+                self.final_norm.apply(stream, ws.rows("normed", n, self.hidden, self.ctx.dtype))
+            self.final_norm.apply(stream, picked, rows=rows)
             self.head.forward(picked, logits)
         return logits

@@ -34,12 +34,15 @@ class Linear:
         self._tc = None
         return self
 
-    def forward(self, a: torch.Tensor, out: torch.Tensor) -> None:
+    def forward(self, a: torch.Tensor, out: torch.Tensor, defer: bool = False):
+        """Writes `out` and returns None; or, with `defer`, may leave the product
+        as split-K partial sums and return them (a `gemm_tc.Partial`) for a
+        consumer that adds them as it reads: `out` is then not written."""
         if a.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16:
             from .. import native
             if native.tensor_core_gemm_enabled():
                 if self._tc is None:
                     self._tc = native.gemm_tc.TensorCoreLinear(self.weight)
-                self._tc.forward(a, out)
-                return
+                return self._tc.forward(a, out, defer)
         ops.gemm_simt(a, self.weight, out)
+        return None

@@ -37,7 +37,10 @@ class SwiGLU(Part):
         n = h.shape[0]
         dt = self.ctx.dtype
         gu = step.workspace.rows("gate_up", n, 2 * self.inter, dt)
-        self.gate_up.forward(h, gu)
+        partial = self.gate_up.forward(h, gu, defer=True)
         act = step.workspace.rows("ffn_act", n, self.inter, dt)
-        ops.swiglu(gu, act)
-        self.down.forward(act, out)
+        if partial is None:
+            ops.swiglu(gu, act)
+        else:
+            ops.swiglu_partial(partial, act)
+        return self.down.forward(act, out, defer=True)

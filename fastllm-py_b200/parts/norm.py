@@ -3,6 +3,8 @@ multiplies (no "+1").  fastllm_py/kernels/ops.py:19-27; the fused
 residual-add form is fastllm_py/graph_decode.py:300-324."""
 from __future__ import annotations
 
+import torch
+
 from ..native import ops
 from .base import Part
 from .registry import register_part
@@ -29,6 +31,12 @@ class RMSNorm(Part):
         """Norm the residual stream into `out`, adding the pending sum first.
         With `rows` (int32 indices) only those rows are normed, into out[0..m)."""
         if stream.pending is not None:
+            if not isinstance(stream.pending, torch.Tensor):         # split-K partial sums
+                if rows is not None:
+                    raise RuntimeError("a gathered norm cannot take partial sums")
+                ops.add_rmsnorm_partial(stream.x, stream.pending, self.weight, out, self.eps)
+                stream.pending = None
+                return
             ops.add_rmsnorm(stream.x, stream.pending, self.weight, out, self.eps, rows)
             if rows is None:
                 stream.pending = None
