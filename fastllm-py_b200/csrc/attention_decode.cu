@@ -25,10 +25,16 @@
 #ifndef HEAD_DIM
 #define HEAD_DIM 128
 #endif
+#ifndef ATD_SPLIT
 #define ATD_SPLIT 256                      // keys per split
+#endif
+#ifndef ATD_WARPS
 #define ATD_WARPS 4
+#endif
 #define ATD_KEYS_PER_WARP (ATD_SPLIT / ATD_WARPS)
+#ifndef ATD_UNROLL
 #define ATD_UNROLL 4
+#endif
 
 static_assert(HEAD_DIM % 8 == 0 && HEAD_DIM >= 8 && HEAD_DIM <= 256, "HEAD_DIM: multiple of 8, at most 256");
 
