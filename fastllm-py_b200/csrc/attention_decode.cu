@@ -57,6 +57,21 @@ __device__ __forceinline__ void unpack8(const Bf16x8& p, float* f) {
     }
 }
 
+// A 16-byte streaming load: the cache is read once per step, so it should not
+// displace anything in L1, and neighbouring sectors are worth fetching into L2.
+__device__ __forceinline__ Bf16x8 load_stream(const bf16* p) {
+    Bf16x8 r;
+    uint32_t* w = reinterpret_cast<uint32_t*>(&r);
+#ifdef ATD_PLAIN_LOADS
+    r = *reinterpret_cast<const Bf16x8*>(p);
+#else
+    asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                 : "l"(p));
+#endif
+    return r;
+}
+
 // exp2f(a - b) with the conventions of a running softmax: an empty state (-inf) weighs nothing.
 __device__ __forceinline__ float weight_of(float a, float b) {
     return (a == -CUDART_INF_F) ? 0.0f : exp2f(a - b);
@@ -71,6 +86,8 @@ __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_kernel(
     int page_shift, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req,
     const int* __restrict__ positions, const int* __restrict__ tok_list, int n_heads, int n_kv_heads,
     int window, float scale_log2e, int n_splits, float* __restrict__ partial) {
+    pdl_wait();
+    pdl_trigger();
     const int li = blockIdx.x;                              // index into the list of decode tokens
     const int t = tok_list ? tok_list[li] : li;
     const int h = blockIdx.y, split = blockIdx.z;
@@ -117,8 +134,8 @@ __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_kernel(
                 const int pg = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
                 const int off = page_shift >= 0 ? (j & (page_size - 1)) : (j - pg * page_size);
                 const long a = (long)bt[pg] * page_stride + head_off + (long)off * HEAD_DIM;
-                kv[u] = *reinterpret_cast<const Bf16x8*>(k_cache + a);
-                vv[u] = *reinterpret_cast<const Bf16x8*>(v_cache + a);
+                kv[u] = load_stream(k_cache + a);
+                vv[u] = load_stream(v_cache + a);
             } else {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -218,6 +235,8 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ partial,
                                               long out_ld, const int* __restrict__ positions,
                                               const int* __restrict__ tok_list, int n_heads, int window,
                                               int n_splits) {
+    pdl_wait();
+    pdl_trigger();
     const int li = blockIdx.x, h = blockIdx.y;
     const int t = tok_list ? tok_list[li] : li;
     const int pos = positions[t];
@@ -264,14 +283,12 @@ FL_API int fl_attention_decode(const void* q, long q_ld, void* out, long out_ld,
         while ((1 << page_shift) < page_size) ++page_shift;
     }
     dim3 grid(n_list, n_heads, n_splits);
-    attention_decode_kernel<<<grid, ATD_WARPS * 32, 0, stream>>>(
-        (const bf16*)q, q_ld, (bf16*)out, out_ld, (const bf16*)k_cache, (const bf16*)v_cache, page_stride,
-        page_size, page_shift, block_table, bt_stride, tok_req, positions, tok_list, n_heads, n_kv_heads,
-        window, scale * 1.4426950408889634f, n_splits, partial);
-    int rc = fl_launch_status();
+    int rc = fl_launch(attention_decode_kernel, grid, dim3(ATD_WARPS * 32), 0, stream, (const bf16*)q, q_ld,
+                       (bf16*)out, out_ld, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, page_size,
+                       page_shift, block_table, bt_stride, tok_req, positions, tok_list, n_heads, n_kv_heads,
+                       window, scale * 1.4426950408889634f, n_splits, partial);
     if (rc || n_splits == 1) return rc;
     dim3 mgrid(n_list, n_heads);
-    attention_decode_merge_kernel<<<mgrid, 128, 0, stream>>>(partial, (bf16*)out, out_ld, positions, tok_list,
-                                                           n_heads, window, n_splits);
-    return fl_launch_status();
+    return fl_launch(attention_decode_merge_kernel, mgrid, dim3(128), 0, stream, (const float*)partial,
+                     (bf16*)out, out_ld, positions, tok_list, n_heads, window, n_splits);
 }

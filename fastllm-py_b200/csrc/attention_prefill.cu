@@ -72,6 +72,8 @@ __global__ void __launch_bounds__(ATP_THREADS) attention_prefill_kernel(
     int page_shift, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ req_start,
     const int* __restrict__ req_ctx, const int* __restrict__ req_qlen, int n_requests, int include_single,
     int n_heads, int n_kv_heads, int window, float scale_log2e) {
+    pdl_wait();
+    pdl_trigger();
     extern __shared__ __align__(16) unsigned char atp_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(atp_raw);                       // [64][DP]
     bf16* Ks = Qs + ATP_BM * ATP_DP;                                   // [2][64][DP]
@@ -280,9 +282,8 @@ FL_API int fl_attention_prefill(const void* q, long q_ld, void* out, long out_ld
     }
     const int max_tiles = n_tokens / ATP_BM + n_requests;   // sum of ceil(q_len / 64) is at most this
     dim3 grid(max_tiles, n_heads);
-    attention_prefill_kernel<<<grid, ATP_THREADS, smem, stream>>>(
-        (const bf16*)q, q_ld, (bf16*)out, out_ld, (const bf16*)k_cache, (const bf16*)v_cache, page_stride,
-        page_size, page_shift, block_table, bt_stride, req_start, req_ctx, req_qlen, n_requests,
-        include_single, n_heads, n_kv_heads, window, scale * 1.4426950408889634f);
-    return fl_launch_status();
+    return fl_launch(attention_prefill_kernel, grid, dim3(ATP_THREADS), smem, stream, (const bf16*)q, q_ld,
+                     (bf16*)out, out_ld, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, page_size,
+                     page_shift, block_table, bt_stride, req_start, req_ctx, req_qlen, n_requests,
+                     include_single, n_heads, n_kv_heads, window, scale * 1.4426950408889634f);
 }

@@ -26,6 +26,8 @@ __global__ void __launch_bounds__(ATT_TILE) paged_attention_simt_kernel(
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req,
     const int* __restrict__ positions, int n_heads, int n_kv_heads, int head_dim, int window,
     float scale) {
+    pdl_wait();
+    pdl_trigger();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     long* off_s = reinterpret_cast<long*>(smem_raw);                  // [ATT_TILE] element offset of each key row
     float* p_s = reinterpret_cast<float*>(off_s + ATT_TILE);          // [ATT_TILE] softmax numerators of the tile
@@ -100,9 +102,9 @@ FL_API int fl_paged_attention_simt(const void* q, int dtype, long q_ld, void* ou
         return (int)cudaErrorInvalidValue;
     const size_t smem = ATT_TILE * (sizeof(long) + sizeof(float)) + (size_t)head_dim * sizeof(float);
     dim3 grid(n_tokens, n_heads);
-    FL_DISPATCH(dtype, T, (paged_attention_simt_kernel<T><<<grid, ATT_TILE, smem, stream>>>(
-        (const T*)q, q_ld, (T*)out, out_ld, (const T*)k_cache, (const T*)v_cache, page_stride,
-        page_size, block_table, bt_stride, tok_req, positions, n_heads, n_kv_heads, head_dim, window,
-        scale)));
-    return fl_launch_status();
+    FL_DISPATCH(dtype, T, return fl_launch(paged_attention_simt_kernel<T>, grid, dim3(ATT_TILE), smem, stream,
+                                           (const T*)q, q_ld, (T*)out, out_ld, (const T*)k_cache,
+                                           (const T*)v_cache, page_stride, page_size, block_table, bt_stride,
+                                           tok_req, positions, n_heads, n_kv_heads, head_dim, window, scale));
+    return 0;
 }

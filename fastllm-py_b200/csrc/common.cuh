@@ -74,3 +74,42 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 static inline int fl_launch_status() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch
+// Kernels of a step run back to back on one stream, most of them for a few
+// microseconds.  Launched with the programmatic-serialization attribute, a
+// kernel may be scheduled while its predecessor is still running; it executes
+// `pdl_wait()` before it touches anything the predecessor wrote (the wait
+// returns once the predecessor has completed and its writes are visible), and
+// `pdl_trigger()` tells the scheduler that the successor may be brought in.
+// What a kernel does before its wait (barrier set-up, fetching weights that no
+// kernel writes) overlaps the predecessor's tail.  FASTLLM_B200_PDL=0 turns the
+// attribute off; the two instructions are then no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <stdlib.h>
+static inline bool fl_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* v = getenv("FASTLLM_B200_PDL");
+        on = (v != nullptr && v[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int fl_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                            cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = fl_pdl_enabled() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

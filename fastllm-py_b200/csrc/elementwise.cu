@@ -36,6 +36,8 @@ template <typename TT>
 __global__ void embed_kernel(const TT* __restrict__ table, long table_ld, const int* __restrict__ ids,
                              float* __restrict__ out, long out_ld, int hidden, int vocab,
                              int* __restrict__ status, int vec_ok) {
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (long)t * out_ld;
@@ -60,11 +62,11 @@ FL_API int fl_embed(const void* table, int table_dtype, long table_ld, const int
                     long out_ld, int n_tokens, int hidden, int vocab, int* status,
                     cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    const int vec = vec4_ok(hidden, table, table_ld, table_dtype == FL_F32 ? 4 : 2) && vec4_ok(hidden, out, out_ld, 4);
     FL_DISPATCH(table_dtype, TT,
-                embed_kernel<TT><<<n_tokens, 256, 0, stream>>>(
-                    (const TT*)table, table_ld, ids, out, out_ld, hidden, vocab, status,
-                    vec4_ok(hidden, table, table_ld, sizeof(TT)) && vec4_ok(hidden, out, out_ld, 4)));
-    return fl_launch_status();
+                return fl_launch(embed_kernel<TT>, dim3(n_tokens), dim3(256), 0, stream, (const TT*)table,
+                                 table_ld, ids, out, out_ld, hidden, vocab, status, vec));
+    return 0;
 }
 
 // -------------------------------------------------------------------- RMSNorm
@@ -76,6 +78,8 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, long x_ld, const TD* __restri
                                long delta_ld, const TW* __restrict__ w, TO* __restrict__ out,
                                long out_ld, int dim, float eps, const int* __restrict__ rows,
                                int write_back) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const long src = rows ? (long)rows[r] : (long)r;
@@ -143,11 +147,12 @@ FL_API int fl_rmsnorm(const void* x, int x_dtype, long x_ld, const void* w, int 
     const int threads = norm_threads(dim, vec);
 #define FL_NORM_LAUNCH(VEC)                                                                          \
     FL_DISPATCH(x_dtype, TX, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,                      \
-        (rmsnorm_kernel<TX, float, TW, TO, false, VEC><<<n_rows, threads, 0, stream>>>(               \
-            (TX*)x, x_ld, nullptr, 0, (const TW*)w, (TO*)out, out_ld, dim, eps, rows, 0)))))
+        return fl_launch(rmsnorm_kernel<TX, float, TW, TO, false, VEC>, dim3(n_rows), dim3(threads), 0,  \
+                         stream, (TX*)x, x_ld, (const float*)nullptr, 0L, (const TW*)w, (TO*)out,       \
+                         out_ld, dim, eps, rows, 0))))
     if (vec) { FL_NORM_LAUNCH(true); } else { FL_NORM_LAUNCH(false); }
 #undef FL_NORM_LAUNCH
-    return fl_launch_status();
+    return 0;
 }
 
 FL_API int fl_add_rmsnorm(float* resid, long resid_ld, const void* delta, int delta_dtype,
@@ -161,18 +166,20 @@ FL_API int fl_add_rmsnorm(float* resid, long resid_ld, const void* delta, int de
     const int threads = norm_threads(dim, vec);
 #define FL_NORM_LAUNCH(VEC)                                                                          \
     FL_DISPATCH(delta_dtype, TD, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,                  \
-        (rmsnorm_kernel<float, TD, TW, TO, true, VEC><<<n_rows, threads, 0, stream>>>(                \
-            resid, resid_ld, (const TD*)delta, delta_ld, (const TW*)w, (TO*)out, out_ld, dim, eps,   \
-            rows, write_back)))))
+        return fl_launch(rmsnorm_kernel<float, TD, TW, TO, true, VEC>, dim3(n_rows), dim3(threads), 0,  \
+                         stream, resid, resid_ld, (const TD*)delta, delta_ld, (const TW*)w, (TO*)out,  \
+                         out_ld, dim, eps, rows, write_back))))
     if (vec) { FL_NORM_LAUNCH(true); } else { FL_NORM_LAUNCH(false); }
 #undef FL_NORM_LAUNCH
-    return fl_launch_status();
+    return 0;
 }
 
 // resid += delta without a norm (the last pending sum of a stream that ends unnormed).
 template <typename TD>
 __global__ void add_kernel(float* __restrict__ resid, long resid_ld, const TD* __restrict__ delta,
                            long delta_ld, int dim) {
+    pdl_wait();
+    pdl_trigger();
     float* xr = resid + (long)blockIdx.x * resid_ld;
     const TD* dr = delta + (long)blockIdx.x * delta_ld;
     for (int i = threadIdx.x; i < dim; i += blockDim.x) xr[i] += to_f32<TD>(dr[i]);
@@ -181,9 +188,9 @@ __global__ void add_kernel(float* __restrict__ resid, long resid_ld, const TD* _
 FL_API int fl_residual_add(float* resid, long resid_ld, const void* delta, int delta_dtype,
                            long delta_ld, int n_rows, int dim, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    FL_DISPATCH(delta_dtype, TD, (add_kernel<TD><<<n_rows, 256, 0, stream>>>(
-        resid, resid_ld, (const TD*)delta, delta_ld, dim)));
-    return fl_launch_status();
+    FL_DISPATCH(delta_dtype, TD, return fl_launch(add_kernel<TD>, dim3(n_rows), dim3(256), 0, stream, resid,
+                                                  resid_ld, (const TD*)delta, delta_ld, dim));
+    return 0;
 }
 
 // --------------------------------------------------------------------- SwiGLU
@@ -191,6 +198,8 @@ FL_API int fl_residual_add(float* resid, long resid_ld, const void* delta, int d
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, long gu_ld, T* __restrict__ out, long out_ld,
                               int inter) {
+    pdl_wait();
+    pdl_trigger();
     const T* g = gu + (long)blockIdx.y * gu_ld;
     T* o = out + (long)blockIdx.y * out_ld;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -205,9 +214,9 @@ FL_API int fl_swiglu(const void* gu, int dtype, long gu_ld, void* out, long out_
                      int inter, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     dim3 grid((inter + 255) / 256, n_rows);
-    FL_DISPATCH(dtype, T, (swiglu_kernel<T><<<grid, 256, 0, stream>>>((const T*)gu, gu_ld, (T*)out,
-                                                                      out_ld, inter)));
-    return fl_launch_status();
+    FL_DISPATCH(dtype, T, return fl_launch(swiglu_kernel<T>, grid, dim3(256), 0, stream, (const T*)gu, gu_ld,
+                                           (T*)out, out_ld, inter));
+    return 0;
 }
 
 // ------------------------------------------- consumers of split-K partial sums
@@ -230,6 +239,8 @@ __global__ void add_rmsnorm_partial_kernel(float* __restrict__ resid, long resid
                                            const float* __restrict__ partial, int splits,
                                            long split_stride, long ld, const TW* __restrict__ w,
                                            TO* __restrict__ out, long out_ld, int dim, float eps) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     float* xr = resid + (long)r * resid_ld;
@@ -255,16 +266,18 @@ FL_API int fl_add_rmsnorm_partial(float* resid, long resid_ld, const float* part
     if (n_rows <= 0) return 0;
     const int threads = norm_threads(dim, false);
     FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,
-        (add_rmsnorm_partial_kernel<TW, TO><<<n_rows, threads, 0, stream>>>(
-            resid, resid_ld, partial, splits, split_stride, ld, (const TW*)w, (TO*)out, out_ld, dim,
-            eps))));
-    return fl_launch_status();
+        return fl_launch(add_rmsnorm_partial_kernel<TW, TO>, dim3(n_rows), dim3(threads), 0, stream, resid,
+                         resid_ld, partial, splits, split_stride, ld, (const TW*)w, (TO*)out, out_ld, dim,
+                         eps)));
+    return 0;
 }
 
 // out[r, i] = silu(sum_z partial[z][r][i]) * sum_z partial[z][r][inter + i]
 template <typename TO>
 __global__ void swiglu_partial_kernel(const float* __restrict__ partial, int splits, long split_stride,
                                       long ld, TO* __restrict__ out, long out_ld, int inter) {
+    pdl_wait();
+    pdl_trigger();
     const float* g = partial + (long)blockIdx.y * ld;
     TO* o = out + (long)blockIdx.y * out_ld;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -280,7 +293,7 @@ FL_API int fl_swiglu_partial(const float* partial, int splits, long split_stride
                              int out_dtype, long out_ld, int n_rows, int inter, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     dim3 grid((inter + 255) / 256, n_rows);
-    FL_DISPATCH(out_dtype, TO, (swiglu_partial_kernel<TO><<<grid, 256, 0, stream>>>(
-        partial, splits, split_stride, ld, (TO*)out, out_ld, inter)));
-    return fl_launch_status();
+    FL_DISPATCH(out_dtype, TO, return fl_launch(swiglu_partial_kernel<TO>, grid, dim3(256), 0, stream, partial,
+                                                splits, split_stride, ld, (TO*)out, out_ld, inter));
+    return 0;
 }

@@ -18,6 +18,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TA* __restrict__ A
                                                         const TW* __restrict__ W, long ldw,
                                                         TC* __restrict__ C, long ldc, int M, int N,
                                                         int K) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ float As[GS_BK][GS_BM + 1];
     __shared__ float Ws[GS_BK][GS_BN + 1];
     const int tid = threadIdx.x;
@@ -66,7 +68,7 @@ FL_API int fl_gemm_simt(const void* A, int a_dtype, long lda, const void* W, int
     dim3 grid((N + GS_BN - 1) / GS_BN, (M + GS_BM - 1) / GS_BM);
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
     FL_DISPATCH(a_dtype, TA, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(c_dtype, TC,
-        (gemm_simt_kernel<TA, TW, TC><<<grid, 256, 0, stream>>>(
-            (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K)))));
-    return fl_launch_status();
+        return fl_launch(gemm_simt_kernel<TA, TW, TC>, grid, dim3(256), 0, stream, (const TA*)A, lda,
+                         (const TW*)W, ldw, (TC*)C, ldc, M, N, K))));
+    return 0;
 }

@@ -200,10 +200,25 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
     tc_fence_after();
     const uint32_t tmem_acc = *tmem_slot;
 
+    pdl_trigger();
     if (warp == 0) {
         if (lane == 0) {
-            // ---- producer: TMA loads of the weight tile and the token tile
-            for (int it = 0; it < n_iters && !*abort_flag; ++it) {
+            // ---- producer: TMA loads of the weight tile and the token tile.
+            // The weights are written by no kernel, so the first ring of weight
+            // tiles is fetched before waiting for the preceding kernel; the token
+            // tiles (its output) follow after the wait.
+            const int ahead = *abort_flag ? 0 : min(n_iters, STAGES);
+            for (int it = 0; it < ahead; ++it) {
+                unsigned char* a_dst = tiles + it * L::STAGE_BYTES;
+                mbar_expect_tx(&full_bar[it], L::STAGE_BYTES);
+                tma_load_2d(a_dst, &map_w, &full_bar[it], (kb_begin + it) * TC_BK, tile_n * TC_BM);
+            }
+            pdl_wait();
+            for (int it = 0; it < ahead; ++it) {
+                unsigned char* b_dst = tiles + it * L::STAGE_BYTES + L::A_BYTES;
+                tma_load_2d(b_dst, &map_a, &full_bar[it], (kb_begin + it) * TC_BK, tile_m * BN);
+            }
+            for (int it = ahead; it < n_iters && !*abort_flag; ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
                 if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
@@ -251,6 +266,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
         const int quarter = warp & 3;
         const int o = tile_n * TC_BM + quarter * 32 + lane;         // output feature of this thread
         bool ok = !*abort_flag;
+        pdl_wait();                                   // C may still be read by the preceding kernel
         if (ok && n_iters > 0) {
             ok = mbar_wait(acc_bar, 0, abort_flag);
             if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_ACC_WAIT); }
@@ -301,6 +317,8 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
 template <typename OutT>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, long ld_partial, int splits,
                                      OutT* __restrict__ C, long ldc, int M, int N) {
+    pdl_wait();
+    pdl_trigger();
     const int o = blockIdx.x * blockDim.x + threadIdx.x;
     const int t = blockIdx.y;
     if (o >= N) return;
@@ -356,9 +374,8 @@ static int launch_tc(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C
         configured = true;
     }
     dim3 grid((N + TC_BM - 1) / TC_BM, (M + BN - 1) / BN, splits);
-    kernel<<<grid, TC_THREADS, L::TOTAL, stream>>>(map_w, map_a, (OutT*)C, ldc, partial, ld_partial, M,
-                                                   N, K, kb_per_split, status);
-    return fl_launch_status();
+    return fl_launch(kernel, grid, dim3(TC_THREADS), (size_t)L::TOTAL, stream, map_w, map_a, (OutT*)C, ldc,
+                     partial, ld_partial, M, N, K, kb_per_split, status);
 }
 
 template <typename OutT>
@@ -368,8 +385,8 @@ static int dispatch_tc(int bn, const CUtensorMap& map_w, const CUtensorMap& map_
     switch (bn) {
         case 16: return launch_tc<16, 6, OutT>(map_w, map_a, C, ldc, partial, ld_partial, M, N, K, splits, kb_per_split, status, stream);
         case 32: return launch_tc<32, 5, OutT>(map_w, map_a, C, ldc, partial, ld_partial, M, N, K, splits, kb_per_split, status, stream);
-        case 64: return launch_tc<64, 6, OutT>(map_w, map_a, C, ldc, partial, ld_partial, M, N, K, splits, kb_per_split, status, stream);
-        case 128: return launch_tc<128, 6, OutT>(map_w, map_a, C, ldc, partial, ld_partial, M, N, K, splits, kb_per_split, status, stream);
+        case 64: return launch_tc<64, 4, OutT>(map_w, map_a, C, ldc, partial, ld_partial, M, N, K, splits, kb_per_split, status, stream);
+        case 128: return launch_tc<128, 3, OutT>(map_w, map_a, C, ldc, partial, ld_partial, M, N, K, splits, kb_per_split, status, stream);
         case 256: return launch_tc<256, 4, OutT>(map_w, map_a, C, ldc, partial, ld_partial, M, N, K, splits, kb_per_split, status, stream);
     }
     return (int)cudaErrorInvalidValue;
@@ -382,10 +399,13 @@ FL_API void fl_gemm_tc_plan(int M, int N, int K, int num_sms, int* bn_out, int* 
     while (bn < 256 && bn < M) bn *= 2;
     const int tiles = ((N + TC_BM - 1) / TC_BM) * ((M + bn - 1) / bn);
     const int num_kb = (K + TC_BK - 1) / TC_BK;
-    const int target = bn <= 32 ? 2 * num_sms : num_sms;
+    // CTAs that can be resident at once: two per SM for token tiles up to 128
+    // wide (their ring of stages is sized for that), one for 256.  Splitting K so
+    // that all CTAs fit in one wave keeps every SM streaming until the end.
+    const int target = bn <= 128 ? 2 * num_sms : num_sms;
     int splits = 1;
     if (tiles < target) {
-        splits = (target + tiles / 2) / tiles;
+        splits = target / tiles;
         const int most = num_kb / 4 > 0 ? num_kb / 4 : 1;       // at least 4 k-blocks per split
         if (splits > most) splits = most;
         if (splits > 16) splits = 16;
@@ -430,10 +450,10 @@ static int gemm_tc_impl(const void* A, long lda, const void* W, long ldw, void* 
     if (rc || splits == 1 || skip_reduce) return rc;
     dim3 grid((N + 255) / 256, M);
     if (c_dtype == FL_BF16)
-        splitk_reduce_kernel<bf16><<<grid, 256, 0, stream>>>(workspace, ld_partial, splits, (bf16*)C, ldc, M, N);
-    else
-        splitk_reduce_kernel<float><<<grid, 256, 0, stream>>>(workspace, ld_partial, splits, (float*)C, ldc, M, N);
-    return fl_launch_status();
+        return fl_launch(splitk_reduce_kernel<bf16>, grid, dim3(256), 0, stream, (const float*)workspace,
+                         ld_partial, splits, (bf16*)C, ldc, M, N);
+    return fl_launch(splitk_reduce_kernel<float>, grid, dim3(256), 0, stream, (const float*)workspace,
+                     ld_partial, splits, (float*)C, ldc, M, N);
 }
 
 FL_API int fl_gemm_tc(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc,

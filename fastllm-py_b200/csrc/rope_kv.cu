@@ -22,6 +22,8 @@ __global__ void rope_kv_kernel(T* __restrict__ qkv, long ld, int n_heads, int n_
                                const float* __restrict__ sin_table, const int* __restrict__ positions,
                                const int* __restrict__ slots, T* __restrict__ k_cache,
                                T* __restrict__ v_cache, long page_stride, int page_size) {
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x, head = blockIdx.y;
     const int half = rot_dim >> 1;
     T* x = qkv + (long)t * ld + (long)head * head_dim;
@@ -76,10 +78,11 @@ FL_API int fl_rope_kv_write(void* qkv, int dtype, long ld, int n_tokens, int n_h
     if (heads > 65535) return (int)cudaErrorInvalidValue;
     dim3 grid(n_tokens, heads);
     const int threads = head_dim >= 128 ? 64 : 32;
-    FL_DISPATCH(dtype, T, (rope_kv_kernel<T><<<grid, threads, 0, stream>>>(
-        (T*)qkv, ld, n_heads, n_kv_heads, head_dim, rot_dim, cos_table, sin_table, positions, slots,
-        (T*)k_cache, (T*)v_cache, page_stride, page_size)));
-    return fl_launch_status();
+    FL_DISPATCH(dtype, T, return fl_launch(rope_kv_kernel<T>, grid, dim3(threads), 0, stream, (T*)qkv, ld,
+                                           n_heads, n_kv_heads, head_dim, rot_dim, cos_table, sin_table,
+                                           positions, slots, (T*)k_cache, (T*)v_cache, page_stride,
+                                           page_size));
+    return 0;
 }
 
 // The same, reading q|k|v as split-K partial sums (float slabs partial[z][t][col],
@@ -96,6 +99,8 @@ __global__ void rope_kv_partial_kernel(const float* __restrict__ partial, int sp
                                        const int* __restrict__ positions, const int* __restrict__ slots,
                                        T* __restrict__ k_cache, T* __restrict__ v_cache, long page_stride,
                                        int page_size) {
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x, head = blockIdx.y;
     const int half = rot_dim >> 1;
     const float* x = partial + (long)t * ld + (long)head * head_dim;
@@ -147,8 +152,9 @@ FL_API int fl_rope_kv_write_partial(const float* partial, int splits, long split
     if (heads > 65535) return (int)cudaErrorInvalidValue;
     dim3 grid(n_tokens, heads);
     const int threads = head_dim >= 128 ? 64 : 32;
-    FL_DISPATCH(dtype, T, (rope_kv_partial_kernel<T><<<grid, threads, 0, stream>>>(
-        partial, splits, split_stride, ld, (T*)q_out, q_ld, n_heads, n_kv_heads, head_dim, rot_dim,
-        cos_table, sin_table, positions, slots, (T*)k_cache, (T*)v_cache, page_stride, page_size)));
-    return fl_launch_status();
+    FL_DISPATCH(dtype, T, return fl_launch(rope_kv_partial_kernel<T>, grid, dim3(threads), 0, stream, partial,
+                                           splits, split_stride, ld, (T*)q_out, q_ld, n_heads, n_kv_heads,
+                                           head_dim, rot_dim, cos_table, sin_table, positions, slots,
+                                           (T*)k_cache, (T*)v_cache, page_stride, page_size));
+    return 0;
 }
