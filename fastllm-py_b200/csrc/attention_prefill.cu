@@ -25,6 +25,9 @@
 #define ATP_BM 64
 #define ATP_BN 64
 #define ATP_THREADS 128
+#ifndef ATP_STAGES
+#define ATP_STAGES 2                      // K/V blocks in shared memory: 2 = fetch the next while multiplying
+#endif
 #define ATP_DP (HEAD_DIM + 8)              // padded row pitch in shared memory: ldmatrix without bank conflicts
 #define ATP_CHUNKS (HEAD_DIM / 8)          // 16-byte chunks per row
 
@@ -76,8 +79,8 @@ __global__ void __launch_bounds__(ATP_THREADS) attention_prefill_kernel(
     pdl_trigger();
     extern __shared__ __align__(16) unsigned char atp_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(atp_raw);                       // [64][DP]
-    bf16* Ks = Qs + ATP_BM * ATP_DP;                                   // [2][64][DP]
-    bf16* Vs = Ks + 2 * ATP_BN * ATP_DP;                               // [2][64][DP]
+    bf16* Ks = Qs + ATP_BM * ATP_DP;                                   // [stages][64][DP]
+    bf16* Vs = Ks + ATP_STAGES * ATP_BN * ATP_DP;                      // [stages][64][DP]
 
     // which request and which 64-row tile of it this CTA serves (heaviest tiles first)
     int req = -1, tile = 0;
@@ -112,21 +115,25 @@ __global__ void __launch_bounds__(ATP_THREADS) attention_prefill_kernel(
             cp_async16(Qs + r * ATP_DP + ch * 8, src, real);
         }
     };
+    // Two threads per key row, half of the row's chunks each: one page lookup per thread and block.
     auto load_kv = [&](int kb, int stage) {
         bf16* kd = Ks + stage * ATP_BN * ATP_DP;
         bf16* vd = Vs + stage * ATP_BN * ATP_DP;
-        for (int c = tid; c < ATP_BN * ATP_CHUNKS; c += ATP_THREADS) {
-            const int r = c / ATP_CHUNKS, ch = c - r * ATP_CHUNKS;
-            const int j = kb * ATP_BN + r;
-            const bool real = j >= lo_tile && j <= pos_last;
-            long a = 0;
-            if (real) {
-                const int pg = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
-                const int off = page_shift >= 0 ? (j & (page_size - 1)) : (j - pg * page_size);
-                a = (long)bt[pg] * page_stride + head_off + (long)off * HEAD_DIM + ch * 8;
-            }
-            cp_async16(kd + r * ATP_DP + ch * 8, k_cache + a, real);
-            cp_async16(vd + r * ATP_DP + ch * 8, v_cache + a, real);
+        const int r = tid >> 1;
+        const int ch0 = (tid & 1) * (ATP_CHUNKS / 2);
+        const int j = kb * ATP_BN + r;
+        const bool real = j >= lo_tile && j <= pos_last;
+        long a = 0;
+        if (real) {
+            const int pg = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
+            const int off = page_shift >= 0 ? (j & (page_size - 1)) : (j - pg * page_size);
+            a = (long)bt[pg] * page_stride + head_off + (long)off * HEAD_DIM;
+        }
+#pragma unroll
+        for (int c = 0; c < ATP_CHUNKS / 2; ++c) {
+            const int ch = ch0 + c;
+            cp_async16(kd + r * ATP_DP + ch * 8, k_cache + a + ch * 8, real);
+            cp_async16(vd + r * ATP_DP + ch * 8, v_cache + a + ch * 8, real);
         }
     };
 
@@ -144,6 +151,7 @@ __global__ void __launch_bounds__(ATP_THREADS) attention_prefill_kernel(
     cp_async_commit();
 
     for (int kb = kb_begin; kb < kb_end; ++kb) {
+#if ATP_STAGES == 2
         const int stage = (kb - kb_begin) & 1;
         if (kb + 1 < kb_end) {
             load_kv(kb + 1, stage ^ 1);
@@ -152,6 +160,14 @@ __global__ void __launch_bounds__(ATP_THREADS) attention_prefill_kernel(
         } else {
             cp_async_wait<0>();
         }
+#else
+        const int stage = 0;
+        if (kb > kb_begin) {
+            load_kv(kb, 0);
+            cp_async_commit();
+        }
+        cp_async_wait<0>();
+#endif
         __syncthreads();
         const bf16* kt = Ks + stage * ATP_BN * ATP_DP;
         const bf16* vt = Vs + stage * ATP_BN * ATP_DP;
@@ -174,37 +190,68 @@ __global__ void __launch_bounds__(ATP_THREADS) attention_prefill_kernel(
                 mma_bf16(s[2 * np + 1], a, b[2], b[3]);
             }
         }
-        // ---- scale, mask, running softmax
-        float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
-#pragma unroll
-        for (int nt = 0; nt < ATP_BN / 8; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int j = kb * ATP_BN + nt * 8 + 2 * tq + (e & 1);
-                const int pr = pos_row[e >> 1];
-                const bool seen = j <= pr && (window <= 0 || j > pr - window);
-                const float v = seen ? s[nt][e] * scale_log2e : -CUDART_INF_F;
-                s[nt][e] = v;
-                mx[e >> 1] = fmaxf(mx[e >> 1], v);
-            }
-        }
+        // ---- scale, mask, running softmax (maxima and sums in units of log2: scores times scale_log2e)
+        const int warp_pos_lo = ctx + row0 + warp * 16, warp_pos_hi = warp_pos_lo + 15;
+        const bool all_seen = (kb * ATP_BN + ATP_BN - 1 <= warp_pos_lo) &&
+                              (window <= 0 || kb * ATP_BN > warp_pos_hi - window);
         float corr[2];
+        if (all_seen) {
+            // every key of the block is visible to every row of this warp: no mask, no special cases
+            float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float m_new = fmaxf(m_run[r], mx[r]);
-            corr[r] = atp_weight(m_run[r], m_new);
-            m_run[r] = m_new;
-            l_run[r] *= corr[r];
-        }
+            for (int nt = 0; nt < ATP_BN / 8; ++nt) {
+                mx[0] = fmaxf(mx[0], fmaxf(s[nt][0], s[nt][1]));
+                mx[1] = fmaxf(mx[1], fmaxf(s[nt][2], s[nt][3]));
+            }
 #pragma unroll
-        for (int nt = 0; nt < ATP_BN / 8; ++nt) {
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m_run[r], mx[r] * scale_log2e);
+                corr[r] = exp2f(m_run[r] - m_new);            // m_new is finite; an empty state gives 0
+                m_run[r] = m_new;
+                l_run[r] *= corr[r];
+            }
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float p = atp_weight(s[nt][e], m_run[e >> 1]);
-                s[nt][e] = p;
-                l_run[e >> 1] += p;
+            for (int nt = 0; nt < ATP_BN / 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p = exp2f(fmaf(s[nt][e], scale_log2e, -m_run[e >> 1]));
+                    s[nt][e] = p;
+                    l_run[e >> 1] += p;
+                }
+            }
+        } else {
+            float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+            for (int nt = 0; nt < ATP_BN / 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = kb * ATP_BN + nt * 8 + 2 * tq + (e & 1);
+                    const int pr = pos_row[e >> 1];
+                    const bool seen = j <= pr && (window <= 0 || j > pr - window);
+                    const float v = seen ? s[nt][e] * scale_log2e : -CUDART_INF_F;
+                    s[nt][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                const float m_new = fmaxf(m_run[r], mx[r]);
+                corr[r] = atp_weight(m_run[r], m_new);
+                m_run[r] = m_new;
+                l_run[r] *= corr[r];
+            }
+#pragma unroll
+            for (int nt = 0; nt < ATP_BN / 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p = atp_weight(s[nt][e], m_run[e >> 1]);
+                    s[nt][e] = p;
+                    l_run[e >> 1] += p;
+                }
             }
         }
 #pragma unroll
@@ -268,7 +315,7 @@ FL_API int fl_attention_prefill(const void* q, long q_ld, void* out, long out_ld
     if (n_requests <= 0 || n_tokens <= 0) return 0;
     if (n_heads > 65535 || n_heads % n_kv_heads) return (int)cudaErrorInvalidValue;
     if ((q_ld % 8) || (out_ld % 2) || (page_stride % 8)) return (int)cudaErrorMisalignedAddress;
-    const size_t smem = (size_t)(ATP_BM + 4 * ATP_BN) * ATP_DP * sizeof(bf16);
+    const size_t smem = (size_t)(ATP_BM + 2 * ATP_STAGES * ATP_BN) * ATP_DP * sizeof(bf16);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -63,6 +63,72 @@ __global__ void rope_kv_kernel(T* __restrict__ qkv, long ld, int n_heads, int n_
     }
 }
 
+// bfloat16, eight elements per thread: a thread takes the pair of 8-element
+// vectors (x[j .. j+8), x[j + half .. j + half + 8)) of one head, or one 8-element
+// vector of a value head.  Used when head_dim is rotated in full and half is a
+// multiple of 8; the form prompt-sized steps use.
+__global__ void rope_kv_bf16x8_kernel(bf16* __restrict__ qkv, long ld, int n_heads, int n_kv_heads,
+                                      int head_dim, const float* __restrict__ cos_table,
+                                      const float* __restrict__ sin_table, const int* __restrict__ positions,
+                                      const int* __restrict__ slots, bf16* __restrict__ k_cache,
+                                      bf16* __restrict__ v_cache, long page_stride, int page_size,
+                                      int has_kv) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int half = head_dim >> 1;
+    const int vec_per_head = half >> 3;                         // pairs of vectors per rotated head
+    const int rot_heads = n_heads + (has_kv ? n_kv_heads : 0);
+    const int rot_items = rot_heads * vec_per_head;
+    const int v_items = has_kv ? n_kv_heads * (head_dim >> 3) : 0;
+    const int item = blockIdx.y * blockDim.x + threadIdx.x;
+    if (item >= rot_items + v_items) return;
+    bf16* row = qkv + (long)t * ld;
+    long cache_off = 0;
+    if (has_kv && item >= n_heads * vec_per_head) {
+        const int slot = slots[t];
+        if (slot < 0) return;
+        const long page = slot / page_size;
+        cache_off = page * page_stride + (long)(slot - (int)page * page_size) * head_dim;
+    }
+    if (item < rot_items) {
+        const int head = item / vec_per_head, j = (item - head * vec_per_head) * 8;
+        const bf16* x = row + (long)head * head_dim;
+        const long pos = positions[t];
+        const float* cs = cos_table + pos * half + j;
+        const float* sn = sin_table + pos * half + j;
+        const uint4 a = *reinterpret_cast<const uint4*>(x + j);
+        const uint4 b = *reinterpret_cast<const uint4*>(x + j + half);
+        const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b);
+        const float4 c0 = *reinterpret_cast<const float4*>(cs), c1 = *reinterpret_cast<const float4*>(cs + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(sn), s1 = *reinterpret_cast<const float4*>(sn + 4);
+        const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        uint4 lo, hi;
+        __nv_bfloat162* lp = reinterpret_cast<__nv_bfloat162*>(&lo);
+        __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 x1 = __bfloat1622float2(ap[k]), x2 = __bfloat1622float2(bp[k]);
+            lp[k] = __floats2bfloat162_rn(x1.x * c[2 * k] - x2.x * sv[2 * k], x1.y * c[2 * k + 1] - x2.y * sv[2 * k + 1]);
+            hp[k] = __floats2bfloat162_rn(x2.x * c[2 * k] + x1.x * sv[2 * k], x2.y * c[2 * k + 1] + x1.y * sv[2 * k + 1]);
+        }
+        bf16* dst = head < n_heads
+                        ? row + (long)head * head_dim
+                        : k_cache + cache_off + (long)(head - n_heads) * page_size * head_dim;
+        *reinterpret_cast<uint4*>(dst + j) = lo;
+        *reinterpret_cast<uint4*>(dst + j + half) = hi;
+    } else {
+        const int vi = item - rot_items;
+        const int per = head_dim >> 3;
+        const int kvh = vi / per, j = (vi - kvh * per) * 8;
+        const bf16* x = row + (long)(n_heads + n_kv_heads + kvh) * head_dim;
+        *reinterpret_cast<uint4*>(v_cache + cache_off + (long)kvh * page_size * head_dim + j) =
+            *reinterpret_cast<const uint4*>(x + j);
+    }
+}
+
 // qkv: [n_tokens, ld] rows of q (n_heads*head_dim) | k | v (n_kv_heads*head_dim each);
 // when has_kv is 0 the rows hold queries only and nothing is written to a cache.
 // k_cache / v_cache point at the key and value halves of a layer's cache
@@ -76,6 +142,16 @@ FL_API int fl_rope_kv_write(void* qkv, int dtype, long ld, int n_tokens, int n_h
     if (rot_dim < 0 || rot_dim > head_dim || (rot_dim & 1)) return (int)cudaErrorInvalidValue;
     const int heads = n_heads + (has_kv ? 2 * n_kv_heads : 0);
     if (heads > 65535) return (int)cudaErrorInvalidValue;
+    if (dtype == FL_BF16 && rot_dim == head_dim && head_dim % 16 == 0 && ld % 8 == 0 && page_stride % 8 == 0 &&
+        ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 16) == 0 &&
+        ((uintptr_t)cos_table % 16) == 0 && ((uintptr_t)sin_table % 16) == 0) {
+        const int items = (n_heads + (has_kv ? n_kv_heads : 0)) * (head_dim / 16) +
+                          (has_kv ? n_kv_heads * (head_dim / 8) : 0);
+        dim3 vgrid(n_tokens, (items + 127) / 128);
+        return fl_launch(rope_kv_bf16x8_kernel, vgrid, dim3(128), 0, stream, (bf16*)qkv, ld, n_heads, n_kv_heads,
+                         head_dim, cos_table, sin_table, positions, slots, (bf16*)k_cache, (bf16*)v_cache,
+                         page_stride, page_size, has_kv);
+    }
     dim3 grid(n_tokens, heads);
     const int threads = head_dim >= 128 ? 64 : 32;
     FL_DISPATCH(dtype, T, return fl_launch(rope_kv_kernel<T>, grid, dim3(threads), 0, stream, (T*)qkv, ld,
