@@ -201,14 +201,15 @@ def time_e2e(model, batch, steps, warmup, context):
     for _ in range(warmup):
         sched.step()
     torch.cuda.synchronize()
+    buf = model.engine.buffers
+    bytes_before = buf.uploaded_bytes
     t0 = time.perf_counter()
     produced = 0
     for _ in range(steps):
         produced += len(sched.step())
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
-    buf = model.engine.buffers
-    h2d = 4 * (buf.small_size + batch * buf.bt_stride * buf.n_groups)
+    h2d = (buf.uploaded_bytes - bytes_before) // steps
     for r in list(sched.running):
         model.engine.end(r.request_id)
     return produced / dt, h2d, 4 * batch

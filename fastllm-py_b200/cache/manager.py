@@ -49,6 +49,9 @@ class RequestCache:
     reserved: int = 0                                 # tokens that the pages taken so far can hold
     pages: list = field(default_factory=list)         # per group: list of page ids by logical index (-1: given back)
     released: list = field(default_factory=list)      # per group: logical pages below this index went back
+    tables: list = field(default_factory=list)        # per group: the same as `pages`, as an int32 row of fixed width
+    version: int = 0                                  # bumped whenever a table row changes
+    uid: int = 0                                      # unique over the manager's life (request ids may be reused)
 
 
 class CacheManager:
@@ -79,6 +82,7 @@ class CacheManager:
                 raise TypeError(f"cache {cid}: unknown need {need!r}")
         self.slots = SlotPool(max_requests)
         self.live: dict = {}                          # request id -> RequestCache
+        self._next_uid = 1
 
     # ------------------------------------------------------------ device side
     def allocate(self, device, activation_dtype):
@@ -111,7 +115,10 @@ class CacheManager:
             raise RuntimeError(f"request {request_id!r} is already live")
         slot = self.slots.take()
         rc = RequestCache(request_id, slot, pages=[[] for _ in self.groups],
-                          released=[0] * len(self.groups))
+                          released=[0] * len(self.groups),
+                          tables=[np.full(self.max_pages_per_request, -1, dtype=np.int32)
+                                  for _ in self.groups], uid=self._next_uid)
+        self._next_uid += 1
         self.live[request_id] = rc
         return rc
 
@@ -146,7 +153,11 @@ class CacheManager:
                     f"request {rc.request_id!r} needs {missing} more pages, "
                     f"{g.pool.free_pages} free of {g.pool.num_pages}")
         for gi, g in enumerate(self.groups):
-            rc.pages[gi].extend(g.pool.take(missing))
+            have = len(rc.pages[gi])
+            new = g.pool.take(missing)
+            rc.pages[gi].extend(new)
+            rc.tables[gi][have:have + missing] = new
+        rc.version += 1
         rc.reserved = total * self.page_size
 
     def commit(self, rc: RequestCache, new_tokens: int) -> None:
@@ -167,6 +178,8 @@ class CacheManager:
                 g.pool.give_back(row[rc.released[gi]:dead_pages])
                 for i in range(rc.released[gi], dead_pages):
                     row[i] = -1
+                rc.tables[gi][rc.released[gi]:dead_pages] = -1
+                rc.version += 1
                 rc.released[gi] = dead_pages
 
     def release(self, request_id) -> None:
@@ -179,16 +192,19 @@ class CacheManager:
 
     # ------------------------------------------------------ tables for a step
     def block_table_row(self, group: int, rc: RequestCache, out: np.ndarray) -> None:
-        row = rc.pages[group]
-        out[:len(row)] = row
-        out[len(row):] = -1
+        out[:] = rc.tables[group]
 
     def slot_mapping(self, group: int, rc: RequestCache, count: int, out: np.ndarray) -> None:
         """Where the next `count` tokens of the request go: page * page_size + offset."""
-        row = rc.pages[group]
         ps = self.page_size
+        if count == 1:
+            page = int(rc.tables[group][rc.seq_len // ps])
+            if page < 0:
+                raise RuntimeError(f"request {rc.request_id!r}: writing into a page that was given back")
+            out[0] = page * ps + rc.seq_len % ps
+            return
         pos = np.arange(rc.seq_len, rc.seq_len + count)
-        pages = np.asarray(row, dtype=np.int64)[pos // ps]
+        pages = rc.tables[group][pos // ps]
         if (pages < 0).any():
             raise RuntimeError(f"request {rc.request_id!r}: writing into a page that was given back")
         out[:count] = pages * ps + pos % ps

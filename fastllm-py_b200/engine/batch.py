@@ -59,6 +59,7 @@ class StepBuffers:
         self.host_np = self.host.numpy()
         self.dev = torch.zeros(self.total, dtype=torch.int32, device=device)
         self.copied = None                                # event after the last upload
+        self.uploaded_bytes = 0                           # host-to-device bytes copied so far
 
     def host_view(self, name):
         off, size = self.offsets[name]
@@ -73,12 +74,17 @@ class StepBuffers:
             self.copied.synchronize()
 
     def upload(self, n_requests: int):
-        """Per-token section whole, block tables only for the rows in use."""
+        """Per-token section whole; block tables for the first `n_requests` rows
+        (0 when no row changed since the last upload)."""
         self.dev[:self.small_size].copy_(self.host[:self.small_size], non_blocking=True)
+        self.uploaded_bytes += 4 * self.small_size
         for g in range(self.n_groups):
+            if n_requests == 0:
+                break
             off, _ = self.offsets[f"bt{g}"]
             used = n_requests * self.bt_stride
             self.dev[off:off + used].copy_(self.host[off:off + used], non_blocking=True)
+            self.uploaded_bytes += 4 * used
         if self.dev.is_cuda:
             self.copied = torch.cuda.Event()
             self.copied.record()

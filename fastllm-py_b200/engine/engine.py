@@ -51,6 +51,7 @@ class Engine:
         self.use_graph = bool(config.cuda_graph)
         self._graphs: dict = {}          # step shape -> (graph, logits view, kernels in it)
         self._warmed: set = set()
+        self._bt_rows: list = [None] * config.max_requests   # (request uid, table version) last written per row
 
     # -------------------------------------------------------------- requests
     def begin(self, request_id):
@@ -93,10 +94,9 @@ class Engine:
             if rc.seq_len + len(e.tokens) > self.max_model_len:
                 raise ValueError(f"request {e.request_id!r} would reach {rc.seq_len + len(e.tokens)} "
                                  f"tokens; the engine's longest sequence is {self.max_model_len}")
-            for t in e.tokens:
-                if not 0 <= int(t) < self.vocab:
-                    raise ValueError(f"request {e.request_id!r}: token id {t} is outside the "
-                                     f"vocabulary of {self.vocab}")
+            if min(e.tokens) < 0 or max(e.tokens) >= self.vocab:
+                raise ValueError(f"request {e.request_id!r}: a token id is outside the "
+                                 f"vocabulary of {self.vocab}")
             for w in e.want:
                 if not 0 <= int(w) < len(e.tokens):
                     raise ValueError(f"request {e.request_id!r}: wanted place {w} is outside its "
@@ -121,6 +121,7 @@ class Engine:
         bt_views = [buf.host_view(f"bt{g}").reshape(buf.max_requests, buf.bt_stride)
                     for g in range(len(cache.groups))]
         at, m = 0, 0
+        bt_dirty = False
         q_lens, ctx_lens, slots_host = [], [], []
         for r, e in enumerate(entries):
             rc = cache.live[e.request_id]
@@ -134,7 +135,11 @@ class Engine:
                 m += 1
             for g in range(len(cache.groups)):
                 cache.slot_mapping(g, rc, q, slot_views[g][at:at + q])
-                cache.block_table_row(g, rc, bt_views[g][r])
+            if self._bt_rows[r] != (rc.uid, rc.version):   # the row on the device is stale
+                for g in range(len(cache.groups)):
+                    cache.block_table_row(g, rc, bt_views[g][r])
+                self._bt_rows[r] = (rc.uid, rc.version)
+                bt_dirty = True
             rstart[r], rctx[r], rqlen[r], rslot[r] = at, rc.seq_len, q, rc.slot
             if q == 1:
                 dec[n_dec] = at
@@ -144,7 +149,7 @@ class Engine:
             slots_host.append(rc.slot)
             at += q
         rstart[len(entries)] = at
-        buf.upload(len(entries))
+        buf.upload(len(entries) if bt_dirty else 0)
         n = len(entries)
         step = StepContext(
             n_tokens=n_tokens, n_requests=n, n_wanted=m,

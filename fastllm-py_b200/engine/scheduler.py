@@ -171,8 +171,14 @@ class Scheduler:
             return []
         entries, sampled = [], []
         for req, n in planned:
-            toks = req.tokens[req.computed:req.computed + n]
-            last = req.computed + n == len(req.prompt) + len(req.output)
+            lp = len(req.prompt)
+            if req.computed >= lp:
+                toks = req.output[req.computed - lp:req.computed - lp + n]
+            elif req.computed + n <= lp:
+                toks = req.prompt[req.computed:req.computed + n]
+            else:
+                toks = req.tokens[req.computed:req.computed + n]
+            last = req.computed + n == lp + len(req.output)
             entries.append(StepEntry(req.request_id, toks, [n - 1] if last else []))
             if last:
                 sampled.append(req)

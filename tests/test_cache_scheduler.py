@@ -66,9 +66,9 @@ def test_extend_commit_tables():
     m.commit(rc, 1)
     m.extend(rc, 2)                                        # token 9 needs a third
     assert len(rc.pages[0]) == 3
-    row = np.zeros(6, dtype=np.int32)
+    row = np.zeros(m.max_pages_per_request, dtype=np.int32)
     m.block_table_row(0, rc, row)
-    assert row.tolist() == rc.pages[0] + [-1, -1, -1]
+    assert row.tolist() == rc.pages[0] + [-1] * (m.max_pages_per_request - 3)
     with pytest.raises(RuntimeError):
         m.commit(rc, 9)                                    # more tokens than pages were taken for
     m.check()
