@@ -1,0 +1,486 @@
+// Paged causal attention for prompt portions on the Blackwell tensor cores:
+// both products (Q K^T and P V) are tcgen05.mma with the accumulators in tensor
+// memory; keys, values and queries arrive by TMA; the softmax runs in float on
+// 128 threads that each own one query row.
+//
+// A CTA takes 128 consecutive query rows of one request and one query head and
+// walks the request's keys in blocks of 128 (starting at multiples of 128 of the
+// absolute position, so a row's sequence of partial maxima does not depend on
+// how the prompt was cut).  Per block:
+//   producer warp   TMA: the block's pages of this head's keys and values into a
+//                   two-stage ring (one box of page_size x 64 per page and 64
+//                   columns; pages that do not exist are fetched from beyond the
+//                   tensor, which fills zeros);
+//   MMA warp        S = Q K^T into one of two S buffers in tensor memory (so the
+//                   next block's scores are computed while this block's are
+//                   being exponentiated), then O_blk = P V;
+//   softmax warps   two threads share query row r: each reads its half of the
+//                   row of S (tcgen05.ld), masks, exchanges the half-row maximum
+//                   with its partner, keeps the running maximum and sum in float,
+//                   writes its half of P as bfloat16 into shared memory in the
+//                   swizzled K-major layout the second MMA reads, then adds its
+//                   half of the columns of O_blk into its part of the output row,
+//                   which it holds in registers (rescaled when the maximum moves).
+// Every wait on an mbarrier is bounded; a give-up sets an error word and all
+// roles leave.
+//
+// fastllm-py's counterpart is `_sdpa` (fastllm_py/model.py:341-353).  The
+// mma.sync kernel in attention_prefill.cu computes the same thing and serves the
+// head sizes and page sizes this one does not take (HEAD_DIM 64 or 128; page
+// sizes that are multiples of 8 and divide 128).
+#include <cuda.h>
+
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 128
+#endif
+static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "the tcgen05 prefill kernel takes head sizes 64 and 128");
+
+#define FT_BM 128                          // query rows per CTA
+#define FT_BN 128                          // keys per block
+#define FT_STAGES 2
+#define FT_THREADS 320                     // 8 softmax warps (two threads per query row), producer warp, MMA warp
+#define FT_SOFTMAX_THREADS 256
+#define FT_ATOMS (HEAD_DIM / 64)           // 64-column swizzle atoms per row
+#define FT_ATOM_BYTES (128 * 128)          // 128 rows x 128 bytes
+#define FT_WAIT_LIMIT_NS 2000000000ull
+enum { FT_ERR_WAIT = 301 };
+
+// ------------------------------------------------------------------ PTX wraps
+__device__ __forceinline__ uint32_t ft_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ft_bar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(ft_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void ft_bar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ft_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void ft_bar_expect(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(ft_smem(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ uint64_t ft_now() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool ft_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    uint32_t ok = 0, spins = 0;
+    uint64_t t0 = 0;
+    while (true) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(ft_smem(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((++spins & 127u) == 0) {
+            if (*abort_flag) return false;
+            if (t0 == 0) t0 = ft_now();
+            else if (ft_now() - t0 > FT_WAIT_LIMIT_NS) return false;
+        }
+    }
+}
+__device__ __forceinline__ void ft_tma_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];" ::"r"(ft_smem(dst)),
+        "l"((uint64_t)map), "r"(ft_smem(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void ft_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void ft_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void ft_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void ft_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(ft_smem(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void ft_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, "
+        "%22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+          "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+          "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void ft_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand, rows of 128 bytes in the 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t ft_desc_kmajor(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand (the contiguous axis is N): 64-element blocks of N are FT_ATOM_BYTES apart
+// (leading offset), groups of 8 K rows 1024 bytes apart (stride offset).
+__device__ __forceinline__ uint64_t ft_desc_mnmajor(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(FT_ATOM_BYTES >> 4) << 16) |
+           ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// float accumulator, bfloat16 operands; b_mn: B is MN-major
+__host__ __device__ constexpr uint32_t ft_idesc(int m, int n, int b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ float ft_weight(float a, float b) { return (a == -CUDART_INF_F) ? 0.0f : exp2f(a - b); }
+
+struct FtSmem {
+    static constexpr int Q_BYTES = FT_ATOMS * FT_ATOM_BYTES;
+    static constexpr int KV_BYTES = FT_ATOMS * FT_ATOM_BYTES;          // one of K or V, one stage
+    static constexpr int P_BYTES = 2 * FT_ATOM_BYTES;                  // 128 rows x 128 keys
+    static constexpr int TILES = Q_BYTES + 2 * FT_STAGES * KV_BYTES + P_BYTES;
+    static constexpr int BARS = 16 * 8 + 16 + 2 * 128 * 4;             // barriers, then the half-row maxima
+    static constexpr int TOTAL = TILES + BARS + 1024;
+};
+
+__global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+    bf16* __restrict__ out, long out_ld, int page_size, int kv_rows_total, const int* __restrict__ block_table,
+    int bt_stride, const int* __restrict__ req_start, const int* __restrict__ req_ctx,
+    const int* __restrict__ req_qlen, int n_requests, int include_single, int n_heads, int n_kv_heads,
+    int window, float scale_log2e, int* __restrict__ status) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ unsigned char ft_raw[];
+    unsigned char* base = (unsigned char*)(((uintptr_t)ft_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_s = base;
+    unsigned char* k_s = q_s + FtSmem::Q_BYTES;                        // [stage][atom][128 rows][128 B]
+    unsigned char* v_s = k_s + FT_STAGES * FtSmem::KV_BYTES;
+    unsigned char* p_s = v_s + FT_STAGES * FtSmem::KV_BYTES;           // [atom][128 rows][128 B]
+    uint64_t* bars = (uint64_t*)(base + FtSmem::TILES);
+    uint64_t* q_full = bars + 0;
+    uint64_t* kv_full = bars + 1;                                      // [2]
+    uint64_t* kv_empty = bars + 3;                                     // [2]
+    uint64_t* s_full = bars + 5;                                       // [2]
+    uint64_t* s_empty = bars + 7;                                      // [2]
+    uint64_t* p_full = bars + 9;
+    uint64_t* p_empty = bars + 10;
+    uint64_t* o_full = bars + 11;
+    uint64_t* o_empty = bars + 12;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 13);
+    uint64_t* x_bar = bars + 14;                                       // the softmax threads' exchange point
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    // which request and which 128-row tile (heaviest first)
+    int req = -1, tile = 0;
+    {
+        int acc = 0;
+        for (int r = 0; r < n_requests; ++r) {
+            const int ql = req_qlen[r];
+            const int nt = (ql > 1 || include_single) ? (ql + FT_BM - 1) / FT_BM : 0;
+            if ((int)blockIdx.x < acc + nt) { req = r; tile = nt - 1 - ((int)blockIdx.x - acc); break; }
+            acc += nt;
+        }
+    }
+    if (req < 0) return;
+    const int h = blockIdx.y;
+    const int kvh = h / (n_heads / n_kv_heads);
+    const int q_len = req_qlen[req], ctx = req_ctx[req], row0 = tile * FT_BM;
+    const int tok0 = req_start[req] + row0;
+    const int rows_here = min(FT_BM, q_len - row0);
+    const int pos_first = ctx + row0, pos_last = ctx + row0 + rows_here - 1;
+    const int lo_tile = window > 0 ? max(0, pos_first - window + 1) : 0;
+    const int kb_begin = lo_tile / FT_BN, kb_end = pos_last / FT_BN + 1;
+    const int n_blocks = kb_end - kb_begin;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        ft_bar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            ft_bar_init(&kv_full[s], 1);
+            ft_bar_init(&kv_empty[s], 1);
+            ft_bar_init(&s_full[s], 1);
+            ft_bar_init(&s_empty[s], FT_SOFTMAX_THREADS);
+        }
+        ft_bar_init(p_full, FT_SOFTMAX_THREADS);
+        ft_bar_init(p_empty, 1);
+        ft_bar_init(o_full, 1);
+        ft_bar_init(o_empty, FT_SOFTMAX_THREADS);
+        ft_bar_init(x_bar, FT_SOFTMAX_THREADS);
+        *abort_flag = (*(volatile int*)status != 0) ? 1 : 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ft_smem(tmem_slot)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    ft_fence_before();
+    __syncthreads();
+    ft_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_s = tmem;                                      // two S buffers: columns 0 and 128
+    const uint32_t tmem_o = tmem + 256;                                // O_blk: HEAD_DIM columns
+
+#define FT_GIVE_UP()                                                             \
+    {                                                                            \
+        if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, FT_ERR_WAIT); } \
+        break;                                                                   \
+    }
+
+    if (warp == 8) {
+        if (lane == 0 && !*abort_flag) {
+            // ---- producer
+            ft_bar_expect(q_full, FtSmem::Q_BYTES);
+            for (int a = 0; a < FT_ATOMS; ++a)
+                ft_tma_2d(q_s + a * FT_ATOM_BYTES, &map_q, q_full, h * HEAD_DIM + a * 64, tok0);
+            const int* bt = block_table + (long)req * bt_stride;
+            const int pages_per_block = FT_BN / page_size;
+            for (int i = 0; i < n_blocks; ++i) {
+                const int s = i & 1;
+                if (!ft_wait(&kv_empty[s], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag)) FT_GIVE_UP();
+                ft_bar_expect(&kv_full[s], 2 * FtSmem::KV_BYTES);
+                const int key0 = (kb_begin + i) * FT_BN;
+                for (int p = 0; p < pages_per_block; ++p) {
+                    const int first_key = key0 + p * page_size;
+                    const int last_key = first_key + page_size - 1;
+                    // a page wholly outside what this tile may see is fetched from beyond the tensor: zeros
+                    int row_k = kv_rows_total, row_v = kv_rows_total;
+                    if (first_key <= pos_last && last_key >= lo_tile) {
+                        const long pg = bt[first_key / page_size];
+                        row_k = (int)(((pg * 2 + 0) * n_kv_heads + kvh) * page_size);
+                        row_v = (int)(((pg * 2 + 1) * n_kv_heads + kvh) * page_size);
+                    }
+                    for (int a = 0; a < FT_ATOMS; ++a) {
+                        const int off = s * FtSmem::KV_BYTES + a * FT_ATOM_BYTES + p * page_size * 128;
+                        ft_tma_2d(k_s + off, &map_kv, &kv_full[s], a * 64, row_k);
+                        ft_tma_2d(v_s + off, &map_kv, &kv_full[s], a * 64, row_v);
+                    }
+                }
+            }
+        }
+    } else if (warp == 9) {
+        if (lane == 0 && !*abort_flag) {
+            // ---- MMA issuer
+            constexpr uint32_t idesc_s = ft_idesc(FT_BM, FT_BN, 0);
+            constexpr uint32_t idesc_o = ft_idesc(FT_BM, HEAD_DIM, 1);
+            auto issue_s = [&](int i) -> bool {                        // S(i) = Q K(i)^T into S buffer i & 1
+                const int s = i & 1;
+                if (!ft_wait(&kv_full[s], (uint32_t)(i >> 1) & 1u, abort_flag)) return false;
+                if (!ft_wait(&s_empty[s], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag)) return false;
+                ft_fence_after();
+                const uint32_t qa = ft_smem(q_s), ka = ft_smem(k_s + s * FtSmem::KV_BYTES);
+#pragma unroll
+                for (int k = 0; k < HEAD_DIM / 16; ++k) {
+                    const uint32_t off = (uint32_t)((k >> 2) * FT_ATOM_BYTES + (k & 3) * 32);
+                    ft_mma(tmem_s + (uint32_t)(s * FT_BN), ft_desc_kmajor(qa + off), ft_desc_kmajor(ka + off),
+                           idesc_s, k > 0 ? 1u : 0u);
+                }
+                ft_commit(&s_full[s]);
+                return true;
+            };
+            bool ok = ft_wait(q_full, 0, abort_flag);
+            if (ok) ok = issue_s(0);
+            for (int i = 0; i < n_blocks && ok; ++i) {
+                if (i + 1 < n_blocks && !issue_s(i + 1)) { ok = false; break; }
+                if (!ft_wait(p_full, (uint32_t)i & 1u, abort_flag)) { ok = false; break; }
+                if (!ft_wait(o_empty, ((uint32_t)i & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                ft_fence_after();
+                const uint32_t pa = ft_smem(p_s), va = ft_smem(v_s + (i & 1) * FtSmem::KV_BYTES);
+#pragma unroll
+                for (int k = 0; k < FT_BN / 16; ++k) {
+                    // A = P: K-major, keys are its K axis; B = V: MN-major, 16 keys = two 8-row groups
+                    const uint32_t a_off = (uint32_t)((k >> 2) * FT_ATOM_BYTES + (k & 3) * 32);
+                    ft_mma(tmem_o, ft_desc_kmajor(pa + a_off), ft_desc_mnmajor(va + (uint32_t)(k * 16 * 128)),
+                           idesc_o, k > 0 ? 1u : 0u);
+                }
+                ft_commit(&kv_empty[i & 1]);
+                ft_commit(p_empty);
+                ft_commit(o_full);
+            }
+            if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, FT_ERR_WAIT); }
+        }
+    } else {
+        // ---- softmax: threads r and r + 128 share query row r; `half` says which
+        // 64 keys of a block and which half of the output columns a thread owns
+        const int r = threadIdx.x & 127;
+        const int half = threadIdx.x >> 7;
+        const int pos_r = ctx + row0 + r;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        float* half_max = reinterpret_cast<float*>(bars + 16);            // [2][128]
+        constexpr int OD = HEAD_DIM / 2;                                 // output columns per thread
+        float m_run = -CUDART_INF_F, l_run = 0.0f;
+        float o_reg[OD];
+#pragma unroll
+        for (int d = 0; d < OD; ++d) o_reg[d] = 0.0f;
+        bool ok = !*abort_flag;
+        for (int i = 0; i < n_blocks && ok; ++i) {
+            const int sb = i & 1;
+            if (!ft_wait(&s_full[sb], (uint32_t)(i >> 1) & 1u, abort_flag)) FT_GIVE_UP();
+            ft_fence_after();
+            const int key0 = (kb_begin + i) * FT_BN + half * 64;         // first key of this thread's half
+            const uint32_t s_addr = tmem_s + (uint32_t)(sb * FT_BN + half * 64) + lane_base;
+            const bool all_seen = (key0 + 63 <= pos_r) && (window <= 0 || key0 > pos_r - window);
+            uint32_t v[64];
+            ft_ld32(s_addr, v);
+            ft_ld32(s_addr + 32u, v + 32);
+            ft_ld_wait();
+            if (!all_seen) {
+#pragma unroll
+                for (int j = 0; j < 64; ++j) {
+                    const int key = key0 + j;
+                    if (!(key <= pos_r && (window <= 0 || key > pos_r - window))) v[j] = 0xff800000u;   // -inf
+                }
+            }
+            float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+            for (int j = 0; j < 64; j += 4) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], __uint_as_float(v[j + e]));
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // exchange the half-row maxima (one barrier among the softmax threads per block)
+            half_max[half * 128 + r] = mx;
+            ft_bar_arrive(x_bar);                                         // (an mbarrier: its wait can give up)
+            if (!ft_wait(x_bar, (uint32_t)i & 1u, abort_flag)) FT_GIVE_UP();
+            const float mx_row = fmaxf(mx, half_max[(half ^ 1) * 128 + r]);
+            const float m_new = fmaxf(m_run, mx_row * scale_log2e);
+            const float corr = ft_weight(m_run, m_new);
+            const float neg_m = (m_new == -CUDART_INF_F) ? 0.0f : -m_new;      // an empty row: every p below is 0
+            if (!ft_wait(p_empty, ((uint32_t)i & 1u) ^ 1u, abort_flag)) FT_GIVE_UP();
+            float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            unsigned char* row_base = p_s + half * FT_ATOM_BYTES + r * 128;
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {                               // 8 keys = one 16-byte chunk
+                uint32_t packed[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p0 = exp2f(fmaf(__uint_as_float(v[c8 * 8 + 2 * e]), scale_log2e, neg_m));
+                    const float p1 = exp2f(fmaf(__uint_as_float(v[c8 * 8 + 2 * e + 1]), scale_log2e, neg_m));
+                    l4[e] += p0 + p1;
+                    const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+                    packed[e] = *reinterpret_cast<const uint32_t*>(&b);
+                }
+                *reinterpret_cast<uint4*>(row_base + ((c8 ^ (r & 7)) << 4)) =
+                    make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+            l_run = l_run * corr + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
+            m_run = m_new;
+            ft_fence_before();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
+            ft_bar_arrive(p_full);
+            ft_bar_arrive(&s_empty[sb]);
+            // the block's P V: this thread's half of the columns, added into its part of the row
+            if (!ft_wait(o_full, (uint32_t)i & 1u, abort_flag)) FT_GIVE_UP();
+            ft_fence_after();
+#pragma unroll
+            for (int c = 0; c < OD; c += 32) {
+                uint32_t w[32];
+                ft_ld32(tmem_o + lane_base + (uint32_t)(half * OD + c), w);
+                ft_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o_reg[c + j] = fmaf(o_reg[c + j], corr, __uint_as_float(w[j]));
+            }
+            ft_fence_before();
+            ft_bar_arrive(o_empty);
+        }
+        // the row's sum is the two halves' sums (both are relative to the same maximum)
+        half_max[half * 128 + r] = l_run;
+        ft_bar_arrive(x_bar);
+        const bool met = ft_wait(x_bar, (uint32_t)n_blocks & 1u, abort_flag);
+        const float l_row = l_run + half_max[(half ^ 1) * 128 + r];
+        if (met && ok && !*abort_flag && r < rows_here) {
+            const float inv = 1.0f / l_row;
+            bf16* dst = out + (long)(tok0 + r) * out_ld + (long)h * HEAD_DIM + half * OD;
+#pragma unroll
+            for (int d = 0; d < OD; d += 8) {
+                uint4 w;
+                __nv_bfloat162* wp = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    wp[e] = __floats2bfloat162_rn(o_reg[d + 2 * e] * inv, o_reg[d + 2 * e + 1] * inv);
+                *reinterpret_cast<uint4*>(dst + d) = w;
+            }
+        }
+    }
+#undef FT_GIVE_UP
+    ft_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        ft_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// ----------------------------------------------------------------- host side
+typedef CUresult (*FtEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static FtEncodeFn ft_encode_fn() {
+    static FtEncodeFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (FtEncodeFn)p;
+    }
+    return fn;
+}
+static int ft_make_map(CUtensorMap* map, const void* base, long rows, long cols, long ld, int box_rows) {
+    FtEncodeFn fn = ft_encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    if (((uintptr_t)base & 15) || ((ld * 2) & 15)) return (int)cudaErrorMisalignedAddress;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+FL_API int fl_attention_prefill_tc_head_dim() { return HEAD_DIM; }
+FL_API int fl_attention_prefill_tc_takes(int page_size) {
+    return page_size >= 8 && page_size <= FT_BN && page_size % 8 == 0 && FT_BN % page_size == 0;
+}
+
+// The arguments of fl_attention_prefill (attention_prefill.cu) with the cache given
+// as one tensor [n_pages, 2, n_kv_heads, page_size, HEAD_DIM] and a status word.
+FL_API int fl_attention_prefill_tc(const void* q, long q_ld, void* out, long out_ld, const void* cache,
+                                   long n_pages, int page_size, const int* block_table, int bt_stride,
+                                   const int* req_start, const int* req_ctx, const int* req_qlen,
+                                   int n_requests, int n_tokens, int include_single, int n_heads,
+                                   int n_kv_heads, int window, float scale, int* status, cudaStream_t stream) {
+    if (n_requests <= 0 || n_tokens <= 0) return 0;
+    if (!fl_attention_prefill_tc_takes(page_size) || n_heads > 65535 || n_heads % n_kv_heads)
+        return (int)cudaErrorInvalidValue;
+    if ((q_ld % 8) || (out_ld % 8)) return (int)cudaErrorMisalignedAddress;
+    const long kv_rows = n_pages * 2 * n_kv_heads * page_size;
+    if (kv_rows >= (1l << 31)) return (int)cudaErrorInvalidValue;
+    CUtensorMap map_q, map_kv;
+    int rc = ft_make_map(&map_q, q, n_tokens, (long)n_heads * HEAD_DIM, q_ld, FT_BM);
+    if (rc) return rc;
+    rc = ft_make_map(&map_kv, cache, kv_rows, HEAD_DIM, HEAD_DIM, page_size);
+    if (rc) return rc;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             FtSmem::TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int max_tiles = n_tokens / FT_BM + n_requests;
+    dim3 grid(max_tiles, n_heads);
+    return fl_launch(attention_prefill_tc_kernel, grid, dim3(FT_THREADS), (size_t)FtSmem::TOTAL, stream, map_q,
+                     map_kv, (bf16*)out, out_ld, page_size, (int)kv_rows, block_table, bt_stride, req_start, req_ctx,
+                     req_qlen, n_requests, include_single, n_heads, n_kv_heads, window,
+                     scale * 1.4426950408889634f, status);
+}

@@ -24,8 +24,21 @@ def handles(dtype, head_dim: int) -> bool:
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
 
 
+TC_PREFILL_HEAD_DIMS = (64, 128)       # head sizes the tcgen05 prefill kernel is built for
+
+
 def libraries(head_dim: int) -> list:
-    return [("attention_decode", {"HEAD_DIM": head_dim}), ("attention_prefill", {"HEAD_DIM": head_dim})]
+    libs = [("attention_decode", {"HEAD_DIM": head_dim}), ("attention_prefill", {"HEAD_DIM": head_dim})]
+    if head_dim in TC_PREFILL_HEAD_DIMS:
+        libs.append(("attention_prefill_tc", {"HEAD_DIM": head_dim}))
+    return libs
+
+
+def tc_prefill_takes(head_dim: int, page_size: int) -> bool:
+    """The tcgen05 prefill kernel's limits: head size 64 or 128, pages of a
+    multiple of 8 tokens that divide its 128-key block."""
+    return head_dim in TC_PREFILL_HEAD_DIMS and page_size % 8 == 0 and 8 <= page_size <= 128 \
+        and 128 % page_size == 0
 
 
 def _decode_lib(head_dim: int):
@@ -53,6 +66,20 @@ def _prefill_lib(head_dim: int):
                                              c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
         lib.fl_attention_prefill.restype = c_int
         assert lib.fl_attention_prefill_head_dim() == head_dim
+        _libs[key] = lib
+    return lib
+
+
+def _prefill_tc_lib(head_dim: int):
+    key = ("prefill_tc", head_dim)
+    lib = _libs.get(key)
+    if lib is None:
+        lib = load_library("attention_prefill_tc", {"HEAD_DIM": head_dim})
+        lib.fl_attention_prefill_tc.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int,
+                                                c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                                c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
+        lib.fl_attention_prefill_tc.restype = c_int
+        assert lib.fl_attention_prefill_tc_head_dim() == head_dim
         _libs[key] = lib
     return lib
 
@@ -92,8 +119,24 @@ def decode_attention(q, out, cache_tensor, block_table, tok_req, positions, tok_
 
 
 def prefill_attention(q, out, cache_tensor, block_table, req_start, req_ctx, req_qlen, n_requests,
-                      n_tokens, include_single, heads, kv_heads, head_dim, window, scale, page_size):
-    """Tensor-core attention for the requests of the step that bring several tokens."""
+                      n_tokens, include_single, heads, kv_heads, head_dim, window, scale, page_size,
+                      variant=0):
+    """Tensor-core attention for the requests of the step that bring several tokens.
+    variant 0 chooses: the tcgen05 kernel where it applies (2), else mma.sync (1)."""
+    if variant == 0:
+        variant = 2 if tc_prefill_takes(head_dim, page_size) and cache_tensor.is_contiguous() else 1
+    if variant == 2:
+        from .gemm_tc import status_word
+
+        lib = _prefill_tc_lib(head_dim)
+        rc = lib.fl_attention_prefill_tc(ops._ptr(q), ops._ld(q), ops._ptr(out), ops._ld(out),
+                                         ops._ptr(cache_tensor), cache_tensor.shape[0], page_size,
+                                         ops._ptr(block_table), block_table.stride(0), ops._ptr(req_start),
+                                         ops._ptr(req_ctx), ops._ptr(req_qlen), n_requests, n_tokens,
+                                         1 if include_single else 0, heads, kv_heads, int(window or 0),
+                                         float(scale), ops._ptr(status_word(q.device)), ops._stream())
+        ops._check(rc, "attention_prefill_tc")
+        return
     lib = _prefill_lib(head_dim)
     k_ptr = c_void_p(cache_tensor.data_ptr())
     v_ptr = c_void_p(cache_tensor.data_ptr() + cache_tensor.stride(1) * cache_tensor.element_size())

@@ -164,7 +164,7 @@ def run_simt(case, window=None):
     return out.float().cpu()
 
 
-def run_fast(case, window=None):
+def run_fast(case, window=None, prefill_variant=0):
     from fastllm_py_b200.native import attention as fast
 
     out = torch.zeros_like(case.q)
@@ -179,7 +179,7 @@ def run_fast(case, window=None):
     if n_dec < case.n_tokens:
         fast.prefill_attention(case.q, out, case.cache, case.block_table, case.req_start, case.req_ctx,
                                case.req_qlen, len(case.q_lens), case.n_tokens, False, case.heads,
-                               case.kv_heads, case.head_dim, window, scale, case.page_size)
+                               case.kv_heads, case.head_dim, window, scale, case.page_size, prefill_variant)
     return out.float().cpu()
 
 
@@ -211,7 +211,34 @@ def test_tensor_core_and_split_key_attention(shape, window):
     assert float(diff) <= case.tolerance()
 
 
-@pytest.mark.parametrize("runner", [run_simt, run_fast])
+TC_SHAPES = [
+    # q_lens, ctx_lens, heads, kv_heads, head_dim, page_size: what the tcgen05 prefill kernel takes
+    ([130], [257], 8, 1, 128, 16),
+    ([5, 300, 128, 2], [0, 40, 7, 129], 6, 2, 64, 8),
+    ([257, 1, 64], [0, 600, 1000], 4, 4, 128, 32),
+    ([129, 127], [383, 0], 2, 2, 64, 128),
+    ([700], [0], 3, 1, 128, 64),
+]
+
+
+@pytest.mark.parametrize("shape", TC_SHAPES)
+@pytest.mark.parametrize("window", [None, 37, 200])
+@pytest.mark.parametrize("variant", [1, 2])
+def test_prefill_attention_both_tensor_core_kernels(shape, window, variant):
+    """variant 1: mma.sync; variant 2: tcgen05 (S and P V in tensor memory)."""
+    from fastllm_py_b200.native.gemm_tc import status_word
+
+    case = AttentionCase(*shape, torch.bfloat16, seed=7)
+    diff = (run_fast(case, window, variant) - case.reference(window)).abs().max()
+    assert int(status_word(torch.device(DEV)).item()) == 0
+    assert float(diff) <= case.tolerance()
+
+
+def run_fast_tcgen05(case, window=None):
+    return run_fast(case, window, 2)
+
+
+@pytest.mark.parametrize("runner", [run_simt, run_fast, run_fast_tcgen05])
 def test_a_far_key_among_hundreds_is_found(runner):
     """One key far back (and one right at a page edge, one at a split edge) gets
     nearly all the weight: the output must be that key's value."""
