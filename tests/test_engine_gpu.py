@@ -147,3 +147,26 @@ def test_long_decoding(model_folders):
         compare(got, ref, tol, f"long decoding {dtype}")
     _plain_cache.pop((name, True), None)
     _plain_cache.pop((name, False), None)
+
+
+def test_weights_stored_in_32_bit_stay_so(tmp_path):
+    """A checkpoint stored in float32 run with bfloat16 activations: the matrices stay 32-bit
+    (the CUDA-core product takes them), and the logits match the plain model."""
+    import tiny as tiny_configs
+
+    name = "tiny_a"
+    folder = tiny_configs.write(name, tmp_path / "f32model", dtype="float32")
+    from safetensors.torch import load_file
+    assert load_file(str(folder / "model.safetensors"))["model.norm.weight"].dtype == torch.float32
+    requests = make_requests(name)
+    weights, config = plain.load_folder(folder)
+    ref = {r: plain.forward(weights, config, t, store=plain.store_bf16) for r, t in requests.items()}
+    exact = {r: plain.forward(weights, config, t) for r, t in requests.items()}
+    tol = 2.0 * max(float((ref[r] - exact[r]).abs().max()) for r in ref) + 1e-3
+    from fastllm_py_b200 import Model
+    model = Model.load(folder, dtype="bfloat16", page_size=16, max_tokens=512, max_requests=8,
+                       max_batched_tokens=512, max_model_len=256, cuda_graph=False)
+    lin = model.decoder.blocks[0].mixer.qkv
+    assert lin.weight.dtype == torch.float32
+    got = replay.run_in_process(model.engine, replay.mixed(requests, live=3, seed=1))
+    compare(got, ref, tol, "float32 weights under bfloat16 activations")

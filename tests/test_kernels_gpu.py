@@ -269,3 +269,137 @@ def test_window_edge(runner):
     assert float((got - ref).abs().max()) <= case.tolerance()
     assert float((got[0].reshape(2, 32)[1] - case.v_full[0][inside, 1]).abs().max()) < 0.05
     assert float((got[0].reshape(2, 32)[0] - case.v_full[0][outside, 0]).abs().max()) > 0.5
+
+
+# ------------------------------------------------ rotary + cache write, norms, SwiGLU
+
+def rope_reference(x, pos, cos, sin, rot):
+    """x: [T, heads, D] float; rotate-half over the first `rot` dimensions."""
+    half = rot // 2
+    x1, x2 = x[..., :half], x[..., half:rot]
+    c, s = cos[pos][:, None, :], sin[pos][:, None, :]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, x[..., rot:]], dim=-1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads, kv_heads, head_dim, rot, page_size", [
+    (4, 2, 16, 16, 8), (3, 3, 48, 48, 16), (8, 1, 128, 128, 16), (2, 2, 64, 32, 4), (5, 5, 80, 80, 12)])
+def test_rope_and_cache_write(dtype, heads, kv_heads, head_dim, rot, page_size):
+    """Every form of the kernel (scalar, 16-byte vectors, reading split-K partial
+    sums) against a float reference, including partial rotation and odd pages."""
+    from fastllm_py_b200.native import ops
+    from fastllm_py_b200.native.gemm_tc import Partial
+
+    g = torch.Generator().manual_seed(head_dim + rot)
+    n, n_pages, max_pos = 23, 9, 64
+    cols = (heads + 2 * kv_heads) * head_dim
+    store = (lambda t: t.to(dtype).float())
+    qkv = store(torch.randn(n, cols, generator=g))
+    pos = torch.randint(0, max_pos, (n,), generator=g)
+    ang = torch.rand(max_pos, max(rot // 2, 1), generator=g) * 6.0
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    slots = torch.randperm(n_pages * page_size, generator=g)[:n]
+    slots[3] = -1                                                  # a token that must not be written
+    q_ref = rope_reference(qkv[:, :heads * head_dim].reshape(n, heads, head_dim), pos, cos, sin, rot)
+    k_ref = rope_reference(qkv[:, heads * head_dim:(heads + kv_heads) * head_dim].reshape(n, kv_heads, head_dim),
+                           pos, cos, sin, rot)
+    v_ref = qkv[:, (heads + kv_heads) * head_dim:].reshape(n, kv_heads, head_dim)
+    tol = 1e-5 if dtype == torch.float32 else 2 ** -7 * float(qkv.abs().max())
+    dev = lambda t, dt=None: t.to(DEV if dt is None else DEV, dtype=dt) if dt else t.to(DEV)
+    i32 = lambda t: t.to(torch.int32).to(DEV)
+
+    def check(q_out, cache):
+        cache = cache.float().cpu()
+        assert float((q_out.float().cpu().reshape(n, heads, head_dim) - q_ref).abs().max()) <= tol
+        for t in range(n):
+            s = int(slots[t])
+            if s < 0:
+                continue
+            pg, off = s // page_size, s % page_size
+            assert float((cache[pg, 0, :, off] - k_ref[t]).abs().max()) <= tol
+            assert float((cache[pg, 1, :, off] - v_ref[t]).abs().max()) <= tol
+        written = {int(s) for s in slots if s >= 0}
+        for s in range(n_pages * page_size):
+            if s not in written:
+                assert float(cache[s // page_size, :, :, s % page_size].abs().max()) == 0.0
+
+    # in place on the activation buffer
+    buf = qkv.to(dtype).to(DEV)
+    cache = torch.zeros(n_pages, 2, kv_heads, page_size, head_dim, dtype=dtype, device=DEV)
+    ops.rope_kv_write(buf, heads, kv_heads, head_dim, rot, cos.to(DEV), sin.to(DEV), i32(pos), i32(slots), cache,
+                      page_size)
+    check(buf[:, :heads * head_dim], cache)
+    # from split-K partial sums: three slabs that add up to qkv
+    if dtype == torch.bfloat16:
+        ld = -(-cols // 4) * 4
+        parts = torch.randn(3, n, ld, generator=g)
+        parts[2, :, :cols] = qkv - parts[0, :, :cols] - parts[1, :, :cols]
+        partial = Partial(parts.to(DEV).contiguous(), 3, n, cols, ld, torch.device(DEV))
+        q_out = torch.zeros(n, heads * head_dim, dtype=dtype, device=DEV)
+        cache2 = torch.zeros_like(cache)
+        ops.rope_kv_write_partial(partial, q_out, heads, kv_heads, head_dim, rot, cos.to(DEV), sin.to(DEV),
+                                  i32(pos), i32(slots), cache2, page_size)
+        tol2 = tol + 2 ** -7 * float(qkv.abs().max())              # the sum is rounded once more on the way
+        q_got = q_out.float().cpu().reshape(n, heads, head_dim)
+        assert float((q_got - q_ref).abs().max()) <= tol2
+        assert float((cache2.float() - cache.float()).abs().max()) <= tol2
+
+
+@pytest.mark.parametrize("dim", [64, 70, 200, 4096, 5000])
+def test_partial_sum_consumers(dim):
+    """add+RMSNorm and SwiGLU reading split-K partial sums equal the same kernels on the summed input."""
+    from fastllm_py_b200.native import ops
+    from fastllm_py_b200.native.gemm_tc import Partial
+
+    g = torch.Generator().manual_seed(dim)
+    n, splits = 5, 4
+    ld = -(-dim // 4) * 4
+    parts = torch.randn(splits, n, ld, generator=g)
+    total = parts[:, :, :dim].sum(0)
+    partial = Partial(parts.to(DEV).contiguous(), splits, n, dim, ld, torch.device(DEV))
+    resid = torch.randn(n, dim, generator=g)
+    w = (1 + 0.1 * torch.randn(dim, generator=g)).to(torch.bfloat16)
+    out = torch.zeros(n, dim, dtype=torch.bfloat16, device=DEV)
+    r_dev = resid.clone().to(DEV)
+    ops.add_rmsnorm_partial(r_dev, partial, w.to(DEV), out, 1e-6)
+    delta = total.to(torch.bfloat16).float()
+    want_resid = resid + delta
+    want = want_resid * torch.rsqrt((want_resid ** 2).mean(-1, keepdim=True) + 1e-6) * w.float()
+    assert float((r_dev.cpu() - want_resid).abs().max()) <= 2 ** -7 * float(total.abs().max())
+    assert float((out.float().cpu() - want).abs().max()) <= 2 ** -6 * float(want.abs().max())
+    if dim % 2 == 0:
+        inter = dim // 2
+        act = torch.zeros(n, inter, dtype=torch.bfloat16, device=DEV)
+        ops.swiglu_partial(partial, act)
+        gate, up = delta[:, :inter], delta[:, inter:dim]
+        want = gate / (1 + torch.exp(-gate)) * up
+        assert float((act.float().cpu() - want).abs().max()) <= 2 ** -7 * float(want.abs().max()) + 1e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("inter", [8, 172, 11008, 77])
+def test_swiglu_kernel(dtype, inter):
+    from fastllm_py_b200.native import ops
+
+    g = torch.Generator().manual_seed(inter)
+    gu = (torch.randn(6, 2 * inter, generator=g) * 2).to(dtype)
+    out = torch.zeros(6, inter, dtype=dtype, device=DEV)
+    ops.swiglu(gu.to(DEV), out)
+    gf = gu.float()
+    want = gf[:, :inter] / (1 + torch.exp(-gf[:, :inter])) * gf[:, inter:]
+    tol = 1e-5 if dtype == torch.float32 else 2 ** -7 * float(want.abs().max())
+    assert float((out.float().cpu() - want).abs().max()) <= tol
+
+
+def test_embedding_kernel_reports_bad_ids():
+    from fastllm_py_b200.native import ops
+
+    table = torch.randn(50, 72).to(torch.bfloat16)
+    ids = torch.tensor([3, 49, 50, 0, -1], dtype=torch.int32)
+    out = torch.full((5, 72), 9.0, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.embed(table.to(DEV), ids.to(DEV), out, status)
+    got = out.cpu()
+    assert torch.equal(got[[0, 1, 3]], table.float()[[3, 49, 0]])
+    assert float(got[[2, 4]].abs().max()) == 0.0                # rows of ids outside the table are zeros
+    assert int(status.item()) in (3, 5)                        # 1 + index of a bad id
