@@ -170,3 +170,37 @@ def test_weights_stored_in_32_bit_stay_so(tmp_path):
     assert lin.weight.dtype == torch.float32
     got = replay.run_in_process(model.engine, replay.mixed(requests, live=3, seed=1))
     compare(got, ref, tol, "float32 weights under bfloat16 activations")
+
+
+def test_medium_model_reaches_the_large_shape_kernels(tmp_path):
+    """A model with head size 128, grouped heads and widths in the hundreds, so that whole prompts of
+    several hundred tokens go through the persistent tensor-core product and the tcgen05 attention,
+    decode steps through the split-K products whose partial sums the next kernel adds, in both cuts."""
+    from fastllm_py_b200.config import LlamaConfig
+    from fastllm_py_b200.weights import write_model_folder
+    from fastllm_py_b200 import Model
+
+    cfg = LlamaConfig(architecture="LlamaForCausalLM", num_layers=2, hidden_size=512, num_heads=4,
+                      num_kv_heads=2, head_dim=128, intermediate_size=1376, vocab_size=2000,
+                      rope_theta=10000.0, rope_scaling=None, rms_norm_eps=1e-6,
+                      max_position_embeddings=1024, tie_word_embeddings=False)
+    folder = write_model_folder(cfg, tmp_path / "medium", seed=3, std=0.03, norm_std=0.05)
+    rng = np.random.default_rng(12)
+    requests = {"m0": rng.integers(0, 2000, size=300).tolist(), "m1": rng.integers(0, 2000, size=70).tolist(),
+                "m2": rng.integers(0, 2000, size=520).tolist()}
+    weights, config = plain.load_folder(folder)
+    ref = {r: plain.forward(weights, config, t, store=plain.store_bf16) for r, t in requests.items()}
+    exact = {r: plain.forward(weights, config, t) for r, t in requests.items()}
+    tol = 2.0 * max(float((ref[r] - exact[r]).abs().max()) for r in ref) + 1e-3
+    model = Model.load(folder, dtype="bfloat16", page_size=16, max_tokens=2048, max_requests=4,
+                       max_batched_tokens=1024, max_model_len=1024, cuda_graph=False)
+    for cut in ("whole", "tail", "portions", "mixed"):
+        steps = CUTS[cut](requests)
+        got = replay.run_in_process(model.engine, steps)
+        compare(got, ref, tol, f"medium {cut}")
+    # the 32-bit path of the same model against the plain 32-bit logits
+    model32 = Model.load(folder, dtype="float32", page_size=16, max_tokens=2048, max_requests=4,
+                         max_batched_tokens=1024, max_model_len=1024, cuda_graph=False)
+    biggest = max(float(v.abs().max()) for v in exact.values())
+    got = replay.run_in_process(model32.engine, replay.portions(requests))
+    compare(got, exact, 1e-4 * max(1.0, biggest), "medium float32")
