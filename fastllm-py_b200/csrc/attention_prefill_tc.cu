@@ -153,8 +153,6 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
     int bt_stride, const int* __restrict__ req_start, const int* __restrict__ req_ctx,
     const int* __restrict__ req_qlen, int n_requests, int include_single, int n_heads, int n_kv_heads,
     int window, float scale_log2e, int* __restrict__ status) {
-    pdl_wait();
-    pdl_trigger();
     extern __shared__ unsigned char ft_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)ft_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = base;
@@ -479,8 +477,9 @@ FL_API int fl_attention_prefill_tc(const void* q, long q_ld, void* out, long out
     }
     const int max_tiles = n_tokens / FT_BM + n_requests;
     dim3 grid(max_tiles, n_heads);
-    return fl_launch(attention_prefill_tc_kernel, grid, dim3(FT_THREADS), (size_t)FtSmem::TOTAL, stream, map_q,
-                     map_kv, (bf16*)out, out_ld, page_size, (int)kv_rows, block_table, bt_stride, req_start, req_ctx,
-                     req_qlen, n_requests, include_single, n_heads, n_kv_heads, window,
-                     scale * 1.4426950408889634f, status);
+    // plain stream order (no programmatic overlap): this kernel takes all of an SM's tensor memory
+    attention_prefill_tc_kernel<<<grid, FT_THREADS, FtSmem::TOTAL, stream>>>(
+        map_q, map_kv, (bf16*)out, out_ld, page_size, (int)kv_rows, block_table, bt_stride, req_start, req_ctx,
+        req_qlen, n_requests, include_single, n_heads, n_kv_heads, window, scale * 1.4426950408889634f, status);
+    return fl_launch_status();
 }

@@ -518,6 +518,276 @@ static int launch_tc_persistent(const CUtensorMap& map_w, const CUtensorMap& map
                      K, tiles_n, num_tiles, status);
 }
 
+// ------------------------------------------------------------- pair variant
+// The persistent kernel again, run by PAIRS of CTAs on neighbouring SMs
+// (a cluster of two) that issue one MMA together (tcgen05 cta_group::2): a pair
+// computes a 256 x 256 tile, each CTA holding 128 of the weight rows and 128 of
+// the token rows in its shared memory and its own 128 x 256 half of the
+// accumulator in its tensor memory.  Per 64-deep K step a CTA now fetches 32 KiB
+// instead of 48 KiB for the same number of multiply-adds, which is what the
+// one-CTA kernel runs out of (operand supply from L2), and the ring is 6 deep.
+//   * both CTAs' producers load their halves; all four loads of a stage signal
+//     the LEADER's full barrier (the even CTA), which the leader arms;
+//   * the leader's MMA thread issues the MMAs and commits to BOTH CTAs' empty and
+//     accumulator-full barriers (tcgen05.commit with a CTA mask);
+//   * both CTAs' epilogue warps drain their own tensor memory and report to the
+//     leader's accumulator-empty barrier.
+// No load is multicast.  The two CTAs meet at a cluster barrier after set-up and
+// before they leave, so neither touches the other's barriers outside its life.
+#define TC2_STAGES 6
+#define TC2_STAGE_BYTES (2 * TC_BM * TC_BK * 2)             // 128 weight rows + 128 token rows
+#define TC2_TILE_BYTES (TC2_STAGES * TC2_STAGE_BYTES)
+#define TC2_SMEM (TC2_TILE_BYTES + 256 + 1024)
+#define TC2_PEER_MASK 0xFEFFFFFFu                          // clears the CTA-rank bit of a shared::cluster address
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint64_t* leader_bar, int x,
+                                                 int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+        "l"((uint64_t)map), "r"(smem_u32(leader_bar) & TC2_PEER_MASK), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {      // arrives on this barrier in both CTAs
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            smem_u32(bar)),
+        "h"((uint16_t)3)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {    // arrive on the even CTA's copy of `bar`
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & TC2_PEER_MASK) : "memory");
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
+    const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+    OutT* __restrict__ C, long ldc, int M, int N, int K, int tiles_n, int num_tiles,
+    int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full_bar = (uint64_t*)(tiles + TC2_TILE_BYTES);
+    uint64_t* empty_bar = full_bar + TC2_STAGES;
+    uint64_t* acc_full = empty_bar + TC2_STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();                   // 0: leader
+    const int pair = (int)blockIdx.x >> 1, num_pairs = (int)gridDim.x >> 1;
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const int my_tiles = (pair < num_tiles) ? (num_tiles - 1 - pair) / num_pairs + 1 : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC2_STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 8);                    // four epilogue warps in each of the two CTAs
+        }
+        *abort_flag = (*(volatile int*)status != 0) ? 1 : 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                     // both CTAs' barriers exist before anyone signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    // This kernel neither starts before its predecessor has finished nor lets its successor in early
+    // (no programmatic launch attribute, no pdl_trigger): with either, runs in which a CTA pair shared
+    // the GPU with another kernel that also allocates tensor memory stalled for good now and then.
+
+    auto tile_coords = [&](int i, int& tn, int& tm) {
+        const int tile = pair + i * num_pairs;
+        tm = tile / tiles_n;
+        tn = tile - tm * tiles_n;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer (both CTAs): this CTA's 128 weight rows and 128 token rows of each stage
+            const int total = my_tiles * num_kb;
+            const int ahead = *abort_flag ? 0 : (total < TC2_STAGES ? total : TC2_STAGES);
+            int tn, tm, ti = 0, kb = 0;
+            tile_coords(0, tn, tm);
+            for (int it = 0; it < ahead; ++it) {           // weights first: no kernel writes them
+                if (rank == 0) mbar_expect_tx(&full_bar[it], 2 * TC2_STAGE_BYTES);
+                tma_load_2d_pair(tiles + it * TC2_STAGE_BYTES, &map_w, &full_bar[it], kb * TC_BK,
+                                 tn * 256 + (int)rank * TC_BM);
+                if (++kb == num_kb) { kb = 0; tile_coords(++ti, tn, tm); }
+            }
+            pdl_wait();
+            ti = 0; kb = 0;
+            tile_coords(0, tn, tm);
+            for (int it = 0; it < ahead; ++it) {
+                tma_load_2d_pair(tiles + it * TC2_STAGE_BYTES + TC2_STAGE_BYTES / 2, &map_a, &full_bar[it],
+                                 kb * TC_BK, tm * 256 + (int)rank * TC_BM);
+                if (++kb == num_kb) { kb = 0; tile_coords(++ti, tn, tm); }
+            }
+            int s = ahead % TC2_STAGES;
+            uint32_t ph = (uint32_t)(ahead / TC2_STAGES) & 1u;
+            for (int it = ahead; it < total && !*abort_flag; ++it) {
+                if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_EMPTY_WAIT); }
+                    break;
+                }
+                unsigned char* a_dst = tiles + s * TC2_STAGE_BYTES;
+                if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * TC2_STAGE_BYTES);
+                tma_load_2d_pair(a_dst, &map_w, &full_bar[s], kb * TC_BK, tn * 256 + (int)rank * TC_BM);
+                tma_load_2d_pair(a_dst + TC2_STAGE_BYTES / 2, &map_a, &full_bar[s], kb * TC_BK,
+                                 tm * 256 + (int)rank * TC_BM);
+                if (++kb == num_kb) { kb = 0; tile_coords(++ti, tn, tm); }
+                if (++s == TC2_STAGES) { s = 0; ph ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // ---- MMA issuer (leader only): one 256 x 256 x 16 MMA per 16 columns of K, for both CTAs
+            constexpr uint32_t idesc = instr_desc_bf16(256, 256);
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = !*abort_flag;
+            for (int i = 0; i < my_tiles && ok; ++i) {
+                const int buf = i & 1;
+                const uint32_t use = (uint32_t)(i >> 1);
+                if (!mbar_wait(&acc_empty[buf], (use & 1u) ^ 1u, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_ACC_WAIT); }
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * 256);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(&full_bar[s], ph, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_FULL_WAIT); }
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + s * TC2_STAGE_BYTES);
+                    const uint64_t adesc = smem_desc_sw128(a_addr);
+                    const uint64_t bdesc = smem_desc_sw128(a_addr + TC2_STAGE_BYTES / 2);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        umma_bf16_pair(tmem_acc, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                                       (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(&empty_bar[s]);
+                    if (++s == TC2_STAGES) { s = 0; ph ^= 1u; }
+                }
+                if (ok) umma_commit_pair(&acc_full[buf]);
+            }
+        }
+    } else {
+        // ---- epilogue warps 2..5 of both CTAs: this CTA's 128 output features of the pair's tile
+        const int quarter = warp & 3;
+        bool ok = !*abort_flag;
+        pdl_wait();
+        for (int i = 0; i < my_tiles && ok; ++i) {
+            const int buf = i & 1;
+            const uint32_t use = (uint32_t)(i >> 1);
+            if (!mbar_wait(&acc_full[buf], use & 1u, abort_flag)) {
+                if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_ACC_WAIT); }
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            int tn, tm;
+            tile_coords(i, tn, tm);
+            const int o = tn * 256 + (int)rank * TC_BM + quarter * 32 + lane;
+            const int t0 = tm * 256;
+            const uint32_t t_base = tmem_base + (uint32_t)(buf * 256) + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < 256; c += 32) {
+                if (t0 + c >= M) break;
+                uint32_t r[32];
+                tmem_ld16(t_base + (uint32_t)c, r);
+                tmem_ld16(t_base + (uint32_t)c + 16u, r + 16);
+                tmem_ld_wait();
+                if (o < N) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int t = t0 + c + j;
+                        if (t < M) C[(long)t * ldc + o] = from_f32<OutT>(__uint_as_float(r[j]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(&acc_empty[buf]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                     // the peer is done with this CTA's barriers and memory
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+    // Neither CTA leaves before both have given their tensor memory back.  Without this barrier a CTA of the
+    // next kernel could take the SM of the CTA that left first and allocate tensor memory there while the
+    // peer's paired deallocation was still to come; such runs stalled for good now and then.
+    cluster_sync_all();
+}
+
+template <typename OutT>
+static int launch_tc_pair(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C, long ldc, int M, int N,
+                          int K, int num_sms, int* status, cudaStream_t stream) {
+    static bool configured = false;
+    auto kernel = gemm_tc_pair_kernel<OutT>;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC2_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int tiles_n = (N + 255) / 256;
+    const int num_tiles = tiles_n * ((M + 255) / 256);
+    const int pairs = num_tiles < num_sms / 2 ? num_tiles : num_sms / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = TC2_SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    // Launched in plain stream order (no programmatic overlap with its neighbours): see the note in the kernel.
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, map_w, map_a, (OutT*)C, ldc, M, N, K, tiles_n, num_tiles, status);
+}
+
 // C[t, o] = sum over splits of partial[z][t][o], added in the order z = 0, 1, ...
 template <typename OutT>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, long ld_partial, int splits,
@@ -599,6 +869,8 @@ static int dispatch_tc(int bn, const CUtensorMap& map_w, const CUtensorMap& map_
 
 // Token-tile width and K splits for a problem: the smallest tile that holds the
 // tokens (up to 256), and as many splits as it takes to give every SM a CTA or two.
+// Products of more than 128 tokens that need no split go to the CTA-pair kernel,
+// reported as width 512.
 FL_API void fl_gemm_tc_plan(int M, int N, int K, int num_sms, int* bn_out, int* splits_out) {
     int bn = 16;
     while (bn < 256 && bn < M) bn *= 2;
@@ -618,6 +890,7 @@ FL_API void fl_gemm_tc_plan(int M, int N, int K, int num_sms, int* bn_out, int* 
     }
     const int per = (num_kb + splits - 1) / splits;
     splits = (num_kb + per - 1) / per;                          // no empty split
+    if (bn == 256 && splits == 1 && num_sms >= 2) bn = 512;     // 512 stands for the CTA-pair kernel (256 x 256 tiles)
     *bn_out = bn;
     *splits_out = splits;
 }
@@ -640,12 +913,19 @@ static int gemm_tc_impl(const void* A, long lda, const void* W, long ldw, void* 
     const long ld_partial = ((long)N + 3) / 4 * 4;
     if (splits > 1 && (workspace == nullptr || workspace_floats < (long)splits * M * ld_partial))
         return (int)cudaErrorMemoryAllocation;
-    if ((M + bn - 1) / bn > 65535) return (int)cudaErrorInvalidValue;
+    if (bn <= 256 && (M + bn - 1) / bn > 65535) return (int)cudaErrorInvalidValue;
     CUtensorMap map_w, map_a;
     int rc = make_map(&map_w, W, N, K, ldw, TC_BM);
     if (rc) return rc;
-    rc = make_map(&map_a, A, M, K, lda, bn);
+    rc = make_map(&map_a, A, M, K, lda, bn > 256 ? TC_BM : bn);
     if (rc) return rc;
+    if (bn == 512 && splits == 1 && num_sms >= 2) {          // the pair kernel: both operands in 128-row boxes
+        rc = make_map(&map_a, A, M, K, lda, TC_BM);
+        if (rc) return rc;
+        if (c_dtype == FL_BF16) return launch_tc_pair<bf16>(map_w, map_a, C, ldc, M, N, K, num_sms, status, stream);
+        if (c_dtype == FL_F32) return launch_tc_pair<float>(map_w, map_a, C, ldc, M, N, K, num_sms, status, stream);
+        return (int)cudaErrorInvalidValue;
+    }
     if (bn == TCP_BN && splits == 1 && num_sms > 0) {
         if (c_dtype == FL_BF16) return launch_tc_persistent<bf16>(map_w, map_a, C, ldc, M, N, K, num_sms, status, stream);
         if (c_dtype == FL_F32) return launch_tc_persistent<float>(map_w, map_a, C, ldc, M, N, K, num_sms, status, stream);

@@ -403,3 +403,27 @@ def test_embedding_kernel_reports_bad_ids():
     assert torch.equal(got[[0, 1, 3]], table.float()[[3, 49, 0]])
     assert float(got[[2, 4]].abs().max()) == 0.0                # rows of ids outside the table are zeros
     assert int(status.item()) in (3, 5)                        # 1 + index of a bad id
+
+
+@pytest.mark.parametrize("m, n, k", [(256, 256, 64), (300, 515, 200), (1024, 768, 1032), (257, 130, 72), (2048, 1024, 512)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_tensor_core_gemm_cta_pairs(m, n, k, out_dtype):
+    """The kernel in which two CTAs issue one 256 x 256 MMA together (cta_group::2), forced."""
+    from fastllm_py_b200.native import gemm_tc
+
+    g = torch.Generator(device="cpu").manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = torch.randn(n, k, generator=g).to(torch.bfloat16)
+    ref = a.float() @ w.float().t()
+    pitch = -(-k // 8) * 8
+    a_dev = torch.zeros(m, pitch, dtype=torch.bfloat16, device=DEV)
+    a_dev[:, :k] = a.to(DEV)
+    lin = gemm_tc.TensorCoreLinear(w.to(DEV))
+    out = torch.full((m, n + 3), -5.0, dtype=out_dtype, device=DEV)
+    gemm_tc.gemm(a_dev[:, :k], lin.weight, out[:, :n], bn=512, splits=1)
+    torch.cuda.synchronize()
+    assert int(gemm_tc.status_word(torch.device(DEV)).item()) == 0
+    assert torch.all(out[:, n:] == -5.0), "wrote outside the output columns"
+    got = out[:, :n].float().cpu()
+    tol = 1e-3 * math.sqrt(k) if out_dtype == torch.float32 else 2 ** -8 * float(ref.abs().max()) + 1e-3
+    assert float((got - ref).abs().max()) <= tol
