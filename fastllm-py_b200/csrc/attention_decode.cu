@@ -80,6 +80,63 @@ __device__ __forceinline__ float weight_of(float a, float b) {
 // workspace rows: [HEAD_DIM values | maximum | sum], one row per (token index, head, split)
 #define ATD_ROW (HEAD_DIM + 2)
 
+// out[:] = sum_s values_s * 2^(m_s - M) / sum_s sum_s * 2^(m_s - M) over the splits s_lo..s_hi of one
+// (token, head), by one CTA.  Splits are taken ATD_WARPS * 32 at a time with a running maximum, in
+// ascending order; the first values of a chunk are requested together with its maxima and sums, so
+// that the usual case (a few splits) is one memory round trip.
+#define ATD_MERGE_AHEAD 8
+#define ATD_MERGE_DPT ((HEAD_DIM + ATD_WARPS * 32 - 1) / (ATD_WARPS * 32))
+__device__ __forceinline__ void merge_splits(const float* __restrict__ rows, int s_lo, int s_hi,
+                                             bf16* __restrict__ dst) {
+    constexpr int NT = ATD_WARPS * 32;
+    __shared__ float s_w[NT];
+    __shared__ float scratch[32];
+    const int tid = threadIdx.x;
+    float M = -CUDART_INF_F, L = 0.0f, acc[ATD_MERGE_DPT];
+#pragma unroll
+    for (int k = 0; k < ATD_MERGE_DPT; ++k) acc[k] = 0.0f;
+#pragma unroll 1
+    for (int s0 = s_lo; s0 <= s_hi; s0 += NT) {
+        const int cnt = min(NT, s_hi - s0 + 1);
+        float m_s = -CUDART_INF_F, l_s = 0.0f;
+        if (tid < cnt) {
+            m_s = __ldcg(rows + (long)(s0 + tid) * ATD_ROW + HEAD_DIM);
+            l_s = __ldcg(rows + (long)(s0 + tid) * ATD_ROW + HEAD_DIM + 1);
+        }
+        float ahead[ATD_MERGE_DPT][ATD_MERGE_AHEAD];
+#pragma unroll
+        for (int k = 0; k < ATD_MERGE_DPT; ++k) {
+            const int d = tid + k * NT;
+#pragma unroll
+            for (int j = 0; j < ATD_MERGE_AHEAD; ++j)
+                ahead[k][j] = (j < cnt && d < HEAD_DIM) ? __ldcg(rows + (long)(s0 + j) * ATD_ROW + d) : 0.0f;
+        }
+        const float new_m = fmaxf(M, block_max(m_s, scratch));
+        s_w[tid] = weight_of(m_s, new_m);
+        const float chunk_l = block_sum(l_s * s_w[tid], scratch);           // its barriers publish s_w
+        const float corr = weight_of(M, new_m);
+        L = L * corr + chunk_l;
+#pragma unroll
+        for (int k = 0; k < ATD_MERGE_DPT; ++k) {
+            const int d = tid + k * NT;
+            float a = acc[k] * corr;
+#pragma unroll
+            for (int j = 0; j < ATD_MERGE_AHEAD; ++j) a += ahead[k][j] * (j < cnt ? s_w[j] : 0.0f);
+            if (d < HEAD_DIM)
+                for (int j = ATD_MERGE_AHEAD; j < cnt; ++j) a += __ldcg(rows + (long)(s0 + j) * ATD_ROW + d) * s_w[j];
+            acc[k] = a;
+        }
+        M = new_m;
+        __syncthreads();                                                    // s_w is rewritten by the next chunk
+    }
+    const float inv = 1.0f / L;
+#pragma unroll
+    for (int k = 0; k < ATD_MERGE_DPT; ++k) {
+        const int d = tid + k * NT;
+        if (d < HEAD_DIM) dst[d] = __float2bfloat16_rn(acc[k] * inv);
+    }
+}
+
 __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_kernel(
     const bf16* __restrict__ q, long q_ld, bf16* __restrict__ out, long out_ld,
     const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, long page_stride, int page_size,
@@ -230,31 +287,18 @@ __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_kernel(
     }
 }
 
-// out[t, h, :] = sum_s values_s * 2^(m_s - M) / sum_s sum_s * 2^(m_s - M) over the splits the token sees
-__global__ void attention_decode_merge_kernel(const float* __restrict__ partial, bf16* __restrict__ out,
-                                              long out_ld, const int* __restrict__ positions,
-                                              const int* __restrict__ tok_list, int n_heads, int window,
-                                              int n_splits) {
+// The merge kernel: one CTA per (token, head).
+__global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_merge_kernel(
+    const float* __restrict__ partial, bf16* __restrict__ out, long out_ld, const int* __restrict__ positions,
+    const int* __restrict__ tok_list, int n_heads, int window, int n_splits) {
     pdl_wait();
     pdl_trigger();
     const int li = blockIdx.x, h = blockIdx.y;
     const int t = tok_list ? tok_list[li] : li;
     const int pos = positions[t];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int s_lo = lo / ATD_SPLIT, s_hi = pos / ATD_SPLIT;
-    const float* rows = partial + ((long)li * n_heads + h) * n_splits * ATD_ROW;
-    float mm = -CUDART_INF_F;
-    for (int s = s_lo; s <= s_hi; ++s) mm = fmaxf(mm, rows[(long)s * ATD_ROW + HEAD_DIM]);
-    float ll = 0.0f;
-    for (int s = s_lo; s <= s_hi; ++s)
-        ll += rows[(long)s * ATD_ROW + HEAD_DIM + 1] * weight_of(rows[(long)s * ATD_ROW + HEAD_DIM], mm);
-    const float inv = 1.0f / ll;
-    for (int d = threadIdx.x; d < HEAD_DIM; d += blockDim.x) {
-        float acc = 0.0f;
-        for (int s = s_lo; s <= s_hi; ++s)
-            acc += rows[(long)s * ATD_ROW + d] * weight_of(rows[(long)s * ATD_ROW + HEAD_DIM], mm);
-        out[(long)t * out_ld + (long)h * HEAD_DIM + d] = __float2bfloat16_rn(acc * inv);
-    }
+    merge_splits(partial + ((long)li * n_heads + h) * n_splits * ATD_ROW, lo / ATD_SPLIT, pos / ATD_SPLIT,
+                 out + (long)t * out_ld + (long)h * HEAD_DIM);
 }
 
 FL_API int fl_attention_decode_head_dim() { return HEAD_DIM; }
@@ -289,6 +333,6 @@ FL_API int fl_attention_decode(const void* q, long q_ld, void* out, long out_ld,
                        window, scale * 1.4426950408889634f, n_splits, partial);
     if (rc || n_splits == 1) return rc;
     dim3 mgrid(n_list, n_heads);
-    return fl_launch(attention_decode_merge_kernel, mgrid, dim3(128), 0, stream, (const float*)partial,
+    return fl_launch(attention_decode_merge_kernel, mgrid, dim3(ATD_WARPS * 32), 0, stream, (const float*)partial,
                      (bf16*)out, out_ld, positions, tok_list, n_heads, window, n_splits);
 }

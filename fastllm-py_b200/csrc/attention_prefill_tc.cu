@@ -9,8 +9,8 @@
 // how the prompt was cut).  Per block:
 //   producer warp   TMA: the block's pages of this head's keys and values into a
 //                   two-stage ring (one box of page_size x 64 per page and 64
-//                   columns; pages that do not exist are fetched from beyond the
-//                   tensor, which fills zeros);
+//                   columns, each issued by a lane of its own; pages that do not
+//                   exist are fetched from beyond the tensor, which fills zeros);
 //   MMA warp        S = Q K^T into one of two S buffers in tensor memory (so the
 //                   next block's scores are computed while this block's are
 //                   being exponentiated), then O_blk = P V;
@@ -42,6 +42,7 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "the tcgen05 prefill kernel tak
 #define FT_STAGES 2
 #define FT_THREADS 320                     // 8 softmax warps (two threads per query row), producer warp, MMA warp
 #define FT_SOFTMAX_THREADS 256
+#define FT_SOFTMAX_WARPS (FT_SOFTMAX_THREADS / 32)
 #define FT_ATOMS (HEAD_DIM / 64)           // 64-column swizzle atoms per row
 #define FT_ATOM_BYTES (128 * 128)          // 128 rows x 128 bytes
 #define FT_WAIT_LIMIT_NS 2000000000ull
@@ -82,6 +83,18 @@ __device__ __forceinline__ bool ft_wait(uint64_t* bar, uint32_t parity, volatile
             else if (ft_now() - t0 > FT_WAIT_LIMIT_NS) return false;
         }
     }
+}
+// A warp waits through its first lane and arrives through it (after __syncwarp, which orders
+// the other lanes' writes before the arrival): a barrier then sees 8 arrivals per phase from the
+// softmax warps instead of 256, and one thread polls instead of 32.
+__device__ __forceinline__ bool ft_warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    uint32_t ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = ft_wait(bar, parity, abort_flag) ? 1u : 0u;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+__device__ __forceinline__ void ft_warp_arrive(uint64_t* bar) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) ft_bar_arrive(bar);
 }
 __device__ __forceinline__ void ft_tma_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
     asm volatile(
@@ -136,6 +149,12 @@ __host__ __device__ constexpr uint32_t ft_idesc(int m, int n, int b_mn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) |
            ((uint32_t)(m >> 4) << 24);
 }
+// 2^x by the special-function unit (relative error about 2^-22; -inf gives 0)
+__device__ __forceinline__ float ft_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ float ft_weight(float a, float b) { return (a == -CUDART_INF_F) ? 0.0f : exp2f(a - b); }
 
 struct FtSmem {
@@ -143,7 +162,7 @@ struct FtSmem {
     static constexpr int KV_BYTES = FT_ATOMS * FT_ATOM_BYTES;          // one of K or V, one stage
     static constexpr int P_BYTES = 2 * FT_ATOM_BYTES;                  // 128 rows x 128 keys
     static constexpr int TILES = Q_BYTES + 2 * FT_STAGES * KV_BYTES + P_BYTES;
-    static constexpr int BARS = 16 * 8 + 16 + 2 * 128 * 4;             // barriers, then the half-row maxima
+    static constexpr int BARS = 16 * 8 + 16 + 4 * 128 * 4;             // barriers, then the half-row maxima (two rounds)
     static constexpr int TOTAL = TILES + BARS + 1024;
 };
 
@@ -166,26 +185,25 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
     uint64_t* s_full = bars + 5;                                       // [2]
     uint64_t* s_empty = bars + 7;                                      // [2]
     uint64_t* p_full = bars + 9;
-    uint64_t* p_empty = bars + 10;
     uint64_t* o_full = bars + 11;
     uint64_t* o_empty = bars + 12;
     uint32_t* tmem_slot = (uint32_t*)(bars + 13);
     uint64_t* x_bar = bars + 14;                                       // the softmax threads' exchange point
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
-    // which request and which 128-row tile (heaviest first)
+    // which request and which 128-row tile: blockIdx.y counts tiles, a request's last (longest) tile first
     int req = -1, tile = 0;
     {
         int acc = 0;
         for (int r = 0; r < n_requests; ++r) {
             const int ql = req_qlen[r];
             const int nt = (ql > 1 || include_single) ? (ql + FT_BM - 1) / FT_BM : 0;
-            if ((int)blockIdx.x < acc + nt) { req = r; tile = nt - 1 - ((int)blockIdx.x - acc); break; }
+            if ((int)blockIdx.y < acc + nt) { req = r; tile = nt - 1 - ((int)blockIdx.y - acc); break; }
             acc += nt;
         }
     }
     if (req < 0) return;
-    const int h = blockIdx.y;
+    const int h = blockIdx.x;
     const int kvh = h / (n_heads / n_kv_heads);
     const int q_len = req_qlen[req], ctx = req_ctx[req], row0 = tile * FT_BM;
     const int tok0 = req_start[req] + row0;
@@ -202,13 +220,12 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
             ft_bar_init(&kv_full[s], 1);
             ft_bar_init(&kv_empty[s], 1);
             ft_bar_init(&s_full[s], 1);
-            ft_bar_init(&s_empty[s], FT_SOFTMAX_THREADS);
+            ft_bar_init(&s_empty[s], FT_SOFTMAX_WARPS);
         }
-        ft_bar_init(p_full, FT_SOFTMAX_THREADS);
-        ft_bar_init(p_empty, 1);
+        ft_bar_init(p_full, FT_SOFTMAX_WARPS);
         ft_bar_init(o_full, 1);
-        ft_bar_init(o_empty, FT_SOFTMAX_THREADS);
-        ft_bar_init(x_bar, FT_SOFTMAX_THREADS);
+        ft_bar_init(o_empty, FT_SOFTMAX_WARPS);
+        ft_bar_init(x_bar, FT_SOFTMAX_WARPS);
         *abort_flag = (*(volatile int*)status != 0) ? 1 : 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -233,33 +250,35 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
     }
 
     if (warp == 8) {
-        if (lane == 0 && !*abort_flag) {
-            // ---- producer
-            ft_bar_expect(q_full, FtSmem::Q_BYTES);
-            for (int a = 0; a < FT_ATOMS; ++a)
-                ft_tma_2d(q_s + a * FT_ATOM_BYTES, &map_q, q_full, h * HEAD_DIM + a * 64, tok0);
+        if (!*abort_flag) {
+            // ---- producer: the whole warp.  A block of 128 keys is pages x atoms x {K, V} boxes of
+            // a few KB; one lane issues one box (looking up its page itself), so the 32 copies of a
+            // block leave together instead of one thread walking through them.
+            if (lane == 0) {
+                ft_bar_expect(q_full, FtSmem::Q_BYTES);
+                for (int a = 0; a < FT_ATOMS; ++a)
+                    ft_tma_2d(q_s + a * FT_ATOM_BYTES, &map_q, q_full, h * HEAD_DIM + a * 64, tok0);
+            }
             const int* bt = block_table + (long)req * bt_stride;
-            const int pages_per_block = FT_BN / page_size;
+            const int n_ops = (FT_BN / page_size) * FT_ATOMS * 2;
             for (int i = 0; i < n_blocks; ++i) {
                 const int s = i & 1;
-                if (!ft_wait(&kv_empty[s], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag)) FT_GIVE_UP();
-                ft_bar_expect(&kv_full[s], 2 * FtSmem::KV_BYTES);
+                if (!ft_warp_wait(&kv_empty[s], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag)) FT_GIVE_UP();
+                if (lane == 0) ft_bar_expect(&kv_full[s], 2 * FtSmem::KV_BYTES);
+                __syncwarp();
                 const int key0 = (kb_begin + i) * FT_BN;
-                for (int p = 0; p < pages_per_block; ++p) {
+                for (int op = lane; op < n_ops; op += 32) {
+                    const int p = op / (FT_ATOMS * 2), a = (op >> 1) % FT_ATOMS, is_v = op & 1;
                     const int first_key = key0 + p * page_size;
                     const int last_key = first_key + page_size - 1;
                     // a page wholly outside what this tile may see is fetched from beyond the tensor: zeros
-                    int row_k = kv_rows_total, row_v = kv_rows_total;
+                    int row = kv_rows_total;
                     if (first_key <= pos_last && last_key >= lo_tile) {
                         const long pg = bt[first_key / page_size];
-                        row_k = (int)(((pg * 2 + 0) * n_kv_heads + kvh) * page_size);
-                        row_v = (int)(((pg * 2 + 1) * n_kv_heads + kvh) * page_size);
+                        row = (int)(((pg * 2 + is_v) * n_kv_heads + kvh) * page_size);
                     }
-                    for (int a = 0; a < FT_ATOMS; ++a) {
-                        const int off = s * FtSmem::KV_BYTES + a * FT_ATOM_BYTES + p * page_size * 128;
-                        ft_tma_2d(k_s + off, &map_kv, &kv_full[s], a * 64, row_k);
-                        ft_tma_2d(v_s + off, &map_kv, &kv_full[s], a * 64, row_v);
-                    }
+                    const int off = s * FtSmem::KV_BYTES + a * FT_ATOM_BYTES + p * page_size * 128;
+                    ft_tma_2d((is_v ? v_s : k_s) + off, &map_kv, &kv_full[s], a * 64, row);
                 }
             }
         }
@@ -299,8 +318,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
                            idesc_o, k > 0 ? 1u : 0u);
                 }
                 ft_commit(&kv_empty[i & 1]);
-                ft_commit(p_empty);
-                ft_commit(o_full);
+                ft_commit(o_full);                  // O_blk(i) is ready; P's memory is free again
             }
             if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, FT_ERR_WAIT); }
         }
@@ -311,16 +329,36 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
         const int half = threadIdx.x >> 7;
         const int pos_r = ctx + row0 + r;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-        float* half_max = reinterpret_cast<float*>(bars + 16);            // [2][128]
+        // [round parity][half][row]: a round's values stay untouched while the next round's are written
+        float* half_max_all = reinterpret_cast<float*>(bars + 16);
         constexpr int OD = HEAD_DIM / 2;                                 // output columns per thread
         float m_run = -CUDART_INF_F, l_run = 0.0f;
         float o_reg[OD];
 #pragma unroll
         for (int d = 0; d < OD; ++d) o_reg[d] = 0.0f;
         bool ok = !*abort_flag;
+        // Block i's exponentials are computed while the tensor core still works on P V of block
+        // i - 1; that product is collected (and its shared-memory P released) only then, so the
+        // correction it needs is the one of the round before: out = out * corr(i - 1) + O_blk(i - 1).
+        float corr_prev = 0.0f;
+        auto collect = [&](int i_done, float corr_of) -> bool {          // adds O_blk(i_done) into the row
+            if (!ft_warp_wait(o_full, (uint32_t)i_done & 1u, abort_flag)) return false;
+            ft_fence_after();
+#pragma unroll
+            for (int c = 0; c < OD; c += 32) {
+                uint32_t w[32];
+                ft_ld32(tmem_o + lane_base + (uint32_t)(half * OD + c), w);
+                ft_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o_reg[c + j] = fmaf(o_reg[c + j], corr_of, __uint_as_float(w[j]));
+            }
+            ft_fence_before();
+            ft_warp_arrive(o_empty);
+            return true;
+        };
         for (int i = 0; i < n_blocks && ok; ++i) {
             const int sb = i & 1;
-            if (!ft_wait(&s_full[sb], (uint32_t)(i >> 1) & 1u, abort_flag)) FT_GIVE_UP();
+            if (!ft_warp_wait(&s_full[sb], (uint32_t)(i >> 1) & 1u, abort_flag)) FT_GIVE_UP();
             ft_fence_after();
             const int key0 = (kb_begin + i) * FT_BN + half * 64;         // first key of this thread's half
             const uint32_t s_addr = tmem_s + (uint32_t)(sb * FT_BN + half * 64) + lane_base;
@@ -329,6 +367,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
             ft_ld32(s_addr, v);
             ft_ld32(s_addr + 32u, v + 32);
             ft_ld_wait();
+            ft_fence_before();
+            ft_warp_arrive(&s_empty[sb]);                                  // S(i) is in registers
             if (!all_seen) {
 #pragma unroll
                 for (int j = 0; j < 64; ++j) {
@@ -343,55 +383,47 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
                 for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], __uint_as_float(v[j + e]));
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            // exchange the half-row maxima (one barrier among the softmax threads per block)
+            // exchange the half-row maxima (one barrier among the softmax warps per block)
+            float* half_max = half_max_all + (i & 1) * 256;
             half_max[half * 128 + r] = mx;
-            ft_bar_arrive(x_bar);                                         // (an mbarrier: its wait can give up)
-            if (!ft_wait(x_bar, (uint32_t)i & 1u, abort_flag)) FT_GIVE_UP();
+            ft_warp_arrive(x_bar);                                        // (an mbarrier: its wait can give up)
+            if (!ft_warp_wait(x_bar, (uint32_t)i & 1u, abort_flag)) FT_GIVE_UP();
             const float mx_row = fmaxf(mx, half_max[(half ^ 1) * 128 + r]);
             const float m_new = fmaxf(m_run, mx_row * scale_log2e);
             const float corr = ft_weight(m_run, m_new);
             const float neg_m = (m_new == -CUDART_INF_F) ? 0.0f : -m_new;      // an empty row: every p below is 0
-            if (!ft_wait(p_empty, ((uint32_t)i & 1u) ^ 1u, abort_flag)) FT_GIVE_UP();
             float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            unsigned char* row_base = p_s + half * FT_ATOM_BYTES + r * 128;
+            uint32_t packed[32];
 #pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8) {                               // 8 keys = one 16-byte chunk
-                uint32_t packed[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = exp2f(fmaf(__uint_as_float(v[c8 * 8 + 2 * e]), scale_log2e, neg_m));
-                    const float p1 = exp2f(fmaf(__uint_as_float(v[c8 * 8 + 2 * e + 1]), scale_log2e, neg_m));
-                    l4[e] += p0 + p1;
-                    const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-                    packed[e] = *reinterpret_cast<const uint32_t*>(&b);
-                }
-                *reinterpret_cast<uint4*>(row_base + ((c8 ^ (r & 7)) << 4)) =
-                    make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            for (int c = 0; c < 32; ++c) {
+                const float p0 = ft_ex2(fmaf(__uint_as_float(v[2 * c]), scale_log2e, neg_m));
+                const float p1 = ft_ex2(fmaf(__uint_as_float(v[2 * c + 1]), scale_log2e, neg_m));
+                l4[c & 3] += p0 + p1;
+                const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+                packed[c] = *reinterpret_cast<const uint32_t*>(&b);
             }
             l_run = l_run * corr + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
             m_run = m_new;
-            ft_fence_before();
+            // P V of the block before is complete by now or soon: take it out, which also frees P's memory
+            if (i > 0 && !collect(i - 1, corr_prev)) FT_GIVE_UP();
+            corr_prev = corr;
+            unsigned char* row_base = p_s + half * FT_ATOM_BYTES + r * 128;
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8)                                 // 8 keys = one 16-byte chunk
+                *reinterpret_cast<uint4*>(row_base + ((c8 ^ (r & 7)) << 4)) =
+                    make_uint4(packed[4 * c8], packed[4 * c8 + 1], packed[4 * c8 + 2], packed[4 * c8 + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
-            ft_bar_arrive(p_full);
-            ft_bar_arrive(&s_empty[sb]);
-            // the block's P V: this thread's half of the columns, added into its part of the row
-            if (!ft_wait(o_full, (uint32_t)i & 1u, abort_flag)) FT_GIVE_UP();
-            ft_fence_after();
-#pragma unroll
-            for (int c = 0; c < OD; c += 32) {
-                uint32_t w[32];
-                ft_ld32(tmem_o + lane_base + (uint32_t)(half * OD + c), w);
-                ft_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) o_reg[c + j] = fmaf(o_reg[c + j], corr, __uint_as_float(w[j]));
-            }
-            ft_fence_before();
-            ft_bar_arrive(o_empty);
+            ft_warp_arrive(p_full);
+        }
+        if (ok && n_blocks > 0 && !collect(n_blocks - 1, corr_prev)) {
+            ok = false;
+            if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, FT_ERR_WAIT); }
         }
         // the row's sum is the two halves' sums (both are relative to the same maximum)
+        float* half_max = half_max_all + (n_blocks & 1) * 256;
         half_max[half * 128 + r] = l_run;
-        ft_bar_arrive(x_bar);
-        const bool met = ft_wait(x_bar, (uint32_t)n_blocks & 1u, abort_flag);
+        ft_warp_arrive(x_bar);
+        const bool met = ft_warp_wait(x_bar, (uint32_t)n_blocks & 1u, abort_flag);
         const float l_row = l_run + half_max[(half ^ 1) * 128 + r];
         if (met && ok && !*abort_flag && r < rows_here) {
             const float inv = 1.0f / l_row;
@@ -476,7 +508,8 @@ FL_API int fl_attention_prefill_tc(const void* q, long q_ld, void* out, long out
         configured = true;
     }
     const int max_tiles = n_tokens / FT_BM + n_requests;
-    dim3 grid(max_tiles, n_heads);
+    if (max_tiles > 65535) return (int)cudaErrorInvalidValue;
+    dim3 grid(n_heads, max_tiles);                 // heads fastest: every head's late (long) tiles start first
     // plain stream order (no programmatic overlap): this kernel takes all of an SM's tensor memory
     attention_prefill_tc_kernel<<<grid, FT_THREADS, FtSmem::TOTAL, stream>>>(
         map_q, map_kv, (bf16*)out, out_ld, page_size, (int)kv_rows, block_table, bt_stride, req_start, req_ctx,

@@ -288,11 +288,74 @@ __global__ void add_rmsnorm_partial_kernel(float* __restrict__ resid, long resid
         o[i] = from_f32<TO>(xr[i] * inv * to_f32<TW>(w[i]));
 }
 
+// The same for rows made of 4-element chunks (dim and every pitch a multiple of
+// 4, 16-byte aligned bases) of at most ARP_KEEP chunks per thread.  A decode
+// step has a handful of rows, so this kernel is one CTA per row and its time is
+// the length of its chain of dependent memory round trips: every load (all slabs,
+// the residual, the norm weight) is issued before the first use, the row stays
+// in registers across the reduction, and nothing is read a second time.
+#define ARP_KEEP 2
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(1024) add_rmsnorm_partial_vec_kernel(
+    float* __restrict__ resid, long resid_ld, const float* __restrict__ partial, int splits, long split_stride,
+    long ld, const TW* __restrict__ w, TO* __restrict__ out, long out_ld, int dim, float eps) {
+    pdl_wait();
+    pdl_trigger();
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    float* xr = resid + (long)r * resid_ld;
+    const float* pr = partial + (long)r * ld;
+    TO* o = out + (long)r * out_ld;
+    float4 keep[ARP_KEEP], gain[ARP_KEEP];
+    float ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < ARP_KEEP; ++c) {
+        const int i = (threadIdx.x + c * blockDim.x) * 4;
+        if (i < dim) {
+            float4 v = *reinterpret_cast<const float4*>(xr + i);
+            load4(w + i, gain[c]);
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 8
+            for (int z = 0; z < splits; ++z) {
+                const float4 p = *reinterpret_cast<const float4*>(pr + i + (long)z * split_stride);
+                acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+            }
+            // the sum is rounded to the activation type first, as the separate reduction stores it
+            v.x += to_f32<TO>(from_f32<TO>(acc.x));
+            v.y += to_f32<TO>(from_f32<TO>(acc.y));
+            v.z += to_f32<TO>(from_f32<TO>(acc.z));
+            v.w += to_f32<TO>(from_f32<TO>(acc.w));
+            *reinterpret_cast<float4*>(xr + i) = v;
+            keep[c] = v;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+#pragma unroll
+    for (int c = 0; c < ARP_KEEP; ++c) {
+        const int i = (threadIdx.x + c * blockDim.x) * 4;
+        if (i < dim)
+            store4(o + i, make_float4(keep[c].x * inv * gain[c].x, keep[c].y * inv * gain[c].y,
+                                      keep[c].z * inv * gain[c].z, keep[c].w * inv * gain[c].w));
+    }
+}
+
 FL_API int fl_add_rmsnorm_partial(float* resid, long resid_ld, const float* partial, int splits,
                                   long split_stride, long ld, const void* w, int w_dtype, void* out,
                                   int out_dtype, long out_ld, int n_rows, int dim, float eps,
                                   cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    const bool vec = vec4_ok(dim, resid, resid_ld, 4) && vec4_ok(dim, partial, ld, 4) && split_stride % 4 == 0 &&
+                     vec4_ok(dim, w, 4, w_dtype == FL_F32 ? 4 : 2) &&
+                     vec4_ok(dim, out, out_ld, out_dtype == FL_F32 ? 4 : 2) && dim <= ARP_KEEP * 4 * 1024;
+    if (vec) {
+        const int vthreads = dim / 4 <= 1024 ? (dim / 4 + 31) / 32 * 32 : 1024;  // one chunk per thread when that fits
+        FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,
+            return fl_launch(add_rmsnorm_partial_vec_kernel<TW, TO>, dim3(n_rows), dim3(vthreads), 0, stream,
+                             resid, resid_ld, partial, splits, split_stride, ld, (const TW*)w, (TO*)out, out_ld,
+                             dim, eps)));
+    }
     const int threads = norm_threads(dim, false);
     FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,
         return fl_launch(add_rmsnorm_partial_kernel<TW, TO>, dim3(n_rows), dim3(threads), 0, stream, resid,
