@@ -287,6 +287,289 @@ __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_kernel(
     }
 }
 
+// ------------------------------------------------- the tensor-core form
+// The same split, but the arithmetic is mma.sync (m16n8k16): the 16 rows of the
+// tile are the query heads that share one key/value head (a group of up to 16;
+// one real row with plain multi-head attention), so a group's keys and values
+// are read once for all its heads, and the dot products, their reductions and
+// the weighted sum of the values cost a few dozen warp instructions per 16 keys
+// instead of several hundred.  What is left is the stream of the cache: every
+// warp owns ATD_KEYS_PER_WARP consecutive keys of the split and brings them in
+// 16 at a time with cp.async through a ring of its own in shared memory (two
+// lanes per key row, one page lookup each), so there is no CTA-wide barrier in
+// the loop.  Scores, maxima and sums are float; P is rounded to bfloat16 as the
+// operand of P V, as in the prompt kernels.  Rows go to the same workspace
+// layout as the kernel above writes, and the same merge follows.
+#ifndef ATM_CHUNK
+#define ATM_CHUNK 16                        // keys per ring stage (a multiple of 16)
+#endif
+#ifndef ATM_STAGES
+#define ATM_STAGES 2
+#endif
+#define ATM_DP (HEAD_DIM + 8)               // padded row pitch: ldmatrix without bank conflicts
+#define ATM_STAGE_ELEMS (ATM_CHUNK * ATM_DP)
+#define ATM_WARP_ELEMS (2 * ATM_STAGES * ATM_STAGE_ELEMS)     // K and V stages of one warp
+#define ATM_MAX_GROUP 16
+
+__device__ __forceinline__ uint32_t atm_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void atm_cp16(void* dst, const void* src, bool real) {
+    const int bytes = real ? 16 : 0;                       // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(atm_smem(dst)), "l"(src), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void atm_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void atm_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void atm_ldmatrix(uint32_t* r, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(atm_smem(p)));
+}
+__device__ __forceinline__ void atm_ldmatrix_trans(uint32_t* r, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(atm_smem(p)));
+}
+__device__ __forceinline__ void atm_mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t atm_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// grid: (tokens of the list, key/value heads, splits)
+__global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_mma_kernel(
+    const bf16* __restrict__ q, long q_ld, bf16* __restrict__ out, long out_ld,
+    const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, long page_stride, int page_size,
+    int page_shift, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req,
+    const int* __restrict__ positions, const int* __restrict__ tok_list, int n_heads, int n_kv_heads,
+    int window, float scale_log2e, int n_splits, float* __restrict__ partial) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ __align__(16) unsigned char atm_raw[];
+    const int li = blockIdx.x;
+    const int t = tok_list ? tok_list[li] : li;
+    const int kvh = blockIdx.y, split = blockIdx.z;
+    const int group = n_heads / n_kv_heads;                 // query heads per key/value head (<= ATM_MAX_GROUP)
+    const int h0 = kvh * group;
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int split_begin = split * ATD_SPLIT;
+    if (split_begin > pos || split_begin + ATD_SPLIT <= lo) return;       // nothing of this split is visible
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gq = lane >> 2, tq = lane & 3;                // fragment coordinates: row (and row + 8), column pair
+    const int* bt = block_table + (long)tok_req[t] * bt_stride;
+    const long head_off = (long)kvh * page_size * HEAD_DIM;
+    bf16* ring = reinterpret_cast<bf16*>(atm_raw) + warp * ATM_WARP_ELEMS;      // [stage][K | V][16][DP]
+
+    // this warp's keys, clipped to what the token sees, in chunks of 16 from the warp's first key
+    const int warp_begin = split_begin + warp * ATD_KEYS_PER_WARP;
+    const int first = max(warp_begin, lo), last = min(warp_begin + ATD_KEYS_PER_WARP - 1, pos);
+    const int c_begin = first > last ? 0 : (first - warp_begin) / ATM_CHUNK;
+    const int c_end = first > last ? 0 : (last - warp_begin) / ATM_CHUNK + 1;
+
+    // Chunk c of this warp into stage (c - c_begin) % ATM_STAGES.  Consecutive lanes take consecutive 16-byte
+    // pieces, so one instruction covers whole rows (whole 32-byte sectors); with pages that are a
+    // multiple of 16 tokens a chunk lies in one page and is one contiguous piece of K and one of V.
+    constexpr int PPR = HEAD_DIM / 8;                       // 16-byte pieces per key row
+    const bool chunk_in_page = (page_size % ATM_CHUNK) == 0;
+    auto fetch = [&](int c) {
+        bf16* kd = ring + ((c - c_begin) % ATM_STAGES) * 2 * ATM_STAGE_ELEMS;
+        bf16* vd = kd + ATM_STAGE_ELEMS;
+        const int key0 = warp_begin + c * ATM_CHUNK;
+        long base = 0;
+        if (chunk_in_page) {
+            const int pg = page_shift >= 0 ? (key0 >> page_shift) : (key0 / page_size);
+            const int off = page_shift >= 0 ? (key0 & (page_size - 1)) : (key0 - pg * page_size);
+            base = (long)bt[pg] * page_stride + head_off + (long)off * HEAD_DIM;
+        }
+#pragma unroll
+        for (int x = 0; x < (ATM_CHUNK * PPR + 31) / 32; ++x) {
+            const int i = x * 32 + lane;
+            const int r = i / PPR, ch = i - r * PPR;
+            if ((ATM_CHUNK * PPR) % 32 != 0 && r >= ATM_CHUNK) break;
+            const int j = key0 + r;
+            const bool real = j >= lo && j <= pos;
+            long a = base + (long)r * HEAD_DIM;
+            if (!chunk_in_page) {
+                a = 0;
+                if (real) {
+                    const int pg = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
+                    const int off = page_shift >= 0 ? (j & (page_size - 1)) : (j - pg * page_size);
+                    a = (long)bt[pg] * page_stride + head_off + (long)off * HEAD_DIM;
+                }
+            }
+            atm_cp16(kd + r * ATM_DP + ch * 8, k_cache + a + ch * 8, real);
+            atm_cp16(vd + r * ATM_DP + ch * 8, v_cache + a + ch * 8, real);
+        }
+    };
+#pragma unroll
+    for (int st = 0; st < ATM_STAGES; ++st) {
+        if (c_begin + st < c_end) fetch(c_begin + st);
+        atm_commit();
+    }
+
+    // the queries of the group as the A operand: row = head within the group, zero rows beyond it
+    uint32_t qa[HEAD_DIM / 16][4];
+    {
+        const bf16* q0 = q + (long)t * q_ld + (long)h0 * HEAD_DIM;
+#pragma unroll
+        for (int ks = 0; ks < HEAD_DIM / 16; ++ks) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int row = gq + (e & 1) * 8, col = ks * 16 + 2 * tq + (e >> 1) * 8;
+                qa[ks][e] = row < group ? *reinterpret_cast<const uint32_t*>(q0 + (long)row * HEAD_DIM + col) : 0u;
+            }
+        }
+    }
+
+    float o_acc[HEAD_DIM / 8][4];
+#pragma unroll
+    for (int i = 0; i < HEAD_DIM / 8; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o_acc[i][e] = 0.0f;
+    float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_run[2] = {0.0f, 0.0f};
+
+#pragma unroll 1
+    for (int c = c_begin; c < c_end; ++c) {
+        atm_wait<ATM_STAGES - 1>();                         // chunk c has landed (younger groups may be in flight)
+        __syncwarp();
+        const bf16* kt = ring + ((c - c_begin) % ATM_STAGES) * 2 * ATM_STAGE_ELEMS;
+        const bf16* vt = kt + ATM_STAGE_ELEMS;
+        // ---- S = Q K^T: 16 heads x ATM_CHUNK keys
+        float sc[ATM_CHUNK / 8][4];
+#pragma unroll
+        for (int i = 0; i < ATM_CHUNK / 8; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sc[i][e] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < HEAD_DIM / 16; ++ks) {
+#pragma unroll
+            for (int np = 0; np < ATM_CHUNK / 16; ++np) {
+                uint32_t b[4];
+                atm_ldmatrix(b, kt + (np * 16 + (lane & 7) + (lane >> 4) * 8) * ATM_DP + ks * 16 + ((lane >> 3) & 1) * 8);
+                atm_mma(sc[2 * np], qa[ks], b[0], b[1]);
+                atm_mma(sc[2 * np + 1], qa[ks], b[2], b[3]);
+            }
+        }
+        // ---- running softmax in units of log2 (scores times scale_log2e); keys outside [lo, pos] weigh nothing
+        const int key0 = warp_begin + c * ATM_CHUNK;
+        const bool all_seen = key0 >= lo && key0 + ATM_CHUNK - 1 <= pos;
+        float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+        for (int nt = 0; nt < ATM_CHUNK / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = key0 + nt * 8 + 2 * tq + (e & 1);
+                const float v = (all_seen || (j >= lo && j <= pos)) ? sc[nt][e] * scale_log2e : -CUDART_INF_F;
+                sc[nt][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_run[r], mx[r]);
+            corr[r] = weight_of(m_run[r], m_new);
+            m_run[r] = m_new;
+            l_run[r] *= corr[r];
+        }
+#pragma unroll
+        for (int nt = 0; nt < ATM_CHUNK / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float p = weight_of(sc[nt][e], m_run[e >> 1]);
+                sc[nt][e] = p;
+                l_run[e >> 1] += p;
+            }
+        }
+        if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
+#pragma unroll
+            for (int i = 0; i < HEAD_DIM / 8; ++i) {
+                o_acc[i][0] *= corr[0];
+                o_acc[i][1] *= corr[0];
+                o_acc[i][2] *= corr[1];
+                o_acc[i][3] *= corr[1];
+            }
+        }
+        // ---- O += P V
+#pragma unroll
+        for (int kk = 0; kk < ATM_CHUNK / 16; ++kk) {
+            uint32_t pa[4];
+            pa[0] = atm_pack(sc[2 * kk][0], sc[2 * kk][1]);
+            pa[1] = atm_pack(sc[2 * kk][2], sc[2 * kk][3]);
+            pa[2] = atm_pack(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+            pa[3] = atm_pack(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+            for (int dp = 0; dp < HEAD_DIM / 16; ++dp) {
+                uint32_t b[4];
+                atm_ldmatrix_trans(b, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ATM_DP + dp * 16 + (lane >> 4) * 8);
+                atm_mma(o_acc[2 * dp], pa, b[0], b[1]);
+                atm_mma(o_acc[2 * dp + 1], pa, b[2], b[3]);
+            }
+        }
+        __syncwarp();                                       // every lane is done with the stage
+        if (c + ATM_STAGES < c_end) fetch(c + ATM_STAGES);
+        atm_commit();
+    }
+    atm_wait<0>();
+    // the four lanes of a row hold different keys' sums
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    // ---- merge the warps through shared memory (the rings are free now), warp 0 first
+    __syncthreads();
+    float* s_o = reinterpret_cast<float*>(atm_raw);                     // [warp][head of the group][HEAD_DIM]
+    float* s_m = s_o + ATD_WARPS * ATM_MAX_GROUP * HEAD_DIM;            // [warp][head]
+    float* s_l = s_m + ATD_WARPS * ATM_MAX_GROUP;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = gq + r * 8;
+        if (row < group) {
+            float* dst = s_o + ((long)warp * ATM_MAX_GROUP + row) * HEAD_DIM + 2 * tq;
+#pragma unroll
+            for (int i = 0; i < HEAD_DIM / 8; ++i)
+                *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o_acc[i][2 * r], o_acc[i][2 * r + 1]);
+            if (tq == 0) {
+                s_m[warp * ATM_MAX_GROUP + row] = m_run[r];
+                s_l[warp * ATM_MAX_GROUP + row] = l_run[r];
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < group * HEAD_DIM; idx += ATD_WARPS * 32) {
+        const int row = idx / HEAD_DIM, d = idx - row * HEAD_DIM;
+        float mm = s_m[row];
+#pragma unroll
+        for (int w = 1; w < ATD_WARPS; ++w) mm = fmaxf(mm, s_m[w * ATM_MAX_GROUP + row]);
+        float ll = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < ATD_WARPS; ++w) {
+            const float a = weight_of(s_m[w * ATM_MAX_GROUP + row], mm);
+            ll += s_l[w * ATM_MAX_GROUP + row] * a;
+            acc += s_o[((long)w * ATM_MAX_GROUP + row) * HEAD_DIM + d] * a;
+        }
+        const int h = h0 + row;
+        if (n_splits == 1) {
+            out[(long)t * out_ld + (long)h * HEAD_DIM + d] = __float2bfloat16_rn(acc / ll);
+        } else {
+            float* prow = partial + (((long)li * n_heads + h) * n_splits + split) * ATD_ROW;
+            prow[d] = acc;
+            if (d == 0) { prow[HEAD_DIM] = mm; prow[HEAD_DIM + 1] = ll; }
+        }
+    }
+}
+
 // The merge kernel: one CTA per (token, head).
 __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_merge_kernel(
     const float* __restrict__ partial, bf16* __restrict__ out, long out_ld, const int* __restrict__ positions,
@@ -310,15 +593,18 @@ FL_API long fl_attention_decode_workspace_floats(int n_list, int n_heads, int n_
 // Tokens tok_list[0..n_list) (or 0..n_list when tok_list is null) of q attend to
 // their requests' cached keys.  n_splits must cover the longest sequence among
 // them: n_splits * ATD_SPLIT > largest position.  `partial` holds
-// fl_attention_decode_workspace_floats(...) floats when n_splits > 1.
+// fl_attention_decode_workspace_floats(...) floats when n_splits > 1.  `variant`:
+// 0 chooses (the tensor-core form when a key/value head serves at most 16 query
+// heads), 1 forces the CUDA-core form.
 FL_API int fl_attention_decode(const void* q, long q_ld, void* out, long out_ld, const void* k_cache,
                                const void* v_cache, long page_stride, int page_size,
                                const int* block_table, int bt_stride, const int* tok_req,
                                const int* positions, const int* tok_list, int n_list, int n_heads,
                                int n_kv_heads, int window, float scale, int n_splits, float* partial,
-                               cudaStream_t stream) {
+                               int variant, cudaStream_t stream) {
     if (n_list <= 0) return 0;
     if (n_heads > 65535 || n_splits < 1 || n_splits > 65535 || n_heads % n_kv_heads) return (int)cudaErrorInvalidValue;
+    if (HEAD_DIM % 16 != 0) variant = 1;
     if ((q_ld % 8) || (out_ld % 8) || (page_stride % 8)) return (int)cudaErrorMisalignedAddress;
     if (n_splits > 1 && partial == nullptr) return (int)cudaErrorInvalidValue;
     int page_shift = -1;
@@ -326,11 +612,31 @@ FL_API int fl_attention_decode(const void* q, long q_ld, void* out, long out_ld,
         page_shift = 0;
         while ((1 << page_shift) < page_size) ++page_shift;
     }
-    dim3 grid(n_list, n_heads, n_splits);
-    int rc = fl_launch(attention_decode_kernel, grid, dim3(ATD_WARPS * 32), 0, stream, (const bf16*)q, q_ld,
+    int rc;
+    if (variant != 1 && n_heads / n_kv_heads <= ATM_MAX_GROUP) {
+        // the tensor-core form: one CTA per (token, key/value head, split)
+        const size_t ring = (size_t)ATD_WARPS * ATM_WARP_ELEMS * sizeof(bf16);
+        const size_t merge = (size_t)ATD_WARPS * ATM_MAX_GROUP * (HEAD_DIM + 2) * sizeof(float);
+        const size_t smem = ring > merge ? ring : merge;
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            configured = true;
+        }
+        dim3 grid(n_list, n_kv_heads, n_splits);
+        rc = fl_launch(attention_decode_mma_kernel, grid, dim3(ATD_WARPS * 32), smem, stream, (const bf16*)q, q_ld,
                        (bf16*)out, out_ld, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, page_size,
                        page_shift, block_table, bt_stride, tok_req, positions, tok_list, n_heads, n_kv_heads,
                        window, scale * 1.4426950408889634f, n_splits, partial);
+    } else {
+        dim3 grid(n_list, n_heads, n_splits);
+        rc = fl_launch(attention_decode_kernel, grid, dim3(ATD_WARPS * 32), 0, stream, (const bf16*)q, q_ld,
+                       (bf16*)out, out_ld, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, page_size,
+                       page_shift, block_table, bt_stride, tok_req, positions, tok_list, n_heads, n_kv_heads,
+                       window, scale * 1.4426950408889634f, n_splits, partial);
+    }
     if (rc || n_splits == 1) return rc;
     dim3 mgrid(n_list, n_heads);
     return fl_launch(attention_decode_merge_kernel, mgrid, dim3(ATD_WARPS * 32), 0, stream, (const float*)partial,

@@ -48,7 +48,7 @@ def _decode_lib(head_dim: int):
         lib = load_library("attention_decode", {"HEAD_DIM": head_dim})
         lib.fl_attention_decode.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_long,
                                             c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                            c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]
+                                            c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p]
         lib.fl_attention_decode.restype = c_int
         assert lib.fl_attention_decode_head_dim() == head_dim
         assert lib.fl_attention_decode_split() == DECODE_SPLIT
@@ -102,8 +102,10 @@ def decode_splits(max_seq_len: int) -> int:
 
 
 def decode_attention(q, out, cache_tensor, block_table, tok_req, positions, tok_list, n_list, heads,
-                     kv_heads, head_dim, window, scale, page_size, n_splits):
-    """Split-key attention for the tokens in tok_list (None: tokens 0..n_list)."""
+                     kv_heads, head_dim, window, scale, page_size, n_splits, variant=0):
+    """Split-key attention for the tokens in tok_list (None: tokens 0..n_list).
+    variant 0 chooses (tensor cores when a key/value head serves at most 16 query heads
+    and the head size is a multiple of 16), 1 forces the CUDA-core kernel."""
     lib = _decode_lib(head_dim)
     ws = None
     if n_splits > 1:
@@ -114,7 +116,7 @@ def decode_attention(q, out, cache_tensor, block_table, tok_req, positions, tok_
                                  cache_tensor.stride(0), page_size, ops._ptr(block_table),
                                  block_table.stride(0), ops._ptr(tok_req), ops._ptr(positions),
                                  ops._ptr(tok_list), n_list, heads, kv_heads, int(window or 0),
-                                 float(scale), n_splits, ops._ptr(ws), ops._stream())
+                                 float(scale), n_splits, ops._ptr(ws), int(variant), ops._stream())
     ops._check(rc, "attention_decode", 2 if n_splits > 1 else 1)
 
 

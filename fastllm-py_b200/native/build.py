@@ -106,7 +106,7 @@ def compile_library(name: str, defines: dict | None = None, verbose_ptxas: bool 
     if out.exists():
         return out
     source = CSRC / f"{name}.cu"
-    tmp = out.with_suffix(f".tmp{os.getpid()}.so")
+    tmp = out.with_suffix(f".tmp{os.getpid()}_{threading.get_ident()}.so")    # one per builder, thread or process
     cmd = [_nvcc(), *ARCH_FLAGS, *COMMON_FLAGS, f"-I{CSRC}"]
     cmd += [f"-D{k}={v}" for k, v in sorted(defines.items())]
     if verbose_ptxas:
@@ -162,6 +162,10 @@ def compile_many(jobs: list, workers: int | None = None) -> list:
     """Build several (name, defines) libraries side by side."""
     from concurrent.futures import ThreadPoolExecutor
 
+    unique = {}
+    for name, defines in jobs:                      # a library asked for twice is built once
+        unique.setdefault((name, tuple(sorted((defines or {}).items()))), (name, defines))
+    jobs = list(unique.values())
     workers = workers or min(len(jobs), os.cpu_count() or 4) or 1
     with ThreadPoolExecutor(max_workers=workers) as pool:
         return list(pool.map(lambda j: compile_library(j[0], j[1]), jobs))

@@ -164,7 +164,7 @@ def run_simt(case, window=None):
     return out.float().cpu()
 
 
-def run_fast(case, window=None, prefill_variant=0):
+def run_fast(case, window=None, prefill_variant=0, decode_variant=0):
     from fastllm_py_b200.native import attention as fast
 
     out = torch.zeros_like(case.q)
@@ -175,7 +175,7 @@ def run_fast(case, window=None, prefill_variant=0):
         fast.decode_attention(case.q, out, case.cache, case.block_table, case.tok_req, case.positions,
                               None if n_dec == case.n_tokens else case.decode_tokens, n_dec, case.heads,
                               case.kv_heads, case.head_dim, window, scale, case.page_size,
-                              fast.decode_splits(longest))
+                              fast.decode_splits(longest), decode_variant)
     if n_dec < case.n_tokens:
         fast.prefill_attention(case.q, out, case.cache, case.block_table, case.req_start, case.req_ctx,
                                case.req_qlen, len(case.q_lens), case.n_tokens, False, case.heads,
@@ -211,6 +211,29 @@ def test_tensor_core_and_split_key_attention(shape, window):
     assert float(diff) <= case.tolerance()
 
 
+DECODE_SHAPES = [
+    # q_lens, ctx_lens, heads, kv_heads, head_dim, page_size
+    ([1, 1, 1], [0, 17, 300], 4, 4, 16, 16),
+    ([1, 1], [1023, 1024], 2, 2, 256, 64),
+    ([1, 1, 1, 1], [5, 255, 256, 700], 6, 2, 48, 8),          # three query heads per key/value head
+    ([1, 1], [300, 1500], 8, 1, 128, 16),                     # eight
+    ([1, 1, 1], [40, 511, 512], 32, 2, 64, 16),               # sixteen: the tensor-core kernel's most
+    ([1], [333], 34, 2, 32, 16),                              # seventeen: the CUDA-core kernel serves it
+    ([1, 1], [100, 200], 3, 3, 112, 12),                      # pages of 12 tokens
+    ([1, 7, 1], [600, 3, 90], 4, 2, 80, 32),                  # decode tokens beside a prompt portion
+]
+
+
+@pytest.mark.parametrize("shape", DECODE_SHAPES)
+@pytest.mark.parametrize("window", [None, 37, 300])
+@pytest.mark.parametrize("variant", [0, 1])
+def test_decode_attention_both_kernels(shape, window, variant):
+    """variant 0: mma.sync over the heads of a group (where it applies); variant 1: CUDA cores."""
+    case = AttentionCase(*shape, torch.bfloat16, seed=11)
+    diff = (run_fast(case, window, 0, variant) - case.reference(window)).abs().max()
+    assert float(diff) <= case.tolerance()
+
+
 TC_SHAPES = [
     # q_lens, ctx_lens, heads, kv_heads, head_dim, page_size: what the tcgen05 prefill kernel takes
     ([130], [257], 8, 1, 128, 16),
@@ -238,7 +261,11 @@ def run_fast_tcgen05(case, window=None):
     return run_fast(case, window, 2)
 
 
-@pytest.mark.parametrize("runner", [run_simt, run_fast, run_fast_tcgen05])
+def run_fast_cuda_core_decode(case, window=None):
+    return run_fast(case, window, 0, 1)
+
+
+@pytest.mark.parametrize("runner", [run_simt, run_fast, run_fast_tcgen05, run_fast_cuda_core_decode])
 def test_a_far_key_among_hundreds_is_found(runner):
     """One key far back (and one right at a page edge, one at a split edge) gets
     nearly all the weight: the output must be that key's value."""
@@ -255,7 +282,7 @@ def test_a_far_key_among_hundreds_is_found(runner):
         assert float((got[t].reshape(6, 64)[h] - want).abs().max()) < 0.05, (r, row, key_pos, h)
 
 
-@pytest.mark.parametrize("runner", [run_simt, run_fast])
+@pytest.mark.parametrize("runner", [run_simt, run_fast, run_fast_cuda_core_decode])
 def test_window_edge(runner):
     """A dominant key just outside the window must be ignored, one just inside must win."""
     window, ctx = 50, 300
