@@ -324,6 +324,23 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
 #define TCP_BN 256
 #define TCP_STAGES 4
 
+// The order in which the persistent kernels walk over output tiles.  The CTAs
+// (or CTA pairs) that run at the same time work on consecutive tiles, so these
+// should share operands: token tiles go fastest inside panels of TC_RASTER_M
+// token tiles, i.e. a weight tile is fetched from DRAM once per panel and used by
+// up to TC_RASTER_M CTAs at about the same time out of L2, while the panel's
+// activations (a few MB) stay in L2 throughout.  (With weight tiles fastest, the
+// whole weight matrix, larger than L2, streamed from DRAM once per token tile.)
+#define TC_RASTER_M 8
+__device__ __forceinline__ void tc_raster(int tile, int tiles_n, int tiles_m, int& tn, int& tm) {
+    const int per_panel = TC_RASTER_M * tiles_n;
+    const int panel = tile / per_panel;
+    const int within = tile - panel * per_panel;
+    const int rows = min(TC_RASTER_M, tiles_m - panel * TC_RASTER_M);     // token tiles in this panel
+    tn = within / rows;
+    tm = panel * TC_RASTER_M + (within - tn * rows);
+}
+
 template <typename OutT>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_persistent_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
@@ -366,12 +383,8 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_persistent_kernel(
     const uint32_t tmem_base = *tmem_slot;
     pdl_trigger();
 
-    // tile -> (which 128 output features, which 256 tokens): neighbours in the
-    // walk share the token tile, so the activations stay hot in L2
     auto tile_coords = [&](int i, int& tn, int& tm) {
-        const int tile = (int)blockIdx.x + i * (int)gridDim.x;
-        tm = tile / tiles_n;
-        tn = tile - tm * tiles_n;
+        tc_raster((int)blockIdx.x + i * (int)gridDim.x, tiles_n, num_tiles / tiles_n, tn, tm);
     };
 
     if (warp == 0) {
@@ -626,9 +639,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
     // the GPU with another kernel that also allocates tensor memory stalled for good now and then.
 
     auto tile_coords = [&](int i, int& tn, int& tm) {
-        const int tile = pair + i * num_pairs;
-        tm = tile / tiles_n;
-        tn = tile - tm * tiles_n;
+        tc_raster(pair + i * num_pairs, tiles_n, num_tiles / tiles_n, tn, tm);
     };
 
     if (warp == 0) {
