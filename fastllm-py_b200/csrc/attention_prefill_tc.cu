@@ -1,26 +1,27 @@
 // Paged causal attention for prompt portions on the Blackwell tensor cores:
 // both products (Q K^T and P V) are tcgen05.mma with the accumulators in tensor
 // memory; keys, values and queries arrive by TMA; the softmax runs in float on
-// 128 threads that each own one query row.
+// FT_PARTS threads per query row.
 //
 // A CTA takes 128 consecutive query rows of one request and one query head and
 // walks the request's keys in blocks of 128 (starting at multiples of 128 of the
 // absolute position, so a row's sequence of partial maxima does not depend on
 // how the prompt was cut).  Per block:
-//   producer warp   TMA: the block's pages of this head's keys and values into a
-//                   two-stage ring (one box of page_size x 64 per page and 64
-//                   columns, each issued by a lane of its own; pages that do not
-//                   exist are fetched from beyond the tensor, which fills zeros);
+//   producer warps  TMA: the block's pages of this head's keys (one warp) and values
+//                   (another) into two-stage rings (one box of page_size x 64
+//                   per page and 64 columns, each issued by a lane of its own;
+//                   pages that do not exist are fetched from beyond the tensor,
+//                   which fills zeros);
 //   MMA warp        S = Q K^T into one of two S buffers in tensor memory (so the
 //                   next block's scores are computed while this block's are
 //                   being exponentiated), then O_blk = P V;
-//   softmax warps   two threads share query row r: each reads its half of the
-//                   row of S (tcgen05.ld), masks, exchanges the half-row maximum
-//                   with its partner, keeps the running maximum and sum in float,
-//                   writes its half of P as bfloat16 into shared memory in the
-//                   swizzled K-major layout the second MMA reads, then adds its
-//                   half of the columns of O_blk into its part of the output row,
-//                   which it holds in registers (rescaled when the maximum moves).
+//   softmax warps   FT_PARTS threads share query row r: each reads its part of the row of S
+//                   (tcgen05.ld), masks, exchanges the part's maximum with its
+//                   partners, keeps the running maximum and sum in float, writes
+//                   its part of P as bfloat16 into shared memory in the swizzled
+//                   K-major layout the second MMA reads, and adds its columns
+//                   of O_blk into its part of the output row, which it holds in
+//                   registers (rescaled when the maximum moves).
 // Every wait on an mbarrier is bounded; a give-up sets an error word and all
 // roles leave.
 //
@@ -40,13 +41,22 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "the tcgen05 prefill kernel tak
 #define FT_BM 128                          // query rows per CTA
 #define FT_BN 128                          // keys per block
 #define FT_STAGES 2
-#define FT_THREADS 320                     // 8 softmax warps (two threads per query row), producer warp, MMA warp
-#define FT_SOFTMAX_THREADS 256
+#ifndef FT_PARTS
+#define FT_PARTS 2                         // softmax threads per query row
+#endif
+#define FT_KP (FT_BN / FT_PARTS)           // keys of a block per softmax thread
+#define FT_OD (HEAD_DIM / FT_PARTS)        // output columns per softmax thread
+static_assert(FT_OD % 32 == 0 && FT_KP % 32 == 0, "a softmax thread owns multiples of 32 keys and of 32 columns");
+#define FT_SOFTMAX_THREADS (128 * FT_PARTS)
 #define FT_SOFTMAX_WARPS (FT_SOFTMAX_THREADS / 32)
+#define FT_PRODUCER_WARP FT_SOFTMAX_WARPS                      // queries and keys
+#define FT_MMA_WARP (FT_SOFTMAX_WARPS + 1)
+#define FT_VPRODUCER_WARP (FT_SOFTMAX_WARPS + 2)              // values
+#define FT_THREADS ((FT_SOFTMAX_WARPS + 3) * 32)
 #define FT_ATOMS (HEAD_DIM / 64)           // 64-column swizzle atoms per row
 #define FT_ATOM_BYTES (128 * 128)          // 128 rows x 128 bytes
 #define FT_WAIT_LIMIT_NS 2000000000ull
-enum { FT_ERR_WAIT = 301 };
+enum { FT_ERR_WAIT = 301, FT_ERR_SMEM = 302 };
 
 // ------------------------------------------------------------------ PTX wraps
 __device__ __forceinline__ uint32_t ft_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -160,10 +170,15 @@ __device__ __forceinline__ float ft_weight(float a, float b) { return (a == -CUD
 struct FtSmem {
     static constexpr int Q_BYTES = FT_ATOMS * FT_ATOM_BYTES;
     static constexpr int KV_BYTES = FT_ATOMS * FT_ATOM_BYTES;          // one of K or V, one stage
-    static constexpr int P_BYTES = 2 * FT_ATOM_BYTES;                  // 128 rows x 128 keys
-    static constexpr int TILES = Q_BYTES + 2 * FT_STAGES * KV_BYTES + P_BYTES;
-    static constexpr int BARS = 16 * 8 + 16 + 4 * 128 * 4;             // barriers, then the half-row maxima (two rounds)
-    static constexpr int TOTAL = TILES + BARS + 1024;
+    static constexpr int P_BYTES = 2 * FT_ATOM_BYTES;                  // 128 rows x 128 keys, one of two buffers
+    static constexpr int TILES = Q_BYTES + 2 * FT_STAGES * KV_BYTES + 2 * P_BYTES;
+    static constexpr int BARS = 24 * 8 + 2 * FT_PARTS * 128 * 4;       // barriers, then the parts' maxima (two rounds)
+    // The tiles want a 1024-byte boundary.  With 128-wide heads they fill the SM's shared memory
+    // to within a KB, so there is no room to round up to one: the kernel then counts on the
+    // dynamic shared memory starting on such a boundary (it has no static shared memory) and
+    // reports FT_ERR_SMEM instead of running if it does not.
+    static constexpr int SLACK = (TILES + BARS + 1024 <= 232448) ? 1024 : 0;
+    static constexpr int TOTAL = TILES + BARS + SLACK;
 };
 
 __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
@@ -172,23 +187,29 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
     int bt_stride, const int* __restrict__ req_start, const int* __restrict__ req_ctx,
     const int* __restrict__ req_qlen, int n_requests, int include_single, int n_heads, int n_kv_heads,
     int window, float scale_log2e, int* __restrict__ status) {
-    extern __shared__ unsigned char ft_raw[];
+    extern __shared__ __align__(1024) unsigned char ft_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)ft_raw + 1023) & ~(uintptr_t)1023);
+    if (base + FtSmem::TILES + FtSmem::BARS > ft_raw + FtSmem::TOTAL) {       // uniform over the CTA
+        if (threadIdx.x == 0) atomicCAS(status, 0, FT_ERR_SMEM);
+        return;
+    }
     unsigned char* q_s = base;
     unsigned char* k_s = q_s + FtSmem::Q_BYTES;                        // [stage][atom][128 rows][128 B]
     unsigned char* v_s = k_s + FT_STAGES * FtSmem::KV_BYTES;
-    unsigned char* p_s = v_s + FT_STAGES * FtSmem::KV_BYTES;           // [atom][128 rows][128 B]
+    unsigned char* p_s = v_s + FT_STAGES * FtSmem::KV_BYTES;           // [buffer][atom][128 rows][128 B]
     uint64_t* bars = (uint64_t*)(base + FtSmem::TILES);
     uint64_t* q_full = bars + 0;
-    uint64_t* kv_full = bars + 1;                                      // [2]
-    uint64_t* kv_empty = bars + 3;                                     // [2]
+    uint64_t* k_full = bars + 1;                                       // [2]
+    uint64_t* k_empty = bars + 3;                                      // [2]
     uint64_t* s_full = bars + 5;                                       // [2]
     uint64_t* s_empty = bars + 7;                                      // [2]
-    uint64_t* p_full = bars + 9;
-    uint64_t* o_full = bars + 11;
-    uint64_t* o_empty = bars + 12;
+    uint64_t* p_full = bars + 9;                                       // [2]
+    uint64_t* o_full = bars + 11;                                      // [2]
     uint32_t* tmem_slot = (uint32_t*)(bars + 13);
     uint64_t* x_bar = bars + 14;                                       // the softmax threads' exchange point
+    uint64_t* v_full = bars + 16;                                      // [2]
+    uint64_t* v_empty = bars + 18;                                     // [2]
+    uint64_t* o_empty = bars + 20;                                     // [2]
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     // which request and which 128-row tile: blockIdx.y counts tiles, a request's last (longest) tile first
@@ -217,20 +238,24 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
     if (threadIdx.x == 0) {
         ft_bar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
-            ft_bar_init(&kv_full[s], 1);
-            ft_bar_init(&kv_empty[s], 1);
+            ft_bar_init(&k_full[s], 1);
+            ft_bar_init(&k_empty[s], 1);
+            ft_bar_init(&v_full[s], 1);
+            ft_bar_init(&v_empty[s], 1);
             ft_bar_init(&s_full[s], 1);
             ft_bar_init(&s_empty[s], FT_SOFTMAX_WARPS);
         }
-        ft_bar_init(p_full, FT_SOFTMAX_WARPS);
-        ft_bar_init(o_full, 1);
-        ft_bar_init(o_empty, FT_SOFTMAX_WARPS);
+        for (int s = 0; s < 2; ++s) {
+            ft_bar_init(&p_full[s], FT_SOFTMAX_WARPS);
+            ft_bar_init(&o_full[s], 1);
+            ft_bar_init(&o_empty[s], FT_SOFTMAX_WARPS);
+        }
         ft_bar_init(x_bar, FT_SOFTMAX_WARPS);
         *abort_flag = (*(volatile int*)status != 0) ? 1 : 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 9) {
+    if (warp == FT_MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ft_smem(tmem_slot)),
                      "r"(512u)
                      : "memory");
@@ -241,7 +266,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
     ft_fence_after();
     const uint32_t tmem = *tmem_slot;
     const uint32_t tmem_s = tmem;                                      // two S buffers: columns 0 and 128
-    const uint32_t tmem_o = tmem + 256;                                // O_blk: HEAD_DIM columns
+    const uint32_t tmem_o = tmem + 256;                                // two O_blk buffers of HEAD_DIM columns
 
 #define FT_GIVE_UP()                                                             \
     {                                                                            \
@@ -249,26 +274,33 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
         break;                                                                   \
     }
 
-    if (warp == 8) {
+    if (warp == FT_PRODUCER_WARP || warp == FT_VPRODUCER_WARP) {
         if (!*abort_flag) {
-            // ---- producer: the whole warp.  A block of 128 keys is pages x atoms x {K, V} boxes of
-            // a few KB; one lane issues one box (looking up its page itself), so the 32 copies of a
-            // block leave together instead of one thread walking through them.
-            if (lane == 0) {
+            // ---- producers: one warp for the queries and the keys, one for the values, each with
+            // a two-stage ring of its own.  A key stage is free again as soon as S of its block is
+            // computed, which is a whole block earlier than P V; with keys and values in one ring
+            // the next keys could only be asked for after P V, and their way through TMA showed.
+            // A block of 128 keys is pages x atoms boxes of a few KB; one lane issues one box
+            // (looking up its page itself), so a block's copies leave together.
+            const int is_v = warp == FT_VPRODUCER_WARP ? 1 : 0;
+            uint64_t* full = is_v ? v_full : k_full;
+            uint64_t* empty = is_v ? v_empty : k_empty;
+            unsigned char* ring = is_v ? v_s : k_s;
+            if (!is_v && lane == 0) {
                 ft_bar_expect(q_full, FtSmem::Q_BYTES);
                 for (int a = 0; a < FT_ATOMS; ++a)
                     ft_tma_2d(q_s + a * FT_ATOM_BYTES, &map_q, q_full, h * HEAD_DIM + a * 64, tok0);
             }
             const int* bt = block_table + (long)req * bt_stride;
-            const int n_ops = (FT_BN / page_size) * FT_ATOMS * 2;
+            const int n_ops = (FT_BN / page_size) * FT_ATOMS;
             for (int i = 0; i < n_blocks; ++i) {
                 const int s = i & 1;
-                if (!ft_warp_wait(&kv_empty[s], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag)) FT_GIVE_UP();
-                if (lane == 0) ft_bar_expect(&kv_full[s], 2 * FtSmem::KV_BYTES);
+                if (!ft_warp_wait(&empty[s], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag)) FT_GIVE_UP();
+                if (lane == 0) ft_bar_expect(&full[s], FtSmem::KV_BYTES);
                 __syncwarp();
                 const int key0 = (kb_begin + i) * FT_BN;
                 for (int op = lane; op < n_ops; op += 32) {
-                    const int p = op / (FT_ATOMS * 2), a = (op >> 1) % FT_ATOMS, is_v = op & 1;
+                    const int p = op / FT_ATOMS, a = op % FT_ATOMS;
                     const int first_key = key0 + p * page_size;
                     const int last_key = first_key + page_size - 1;
                     // a page wholly outside what this tile may see is fetched from beyond the tensor: zeros
@@ -278,18 +310,18 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
                         row = (int)(((pg * 2 + is_v) * n_kv_heads + kvh) * page_size);
                     }
                     const int off = s * FtSmem::KV_BYTES + a * FT_ATOM_BYTES + p * page_size * 128;
-                    ft_tma_2d((is_v ? v_s : k_s) + off, &map_kv, &kv_full[s], a * 64, row);
+                    ft_tma_2d(ring + off, &map_kv, &full[s], a * 64, row);
                 }
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == FT_MMA_WARP) {
         if (lane == 0 && !*abort_flag) {
             // ---- MMA issuer
             constexpr uint32_t idesc_s = ft_idesc(FT_BM, FT_BN, 0);
             constexpr uint32_t idesc_o = ft_idesc(FT_BM, HEAD_DIM, 1);
             auto issue_s = [&](int i) -> bool {                        // S(i) = Q K(i)^T into S buffer i & 1
                 const int s = i & 1;
-                if (!ft_wait(&kv_full[s], (uint32_t)(i >> 1) & 1u, abort_flag)) return false;
+                if (!ft_wait(&k_full[s], (uint32_t)(i >> 1) & 1u, abort_flag)) return false;
                 if (!ft_wait(&s_empty[s], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag)) return false;
                 ft_fence_after();
                 const uint32_t qa = ft_smem(q_s), ka = ft_smem(k_s + s * FtSmem::KV_BYTES);
@@ -299,6 +331,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
                     ft_mma(tmem_s + (uint32_t)(s * FT_BN), ft_desc_kmajor(qa + off), ft_desc_kmajor(ka + off),
                            idesc_s, k > 0 ? 1u : 0u);
                 }
+                ft_commit(&k_empty[s]);             // the key stage is free once these MMAs have read it
                 ft_commit(&s_full[s]);
                 return true;
             };
@@ -306,96 +339,102 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
             if (ok) ok = issue_s(0);
             for (int i = 0; i < n_blocks && ok; ++i) {
                 if (i + 1 < n_blocks && !issue_s(i + 1)) { ok = false; break; }
-                if (!ft_wait(p_full, (uint32_t)i & 1u, abort_flag)) { ok = false; break; }
-                if (!ft_wait(o_empty, ((uint32_t)i & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                if (!ft_wait(&v_full[i & 1], (uint32_t)(i >> 1) & 1u, abort_flag)) { ok = false; break; }
+                const int b = i & 1;                                   // P and O_blk buffer of this block
+                const uint32_t ph = (uint32_t)(i >> 1) & 1u;
+                if (!ft_wait(&p_full[b], ph, abort_flag)) { ok = false; break; }
+                if (!ft_wait(&o_empty[b], ph ^ 1u, abort_flag)) { ok = false; break; }
                 ft_fence_after();
-                const uint32_t pa = ft_smem(p_s), va = ft_smem(v_s + (i & 1) * FtSmem::KV_BYTES);
+                const uint32_t pa = ft_smem(p_s + b * FtSmem::P_BYTES), va = ft_smem(v_s + b * FtSmem::KV_BYTES);
 #pragma unroll
                 for (int k = 0; k < FT_BN / 16; ++k) {
                     // A = P: K-major, keys are its K axis; B = V: MN-major, 16 keys = two 8-row groups
                     const uint32_t a_off = (uint32_t)((k >> 2) * FT_ATOM_BYTES + (k & 3) * 32);
-                    ft_mma(tmem_o, ft_desc_kmajor(pa + a_off), ft_desc_mnmajor(va + (uint32_t)(k * 16 * 128)),
+                    ft_mma(tmem_o + (uint32_t)(b * HEAD_DIM), ft_desc_kmajor(pa + a_off),
+                           ft_desc_mnmajor(va + (uint32_t)(k * 16 * 128)),
                            idesc_o, k > 0 ? 1u : 0u);
                 }
-                ft_commit(&kv_empty[i & 1]);
-                ft_commit(o_full);                  // O_blk(i) is ready; P's memory is free again
+                ft_commit(&v_empty[i & 1]);
+                ft_commit(&o_full[b]);              // O_blk(i) is ready; P's buffer is free again
             }
             if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, FT_ERR_WAIT); }
         }
     } else {
-        // ---- softmax: threads r and r + 128 share query row r; `half` says which
-        // 64 keys of a block and which half of the output columns a thread owns
+        // ---- softmax: FT_PARTS threads (r, r + 128, ...) share query row r; `part` says which
+        // FT_KP keys of a block and which FT_OD output columns a thread owns
         const int r = threadIdx.x & 127;
-        const int half = threadIdx.x >> 7;
+        const int part = threadIdx.x >> 7;
         const int pos_r = ctx + row0 + r;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-        // [round parity][half][row]: a round's values stay untouched while the next round's are written
-        float* half_max_all = reinterpret_cast<float*>(bars + 16);
-        constexpr int OD = HEAD_DIM / 2;                                 // output columns per thread
+        // [round parity][part][row]: a round's values stay untouched while the next round's are written
+        float* part_max_all = reinterpret_cast<float*>(bars + 24);
         float m_run = -CUDART_INF_F, l_run = 0.0f;
-        float o_reg[OD];
+        float o_reg[FT_OD];
 #pragma unroll
-        for (int d = 0; d < OD; ++d) o_reg[d] = 0.0f;
+        for (int d = 0; d < FT_OD; ++d) o_reg[d] = 0.0f;
         bool ok = !*abort_flag;
-        // Block i's exponentials are computed while the tensor core still works on P V of block
-        // i - 1; that product is collected (and its shared-memory P released) only then, so the
-        // correction it needs is the one of the round before: out = out * corr(i - 1) + O_blk(i - 1).
+        // P and O_blk have two buffers each, so the softmax of block i does not wait for P V of
+        // block i - 1: that product is collected after P(i) is handed over, and the correction it
+        // needs is the one of the round before: out = out * corr(i - 1) + O_blk(i - 1).
         float corr_prev = 0.0f;
         auto collect = [&](int i_done, float corr_of) -> bool {          // adds O_blk(i_done) into the row
-            if (!ft_warp_wait(o_full, (uint32_t)i_done & 1u, abort_flag)) return false;
+            const int b = i_done & 1;
+            if (!ft_warp_wait(&o_full[b], (uint32_t)(i_done >> 1) & 1u, abort_flag)) return false;
             ft_fence_after();
 #pragma unroll
-            for (int c = 0; c < OD; c += 32) {
+            for (int c = 0; c < FT_OD; c += 32) {
                 uint32_t w[32];
-                ft_ld32(tmem_o + lane_base + (uint32_t)(half * OD + c), w);
+                ft_ld32(tmem_o + lane_base + (uint32_t)(b * HEAD_DIM + part * FT_OD + c), w);
                 ft_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 32; ++j) o_reg[c + j] = fmaf(o_reg[c + j], corr_of, __uint_as_float(w[j]));
             }
             ft_fence_before();
-            ft_warp_arrive(o_empty);
+            ft_warp_arrive(&o_empty[b]);
             return true;
         };
         for (int i = 0; i < n_blocks && ok; ++i) {
             const int sb = i & 1;
             if (!ft_warp_wait(&s_full[sb], (uint32_t)(i >> 1) & 1u, abort_flag)) FT_GIVE_UP();
             ft_fence_after();
-            const int key0 = (kb_begin + i) * FT_BN + half * 64;         // first key of this thread's half
-            const uint32_t s_addr = tmem_s + (uint32_t)(sb * FT_BN + half * 64) + lane_base;
-            const bool all_seen = (key0 + 63 <= pos_r) && (window <= 0 || key0 > pos_r - window);
-            uint32_t v[64];
-            ft_ld32(s_addr, v);
-            ft_ld32(s_addr + 32u, v + 32);
+            const int key0 = (kb_begin + i) * FT_BN + part * FT_KP;      // first key of this thread's part
+            const uint32_t s_addr = tmem_s + (uint32_t)(sb * FT_BN + part * FT_KP) + lane_base;
+            const bool all_seen = (key0 + FT_KP - 1 <= pos_r) && (window <= 0 || key0 > pos_r - window);
+            uint32_t v[FT_KP];
+#pragma unroll
+            for (int c = 0; c < FT_KP; c += 32) ft_ld32(s_addr + (uint32_t)c, v + c);
             ft_ld_wait();
             ft_fence_before();
             ft_warp_arrive(&s_empty[sb]);                                  // S(i) is in registers
             if (!all_seen) {
 #pragma unroll
-                for (int j = 0; j < 64; ++j) {
+                for (int j = 0; j < FT_KP; ++j) {
                     const int key = key0 + j;
                     if (!(key <= pos_r && (window <= 0 || key > pos_r - window))) v[j] = 0xff800000u;   // -inf
                 }
             }
             float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-            for (int j = 0; j < 64; j += 4) {
+            for (int j = 0; j < FT_KP; j += 4) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], __uint_as_float(v[j + e]));
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            // exchange the half-row maxima (one barrier among the softmax warps per block)
-            float* half_max = half_max_all + (i & 1) * 256;
-            half_max[half * 128 + r] = mx;
+            // exchange the parts' maxima (one barrier among the softmax warps per block)
+            float* part_max = part_max_all + (i & 1) * (FT_PARTS * 128);
+            part_max[part * 128 + r] = mx;
             ft_warp_arrive(x_bar);                                        // (an mbarrier: its wait can give up)
             if (!ft_warp_wait(x_bar, (uint32_t)i & 1u, abort_flag)) FT_GIVE_UP();
-            const float mx_row = fmaxf(mx, half_max[(half ^ 1) * 128 + r]);
+            float mx_row = part_max[r];
+#pragma unroll
+            for (int q = 1; q < FT_PARTS; ++q) mx_row = fmaxf(mx_row, part_max[q * 128 + r]);
             const float m_new = fmaxf(m_run, mx_row * scale_log2e);
             const float corr = ft_weight(m_run, m_new);
             const float neg_m = (m_new == -CUDART_INF_F) ? 0.0f : -m_new;      // an empty row: every p below is 0
             float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            uint32_t packed[32];
+            uint32_t packed[FT_KP / 2];
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
+            for (int c = 0; c < FT_KP / 2; ++c) {
                 const float p0 = ft_ex2(fmaf(__uint_as_float(v[2 * c]), scale_log2e, neg_m));
                 const float p1 = ft_ex2(fmaf(__uint_as_float(v[2 * c + 1]), scale_log2e, neg_m));
                 l4[c & 3] += p0 + p1;
@@ -404,32 +443,39 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
             }
             l_run = l_run * corr + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
             m_run = m_new;
-            // P V of the block before is complete by now or soon: take it out, which also frees P's memory
+            // P(i) goes into the buffer that P V of block i - 2 read; that product was collected in
+            // the round before, so the buffer is free.  Then the product of block i - 1 is taken
+            // out of tensor memory, while the tensor core already has block i's P to work on.
+#pragma unroll
+            for (int c = 0; c < FT_KP / 8; ++c) {                          // 8 keys = one 16-byte chunk
+                const int chunk = part * (FT_KP / 8) + c;                 // of the row's 16 chunks
+                unsigned char* dst = p_s + sb * FtSmem::P_BYTES + (chunk >> 3) * FT_ATOM_BYTES + r * 128 +
+                                     (((chunk & 7) ^ (r & 7)) << 4);
+                *reinterpret_cast<uint4*>(dst) =
+                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
+            ft_warp_arrive(&p_full[sb]);
             if (i > 0 && !collect(i - 1, corr_prev)) FT_GIVE_UP();
             corr_prev = corr;
-            unsigned char* row_base = p_s + half * FT_ATOM_BYTES + r * 128;
-#pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8)                                 // 8 keys = one 16-byte chunk
-                *reinterpret_cast<uint4*>(row_base + ((c8 ^ (r & 7)) << 4)) =
-                    make_uint4(packed[4 * c8], packed[4 * c8 + 1], packed[4 * c8 + 2], packed[4 * c8 + 3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
-            ft_warp_arrive(p_full);
         }
         if (ok && n_blocks > 0 && !collect(n_blocks - 1, corr_prev)) {
             ok = false;
             if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, FT_ERR_WAIT); }
         }
-        // the row's sum is the two halves' sums (both are relative to the same maximum)
-        float* half_max = half_max_all + (n_blocks & 1) * 256;
-        half_max[half * 128 + r] = l_run;
+        // the row's sum is the parts' sums (all relative to the same maximum)
+        float* part_sum = part_max_all + (n_blocks & 1) * (FT_PARTS * 128);
+        part_sum[part * 128 + r] = l_run;
         ft_warp_arrive(x_bar);
         const bool met = ft_warp_wait(x_bar, (uint32_t)n_blocks & 1u, abort_flag);
-        const float l_row = l_run + half_max[(half ^ 1) * 128 + r];
+        float l_row = part_sum[r];
+#pragma unroll
+        for (int q = 1; q < FT_PARTS; ++q) l_row += part_sum[q * 128 + r];
         if (met && ok && !*abort_flag && r < rows_here) {
             const float inv = 1.0f / l_row;
-            bf16* dst = out + (long)(tok0 + r) * out_ld + (long)h * HEAD_DIM + half * OD;
+            bf16* dst = out + (long)(tok0 + r) * out_ld + (long)h * HEAD_DIM + part * FT_OD;
 #pragma unroll
-            for (int d = 0; d < OD; d += 8) {
+            for (int d = 0; d < FT_OD; d += 8) {
                 uint4 w;
                 __nv_bfloat162* wp = reinterpret_cast<__nv_bfloat162*>(&w);
 #pragma unroll
@@ -442,7 +488,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
 #undef FT_GIVE_UP
     ft_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == FT_MMA_WARP) {
         ft_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
