@@ -341,3 +341,199 @@ def test_toy_architecture_with_state_window_repeat_and_shared_cache(dtype, tmp_p
     eng.end("a")
     eng.end("b")
     assert all(g.pool.free_pages == g.pool.num_pages for g in eng.cache.groups)
+
+
+# ------------------------- a second toy: another position encoding and a feed-forward with routing
+
+@dataclass(frozen=True)
+class Toy2Config:
+    hidden_size: int = 40
+    vocab_size: int = 83
+    num_heads: int = 4
+    num_kv_heads: int = 2
+    head_dim: int = 32
+    experts: int = 3
+    expert_size: int = 56
+    eps: float = 1e-5
+
+    @classmethod
+    def from_hf(cls, raw):
+        return cls(**{k: raw[k] for k in cls.__dataclass_fields__})
+
+    def to_hf(self):
+        return dict(architectures=["Toy2ForCausalLM"], **self.__dict__)
+
+
+def toy2_angles(positions, rot_dim):
+    """The toy position encoding: only the first `rot_dim` of a head's dimensions turn, the
+    j-th pair by sqrt(position + 1) * (j + 1) / 7 (nothing anyone uses; it is no power law
+    and not linear in the position, so a kernel that assumed either would show)."""
+    pos = np.asarray(positions, dtype=np.float64)
+    j = np.arange(rot_dim // 2, dtype=np.float64)
+    return (np.sqrt(pos + 1.0)[:, None] * (j[None, :] + 1.0) / 7.0).astype(np.float32)
+
+
+def register_toy2():
+    from fastllm_py_b200.config import register_architecture
+    from fastllm_py_b200.native import ops
+    from fastllm_py_b200.parts import LayerRun, LayerSpec, ModelPlan, Part, PartSpec, register_part
+    from fastllm_py_b200.parts.linear import Linear
+
+    @register_part("position", "toy_sqrt_turn")
+    class SqrtTurn(Part):
+        category = "position"
+
+        def __init__(self, spec, ctx):
+            super().__init__(spec, ctx)
+            self.rot_dim = int(spec.params["rot_dim"])
+
+        def tables(self):
+            key = ("toy_sqrt_turn", self.rot_dim, self.ctx.max_positions)
+            if key not in self.ctx.shared:
+                ang = toy2_angles(np.arange(self.ctx.max_positions), self.rot_dim)
+                self.ctx.shared[key] = tuple(torch.from_numpy(f(ang).astype(np.float32)).to(self.ctx.device)
+                                             for f in (np.cos, np.sin))
+            return self.ctx.shared[key]
+
+    @register_part("feed_forward", "toy_top1")
+    class Top1Experts(Part):
+        """Every token goes to the one expert with the largest router logit (float32
+        logits); its output is scaled by the sigmoid of that logit.  Tokens are grouped
+        by expert and each group runs the framework's Linear and SwiGLU kernels."""
+        category = "feed_forward"
+
+        def __init__(self, spec, ctx):
+            super().__init__(spec, ctx)
+            self.hidden = spec.params["hidden_size"]
+            self.n, self.inter = spec.params["experts"], spec.params["expert_size"]
+
+        def weight_shapes(self):
+            shapes = {"router": (self.n, self.hidden)}
+            for e in range(self.n):
+                shapes.update({f"gate{e}": (self.inter, self.hidden), f"up{e}": (self.inter, self.hidden),
+                               f"down{e}": (self.hidden, self.inter)})
+            return shapes
+
+        def load(self, tensors):
+            self.router = tensors["router"].float()
+            self.gate_up = [Linear([tensors[f"gate{e}"], tensors[f"up{e}"]]) for e in range(self.n)]
+            self.down = [Linear([tensors[f"down{e}"]]) for e in range(self.n)]
+
+        def forward(self, h, out, step):
+            logits = h.float() @ self.router.t()                      # router logits in 32-bit
+            top = logits.argmax(dim=-1)
+            scale = torch.sigmoid(logits.gather(1, top[:, None]))
+            for e in range(self.n):
+                rows = (top == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                x = h[rows].contiguous()
+                gu = torch.empty(x.shape[0], 2 * self.inter, dtype=h.dtype, device=h.device)
+                self.gate_up[e].forward(x, gu)
+                act = torch.empty(x.shape[0], self.inter, dtype=h.dtype, device=h.device)
+                ops.swiglu(gu, act)
+                y = torch.empty(x.shape[0], self.hidden, dtype=h.dtype, device=h.device)
+                self.down[e].forward(act, y)
+                out[rows] = (y.float() * scale[rows]).to(h.dtype)
+            return None
+
+    def make_plan(cfg, names=None):
+        def norm(n):
+            return PartSpec("rmsnorm", dict(size=cfg.hidden_size, eps=cfg.eps), {"weight": n})
+
+        def attn(i):
+            return PartSpec("attention", dict(
+                hidden_size=cfg.hidden_size, num_heads=cfg.num_heads, num_kv_heads=cfg.num_kv_heads,
+                head_dim=cfg.head_dim, window=None, shares_cache=False,
+                position=PartSpec("toy_sqrt_turn", dict(rot_dim=cfg.head_dim // 2))),
+                {s: f"l{i}.{s}" for s in ("q", "k", "v", "o")})
+
+        def experts(i):
+            names_ = {"router": f"l{i}.router"}
+            for e in range(cfg.experts):
+                names_.update({f"{s}{e}": f"l{i}.e{e}.{s}" for s in ("gate", "up", "down")})
+            return PartSpec("toy_top1", dict(hidden_size=cfg.hidden_size, experts=cfg.experts,
+                                             expert_size=cfg.expert_size), names_)
+
+        def dense(i):
+            return PartSpec("swiglu", dict(hidden_size=cfg.hidden_size, intermediate_size=cfg.expert_size),
+                            {s: f"l{i}.ffn.{s}" for s in ("gate", "up", "down")})
+
+        # a dense layer between two routed ones: the feed-forward is chosen layer by layer
+        ffs = [experts(0), dense(1), experts(2)]
+        layers = [LayerSpec("prenorm", attn(i), ff, {"mixer": norm(f"l{i}.n1"), "feed_forward": norm(f"l{i}.n2")})
+                  for i, ff in enumerate(ffs)]
+        io = dict(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size)
+        return ModelPlan(cfg.hidden_size, cfg.vocab_size, 128, PartSpec("table", io, {"weight": "emb"}), layers,
+                         [LayerRun(i) for i in range(3)], norm("final"), PartSpec("linear", io, {"weight": "head"}))
+
+    register_architecture("Toy2ForCausalLM", Toy2Config, make_plan)
+
+
+def toy2_plain(w, cfg, ids, store):
+    T, H, KVH, D = len(ids), cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+    rot = D // 2
+    ang = torch.from_numpy(toy2_angles(np.arange(T), rot))
+    cos, sin = torch.cos(ang), torch.sin(ang)
+
+    def turn(x):                                   # rotate-half over the first `rot` dimensions only
+        return torch.cat([plain.apply_rope(x[..., :rot], cos, sin), x[..., rot:]], dim=-1)
+
+    x = plain.embedding(w["emb"], torch.as_tensor(ids))
+    routed_to = []
+    for i in range(3):
+        p = f"l{i}."
+        h = store(plain.rms_norm(x, w[p + "n1"], cfg.eps))
+        q = store(turn(store(plain.linear(h, w[p + "q"])).reshape(T, H, D)))
+        k = store(turn(store(plain.linear(h, w[p + "k"])).reshape(T, KVH, D)))
+        v = store(plain.linear(h, w[p + "v"])).reshape(T, KVH, D)
+        x = x + store(plain.linear(store(plain.attention(q, k, v)), w[p + "o"]))
+        h = store(plain.rms_norm(x, w[p + "n2"], cfg.eps))
+        if i == 1:
+            a = store(plain.swiglu(store(plain.linear(h, w[p + "ffn.gate"])), store(plain.linear(h, w[p + "ffn.up"]))))
+            x = x + store(plain.linear(a, w[p + "ffn.down"]))
+            continue
+        logits = h @ w[p + "router"].t()
+        top = logits.argmax(dim=-1)
+        routed_to.append(top)
+        delta = torch.zeros_like(x)
+        for e in range(cfg.experts):
+            rows = (top == e).nonzero().flatten()
+            if rows.numel() == 0:
+                continue
+            pe = f"{p}e{e}."
+            a = store(plain.swiglu(store(plain.linear(h[rows], w[pe + "gate"])), store(plain.linear(h[rows], w[pe + "up"]))))
+            y = store(plain.linear(a, w[pe + "down"]))
+            delta[rows] = store(y * torch.sigmoid(logits[rows, e])[:, None])
+        x = x + delta
+    return plain.linear(store(plain.rms_norm(x, w["final"], cfg.eps)), w["head"]), routed_to
+
+
+def test_toy_position_encoding_and_routed_feed_forward(tmp_path):
+    """Registered from here, built from config.json, stepped in portions and one by one: a
+    position encoding that is neither a power law nor linear in the position (and turns
+    only half of each head), and a feed-forward that routes every token to one expert."""
+    from safetensors.torch import load_file
+
+    from fastllm_py_b200 import Model, StepEntry
+    from fastllm_py_b200.weights import write_model_folder
+
+    register_toy2()
+    cfg = Toy2Config()
+    folder = write_model_folder(cfg, tmp_path / "toy2", seed=9, std=0.15, norm_std=0.1)
+    weights = {k: v.float() for k, v in load_file(str(folder / "model.safetensors")).items()}
+    ids = np.random.default_rng(4).integers(0, cfg.vocab_size, 61).tolist()
+    want, routed = toy2_plain(weights, cfg, ids, plain.identity)
+    assert all(len(set(t.tolist())) == cfg.experts for t in routed), "the test should use every expert"
+    model = Model.load(folder, dtype="float32", page_size=8, max_tokens=128, max_requests=2,
+                       max_batched_tokens=64, max_model_len=96, cuda_graph=False)
+    eng = model.engine
+    eng.begin("r")
+    at = 0
+    for n in (23, 2, 1, 1, 19, 15):
+        logits = eng.step([StepEntry("r", ids[at:at + n], list(range(n)))]).cpu()
+        diff = float((logits - want[at:at + n]).abs().max())
+        assert diff <= 1e-4 * max(1.0, float(want.abs().max())), f"tokens {at}..{at + n}: {diff:.3e}"
+        at += n
+    eng.end("r")
+    eng.cache.check()
