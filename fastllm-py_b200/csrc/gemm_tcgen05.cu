@@ -126,6 +126,14 @@ __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// silu(g) * u with the fast exponential and division: the epilogue has a fixed budget per tile (the
+// next tile's MMAs), and the exact forms cost five times the instructions for digits that a
+// bfloat16 result cannot hold (relative error about 1e-6 against bfloat16's 4e-3).
+__device__ __forceinline__ float gated_act(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+
+// A barrier among the four epilogue warps only (hardware barrier 1; barrier 0 is __syncthreads).
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes
 // (64 bfloat16) in the 128-byte swizzle: 8-row groups are 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
@@ -156,11 +164,16 @@ struct TcSmem {
 
 // grid: (ceil(N / 128), ceil(M / BN), splits).  OutT: the type of C when
 // splits == 1; with splits > 1 float partial sums go to `partial[z][M][ld_partial]`.
-template <int BN, int STAGES, typename OutT>
+//
+// GATED (the SwiGLU feed-forward's first product, no K split): W holds the gate rows and, `gate_rows`
+// further down, the up rows; a CTA's 128-row weight tile is 64 gate rows and the 64 up rows of the
+// same features (two TMA boxes of 64 rows: map_w has 64-row boxes then), N counts features, and the
+// epilogue writes silu(gate) * up: the product's 2 x N columns never go to memory.
+template <int BN, int STAGES, typename OutT, bool GATED>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
     OutT* __restrict__ C, long ldc, float* __restrict__ partial, long ld_partial, int M, int N, int K,
-    int kb_per_split, int* __restrict__ status) {
+    int kb_per_split, int* __restrict__ status, int gate_rows) {
     using L = TcSmem<BN, STAGES>;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
     extern __shared__ unsigned char smem_raw[];
@@ -172,7 +185,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_n = blockIdx.x;            // which 128 output features
+    const int tile_n = blockIdx.x;            // which 128 output features (GATED: which 64)
     const int tile_m = blockIdx.y;            // which BN tokens
     const int num_kb = (K + TC_BK - 1) / TC_BK;
     const int kb_begin = blockIdx.z * kb_per_split;
@@ -211,7 +224,13 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
             for (int it = 0; it < ahead; ++it) {
                 unsigned char* a_dst = tiles + it * L::STAGE_BYTES;
                 mbar_expect_tx(&full_bar[it], L::STAGE_BYTES);
-                tma_load_2d(a_dst, &map_w, &full_bar[it], (kb_begin + it) * TC_BK, tile_n * TC_BM);
+                if (GATED) {
+                    tma_load_2d(a_dst, &map_w, &full_bar[it], (kb_begin + it) * TC_BK, tile_n * 64);
+                    tma_load_2d(a_dst + L::A_BYTES / 2, &map_w, &full_bar[it], (kb_begin + it) * TC_BK,
+                                gate_rows + tile_n * 64);
+                } else {
+                    tma_load_2d(a_dst, &map_w, &full_bar[it], (kb_begin + it) * TC_BK, tile_n * TC_BM);
+                }
             }
             pdl_wait();
             for (int it = 0; it < ahead; ++it) {
@@ -229,7 +248,12 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
                 unsigned char* b_dst = a_dst + L::A_BYTES;
                 mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
                 const int k0 = (kb_begin + it) * TC_BK;
-                tma_load_2d(a_dst, &map_w, &full_bar[s], k0, tile_n * TC_BM);
+                if (GATED) {
+                    tma_load_2d(a_dst, &map_w, &full_bar[s], k0, tile_n * 64);
+                    tma_load_2d(a_dst + L::A_BYTES / 2, &map_w, &full_bar[s], k0, gate_rows + tile_n * 64);
+                } else {
+                    tma_load_2d(a_dst, &map_w, &full_bar[s], k0, tile_n * TC_BM);
+                }
                 tma_load_2d(b_dst, &map_a, &full_bar[s], k0, tile_m * BN);
             }
         }
@@ -272,7 +296,50 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
             if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_ACC_WAIT); }
         }
         tc_fence_after();
-        if (ok) {
+        if (GATED) {
+            // Lanes 0..63 of the accumulator are gate features, 64..127 the same features' up
+            // values: the two sides trade values through shared memory (the ring is idle once the
+            // accumulator is complete), 16 tokens at a time.
+            // All four warps take the same decisions, so that the barrier below is always met.
+            if (!ok) *abort_flag = 1;
+            epilogue_sync();
+            ok = !*abort_flag;
+            const bool is_up = quarter >= 2;
+            const int col = (quarter & 1) * 32 + lane;               // feature within the CTA's 64
+            const int f = tile_n * 64 + col;
+            const uint32_t t_base = tmem_acc + ((uint32_t)(quarter * 32) << 16);
+            const int t0 = tile_m * BN;
+            float* xch = reinterpret_cast<float*>(tiles);            // [2][16 tokens][64 features]
+            if (ok) {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    if (t0 + c >= M) break;                           // uniform over the four warps
+                    uint32_t r[16];
+                    tmem_ld16(t_base + (uint32_t)c, r);
+                    tmem_ld_wait();
+                    // the gate warps finish the even tokens, the up warps the odd ones: each side hands
+                    // over the values the other needs (both factors rounded to the activation type
+                    // first, as the unfused route stores them)
+                    float* x = xch + ((c >> 4) & 1) * (16 * 64);
+                    const int mine = is_up ? 1 : 0;                    // parity of the tokens this warp finishes
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if ((j & 1) != mine)
+                            x[j * 64 + col] = to_f32<OutT>(from_f32<OutT>(__uint_as_float(r[j])));
+                    epilogue_sync();
+                    if (f < N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if ((j & 1) != mine) continue;
+                            const int t = t0 + c + j;
+                            const float own = to_f32<OutT>(from_f32<OutT>(__uint_as_float(r[j])));
+                            const float other = x[j * 64 + col];
+                            if (t < M) C[(long)t * ldc + f] = from_f32<OutT>(is_up ? gated_act(other, own) : gated_act(own, other));
+                        }
+                    }
+                }
+            }
+        } else if (ok) {
             const uint32_t t_base = tmem_acc + ((uint32_t)(quarter * 32) << 16);
             const int t0 = tile_m * BN;
 #pragma unroll 1
@@ -551,6 +618,8 @@ static int launch_tc_persistent(const CUtensorMap& map_w, const CUtensorMap& map
 #define TC2_STAGE_BYTES (2 * TC_BM * TC_BK * 2)             // 128 weight rows + 128 token rows
 #define TC2_TILE_BYTES (TC2_STAGES * TC2_STAGE_BYTES)
 #define TC2_SMEM (TC2_TILE_BYTES + 256 + 1024)
+#define TC2_XCH_BYTES (2 * 32 * 64 * 4)                      // GATED: two rounds of 32 tokens x 64 up values
+#define TC2_SMEM_GATED (TC2_SMEM + TC2_XCH_BYTES)
 #define TC2_PEER_MASK 0xFEFFFFFFu                          // clears the CTA-rank bit of a shared::cluster address
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -590,11 +659,13 @@ __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {    // arrive
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & TC2_PEER_MASK) : "memory");
 }
 
-template <typename OutT>
+// GATED as in gemm_tc_kernel: each CTA's 128 weight rows are 64 gate rows and the 64 up rows of the
+// same features, a pair's tile is 128 features wide, and the epilogue writes silu(gate) * up.
+template <typename OutT, bool GATED>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
     OutT* __restrict__ C, long ldc, int M, int N, int K, int tiles_n, int num_tiles,
-    int* __restrict__ status) {
+    int* __restrict__ status, int gate_rows) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full_bar = (uint64_t*)(tiles + TC2_TILE_BYTES);
@@ -603,6 +674,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    float* xch = reinterpret_cast<float*>(tiles + TC2_TILE_BYTES + 256);     // GATED only
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();                   // 0: leader
@@ -642,6 +714,17 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
         tc_raster(pair + i * num_pairs, tiles_n, num_tiles / tiles_n, tn, tm);
     };
 
+    // this CTA's 128 weight rows of a stage (GATED: 64 gate rows and the 64 up rows of the same features)
+    auto load_weights = [&](unsigned char* dst, uint64_t* bar, int kb, int tn) {
+        if (GATED) {
+            const int f0 = tn * 128 + (int)rank * 64;
+            tma_load_2d_pair(dst, &map_w, bar, kb * TC_BK, f0);
+            tma_load_2d_pair(dst + TC2_STAGE_BYTES / 4, &map_w, bar, kb * TC_BK, gate_rows + f0);
+        } else {
+            tma_load_2d_pair(dst, &map_w, bar, kb * TC_BK, tn * 256 + (int)rank * TC_BM);
+        }
+    };
+
     if (warp == 0) {
         if (lane == 0) {
             // ---- producer (both CTAs): this CTA's 128 weight rows and 128 token rows of each stage
@@ -651,8 +734,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
             tile_coords(0, tn, tm);
             for (int it = 0; it < ahead; ++it) {           // weights first: no kernel writes them
                 if (rank == 0) mbar_expect_tx(&full_bar[it], 2 * TC2_STAGE_BYTES);
-                tma_load_2d_pair(tiles + it * TC2_STAGE_BYTES, &map_w, &full_bar[it], kb * TC_BK,
-                                 tn * 256 + (int)rank * TC_BM);
+                load_weights(tiles + it * TC2_STAGE_BYTES, &full_bar[it], kb, tn);
                 if (++kb == num_kb) { kb = 0; tile_coords(++ti, tn, tm); }
             }
             pdl_wait();
@@ -672,7 +754,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
                 }
                 unsigned char* a_dst = tiles + s * TC2_STAGE_BYTES;
                 if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * TC2_STAGE_BYTES);
-                tma_load_2d_pair(a_dst, &map_w, &full_bar[s], kb * TC_BK, tn * 256 + (int)rank * TC_BM);
+                load_weights(a_dst, &full_bar[s], kb, tn);
                 tma_load_2d_pair(a_dst + TC2_STAGE_BYTES / 2, &map_a, &full_bar[s], kb * TC_BK,
                                  tm * 256 + (int)rank * TC_BM);
                 if (++kb == num_kb) { kb = 0; tile_coords(++ti, tn, tm); }
@@ -719,34 +801,73 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
     } else {
         // ---- epilogue warps 2..5 of both CTAs: this CTA's 128 output features of the pair's tile
         const int quarter = warp & 3;
-        bool ok = !*abort_flag;
+        bool ok = GATED ? true : !*abort_flag;
         pdl_wait();
         for (int i = 0; i < my_tiles && ok; ++i) {
             const int buf = i & 1;
             const uint32_t use = (uint32_t)(i >> 1);
-            if (!mbar_wait(&acc_full[buf], use & 1u, abort_flag)) {
-                if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_ACC_WAIT); }
+            bool got = mbar_wait(&acc_full[buf], use & 1u, abort_flag);
+            if (!got && !*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_ACC_WAIT); }
+            if (GATED) {                                    // the four warps decide together (they share a barrier below)
+                epilogue_sync();
+                got = !*abort_flag;
+            }
+            if (!got) {
                 ok = false;
                 break;
             }
             tc_fence_after();
             int tn, tm;
             tile_coords(i, tn, tm);
-            const int o = tn * 256 + (int)rank * TC_BM + quarter * 32 + lane;
             const int t0 = tm * 256;
             const uint32_t t_base = tmem_base + (uint32_t)(buf * 256) + ((uint32_t)(quarter * 32) << 16);
+            if (GATED) {
+                // accumulator lanes 0..63: gate features, 64..127: the same features' up values; the
+                // gate warps finish the even tokens, the up warps the odd ones, trading the values
+                // the other side needs through shared memory, 32 tokens at a time
+                const bool is_up = quarter >= 2;
+                const int col = (quarter & 1) * 32 + lane;
+                const int f = tn * 128 + (int)rank * 64 + col;
 #pragma unroll 1
-            for (int c = 0; c < 256; c += 32) {
-                if (t0 + c >= M) break;
-                uint32_t r[32];
-                tmem_ld16(t_base + (uint32_t)c, r);
-                tmem_ld16(t_base + (uint32_t)c + 16u, r + 16);
-                tmem_ld_wait();
-                if (o < N) {
+                for (int c = 0; c < 256; c += 32) {
+                    if (t0 + c >= M) break;                 // uniform over the four warps
+                    uint32_t r[32];
+                    tmem_ld16(t_base + (uint32_t)c, r);
+                    tmem_ld16(t_base + (uint32_t)c + 16u, r + 16);
+                    tmem_ld_wait();
+                    float* x = xch + ((c >> 5) & 1) * (32 * 64);
+                    const int mine = is_up ? 1 : 0;         // parity of the tokens this warp finishes
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int t = t0 + c + j;
-                        if (t < M) C[(long)t * ldc + o] = from_f32<OutT>(__uint_as_float(r[j]));
+                    for (int j = 0; j < 32; ++j)
+                        if ((j & 1) != mine)
+                            x[j * 64 + col] = to_f32<OutT>(from_f32<OutT>(__uint_as_float(r[j])));
+                    epilogue_sync();
+                    if (f < N) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if ((j & 1) != mine) continue;
+                            const int t = t0 + c + j;
+                            const float own = to_f32<OutT>(from_f32<OutT>(__uint_as_float(r[j])));
+                            const float other = x[j * 64 + col];
+                            if (t < M) C[(long)t * ldc + f] = from_f32<OutT>(is_up ? gated_act(other, own) : gated_act(own, other));
+                        }
+                    }
+                }
+            } else {
+                const int o = tn * 256 + (int)rank * TC_BM + quarter * 32 + lane;
+#pragma unroll 1
+                for (int c = 0; c < 256; c += 32) {
+                    if (t0 + c >= M) break;
+                    uint32_t r[32];
+                    tmem_ld16(t_base + (uint32_t)c, r);
+                    tmem_ld16(t_base + (uint32_t)c + 16u, r + 16);
+                    tmem_ld_wait();
+                    if (o < N) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int t = t0 + c + j;
+                            if (t < M) C[(long)t * ldc + o] = from_f32<OutT>(__uint_as_float(r[j]));
+                        }
                     }
                 }
             }
@@ -768,23 +889,24 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
     cluster_sync_all();
 }
 
-template <typename OutT>
+template <typename OutT, bool GATED = false>
 static int launch_tc_pair(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C, long ldc, int M, int N,
-                          int K, int num_sms, int* status, cudaStream_t stream) {
+                          int K, int num_sms, int* status, cudaStream_t stream, int gate_rows = 0) {
     static bool configured = false;
-    auto kernel = gemm_tc_pair_kernel<OutT>;
+    auto kernel = gemm_tc_pair_kernel<OutT, GATED>;
+    constexpr int smem = GATED ? TC2_SMEM_GATED : TC2_SMEM;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC2_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const int tiles_n = (N + 255) / 256;
+    const int tiles_n = GATED ? (N + 127) / 128 : (N + 255) / 256;
     const int num_tiles = tiles_n * ((M + 255) / 256);
     const int pairs = num_tiles < num_sms / 2 ? num_tiles : num_sms / 2;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs);
     cfg.blockDim = dim3(TC_THREADS);
-    cfg.dynamicSmemBytes = TC2_SMEM;
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -796,7 +918,8 @@ static int launch_tc_pair(const CUtensorMap& map_w, const CUtensorMap& map_a, vo
     cfg.attrs = attr;
     // Launched in plain stream order (no programmatic overlap with its neighbours): see the note in the kernel.
     cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, kernel, map_w, map_a, (OutT*)C, ldc, M, N, K, tiles_n, num_tiles, status);
+    return (int)cudaLaunchKernelEx(&cfg, kernel, map_w, map_a, (OutT*)C, ldc, M, N, K, tiles_n, num_tiles, status,
+                                   gate_rows);
 }
 
 // C[t, o] = sum over splits of partial[z][t][o], added in the order z = 0, 1, ...
@@ -847,21 +970,21 @@ static int make_map(CUtensorMap* map, const void* base, long rows, long cols, lo
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <int BN, int STAGES, typename OutT>
+template <int BN, int STAGES, typename OutT, bool GATED = false>
 static int launch_tc(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C, long ldc,
                      float* partial, long ld_partial, int M, int N, int K, int splits,
-                     int kb_per_split, int* status, cudaStream_t stream) {
+                     int kb_per_split, int* status, cudaStream_t stream, int gate_rows = 0) {
     using L = TcSmem<BN, STAGES>;
     static bool configured = false;
-    auto kernel = gemm_tc_kernel<BN, STAGES, OutT>;
+    auto kernel = gemm_tc_kernel<BN, STAGES, OutT, GATED>;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid((N + TC_BM - 1) / TC_BM, (M + BN - 1) / BN, splits);
+    dim3 grid(GATED ? (N + 63) / 64 : (N + TC_BM - 1) / TC_BM, (M + BN - 1) / BN, splits);
     return fl_launch(kernel, grid, dim3(TC_THREADS), (size_t)L::TOTAL, stream, map_w, map_a, (OutT*)C, ldc,
-                     partial, ld_partial, M, N, K, kb_per_split, status);
+                     partial, ld_partial, M, N, K, kb_per_split, status, gate_rows);
 }
 
 template <typename OutT>
@@ -972,6 +1095,34 @@ FL_API int fl_gemm_tc_partial(const void* A, long lda, const void* W, long ldw, 
                               long workspace_floats, int num_sms, int* status, cudaStream_t stream) {
     return gemm_tc_impl(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, bn, splits, workspace, workspace_floats,
                         num_sms, status, stream, 1);
+}
+
+// The SwiGLU feed-forward's first product with its activation: W holds the gate matrix [I, K] and
+// below it the up matrix [I, K]; C[M, I] = silu(A gate^T) * (A up^T), bfloat16.  Returns 0 when the
+// fused kernel was launched, -1 when this problem is not taken (the plan for the [2 I, K] product
+// splits K, or has no fused kernel): the caller then runs the product and the activation apart.
+FL_API int fl_gemm_tc_swiglu(const void* A, long lda, const void* W, long ldw, void* C, long ldc, int M, int I,
+                             int K, int num_sms, int* status, cudaStream_t stream) {
+    if (M <= 0 || I <= 0) return 0;
+    if (K <= 0) return (int)cudaErrorInvalidValue;
+    int bn = 0, splits = 0;
+    fl_gemm_tc_plan(M, 2 * I, K, num_sms, &bn, &splits);
+    if (splits != 1 || bn == 256) return -1;
+    if ((M + (bn > 256 ? 256 : bn) - 1) / (bn > 256 ? 256 : bn) > 65535) return (int)cudaErrorInvalidValue;
+    CUtensorMap map_w, map_a;
+    int rc = make_map(&map_w, W, 2L * I, K, ldw, 64);               // boxes of 64 weight rows
+    if (rc) return rc;
+    rc = make_map(&map_a, A, M, K, lda, bn > 256 ? TC_BM : bn);
+    if (rc) return rc;
+    if (bn == 512) return launch_tc_pair<bf16, true>(map_w, map_a, C, ldc, M, I, K, num_sms, status, stream, I);
+    const int kb = (K + TC_BK - 1) / TC_BK;
+    switch (bn) {
+        case 16: return launch_tc<16, 6, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I);
+        case 32: return launch_tc<32, 5, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I);
+        case 64: return launch_tc<64, 4, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I);
+        case 128: return launch_tc<128, 3, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I);
+    }
+    return -1;
 }
 
 // ------------------------------------------- entry point that allocates nothing

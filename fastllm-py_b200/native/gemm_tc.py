@@ -25,6 +25,9 @@ def _lib():
         lib.fl_gemm_tc_plan.argtypes = [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int),
                                         ctypes.POINTER(c_int)]
         lib.fl_gemm_tc_plan.restype = None
+        lib.fl_gemm_tc_swiglu.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
+                                          c_int, c_int, c_void_p, c_void_p]
+        lib.fl_gemm_tc_swiglu.restype = c_int
         _state["lib"] = lib
     return lib
 
@@ -127,6 +130,29 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int = 0, split
     if deferred:
         return Partial(ws, splits, m, n, -(-n // 4) * 4, a.device)
     return None
+
+
+def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    """out[M, I] = silu(a @ gate^T) * (a @ up^T) for w = [gate; up] stacked as [2 I, K], all
+    bfloat16, in one kernel (the activation in the product's epilogue).  Returns False, having
+    done nothing, when the kernel does not take the problem (its plan splits K)."""
+    m, k = a.shape
+    inter = w.shape[0] // 2
+    if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16
+            or w.shape[0] != 2 * inter or w.shape[1] != k or tuple(out.shape) != (m, inter)):
+        raise ops.KernelError(f"gemm_swiglu: {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}, "
+                              f"{a.dtype}/{w.dtype}/{out.dtype}")
+    if m == 0:
+        return True
+    lda, ldw = ops._ld(a), ops._ld(w)
+    if lda % 8 or ldw % 8 or a.data_ptr() % 16 or w.data_ptr() % 16:
+        return False
+    rc = _lib().fl_gemm_tc_swiglu(ops._ptr(a), lda, ops._ptr(w), ldw, ops._ptr(out), ops._ld(out), m, inter, k,
+                                  _num_sms(a.device), ops._ptr(status_word(a.device)), ops._stream())
+    if rc == -1:
+        return False
+    ops._check(rc, "gemm_tcgen05 (gated)")
+    return True
 
 
 class TensorCoreLinear:

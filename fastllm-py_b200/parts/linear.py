@@ -46,3 +46,13 @@ class Linear:
                 return self._tc.forward(a, out, defer)
         ops.gemm_simt(a, self.weight, out)
         return None
+
+    def forward_gated(self, a: torch.Tensor, out: torch.Tensor) -> bool:
+        """For a Linear that stacks a gate and an up matrix: out = silu(a gate^T) * (a up^T)
+        in one tensor-core kernel.  False (nothing done) when that kernel does not apply; the
+        caller then takes `forward` and the activation kernel."""
+        if a.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and self.weight.is_contiguous():
+            from .. import native
+            if native.tensor_core_gemm_enabled():
+                return native.gemm_tc.gemm_swiglu(a, self.weight, out)
+        return False

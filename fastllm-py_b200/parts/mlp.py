@@ -36,9 +36,11 @@ class SwiGLU(Part):
     def forward(self, h, out, step):
         n = h.shape[0]
         dt = self.ctx.dtype
+        act = step.workspace.rows("ffn_act", n, self.inter, dt)
+        if self.gate_up.forward_gated(h, act):               # product and activation in one kernel
+            return self.down.forward(act, out, defer=True)
         gu = step.workspace.rows("gate_up", n, 2 * self.inter, dt)
         partial = self.gate_up.forward(h, gu, defer=True)
-        act = step.workspace.rows("ffn_act", n, self.inter, dt)
         if partial is None:
             ops.swiglu(gu, act)
         else:

@@ -432,6 +432,42 @@ def test_embedding_kernel_reports_bad_ids():
     assert int(status.item()) in (3, 5)                        # 1 + index of a bad id
 
 
+@pytest.mark.parametrize("m", [1, 7, 16, 50, 100, 129, 300, 513])
+@pytest.mark.parametrize("inter, k", [(11048, 320), (9728, 72)])
+def test_gate_up_product_with_swiglu_epilogue(m, inter, k):
+    """silu(a gate^T) * (a up^T) written by the product's epilogue (one-tile kernel for few
+    tokens, CTA pairs for many), against the product and the activation done apart; an
+    intermediate size that is no multiple of the 64-feature tiles; nothing written outside."""
+    from fastllm_py_b200.native import gemm_tc
+
+    g = torch.Generator(device="cpu").manual_seed(m + inter + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, k, generator=g) * k ** -0.5).to(torch.bfloat16)
+    gu = (a.float() @ w.float().t()).to(torch.bfloat16).float()
+    ref = gu[:, :inter] / (1.0 + torch.exp(-gu[:, :inter])) * gu[:, inter:]
+    out = torch.full((m, inter + 5), -5.0, dtype=torch.bfloat16, device=DEV)
+    done = gemm_tc.gemm_swiglu(a.to(DEV), w.to(DEV), out[:, :inter])
+    assert done, "this size should be taken by the fused kernel"
+    torch.cuda.synchronize()
+    assert int(gemm_tc.status_word(torch.device(DEV)).item()) == 0
+    assert torch.all(out[:, inter:] == -5.0), "wrote outside the output columns"
+    got = out[:, :inter].float().cpu()
+    # the factors may round to the neighbouring bfloat16 (another summation order), hence a few ulps
+    tol = 2 ** -6 * float(ref.abs().max()) + 1e-3
+    assert float((got - ref).abs().max()) <= tol
+
+
+def test_gate_up_product_with_swiglu_epilogue_declines_split_problems():
+    from fastllm_py_b200.native import gemm_tc
+
+    a = torch.randn(4, 4096, device=DEV).to(torch.bfloat16)
+    w = torch.randn(2 * 256, 4096, device=DEV).to(torch.bfloat16)      # few tiles: the plan splits K
+    out = torch.full((4, 256), -5.0, dtype=torch.bfloat16, device=DEV)
+    assert gemm_tc.gemm_swiglu(a, w, out) is False
+    torch.cuda.synchronize()
+    assert torch.all(out == -5.0)
+
+
 @pytest.mark.parametrize("m, n, k", [(256, 256, 64), (300, 515, 200), (1024, 768, 1032), (257, 130, 72), (2048, 1024, 512)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_tensor_core_gemm_cta_pairs(m, n, k, out_dtype):
