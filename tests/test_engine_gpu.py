@@ -172,6 +172,35 @@ def test_weights_stored_in_32_bit_stay_so(tmp_path):
     compare(got, ref, tol, "float32 weights under bfloat16 activations")
 
 
+def test_wide_feed_forward_takes_the_fused_gate_up_kernels(tmp_path):
+    """An intermediate size large enough that the gate|up product is planned without a K split:
+    prompts then go through the CTA-pair kernel with the SwiGLU epilogue, decode steps through
+    the one-tile kernel with it; compared in every cut with the plain implementation."""
+    from fastllm_py_b200.config import LlamaConfig
+    from fastllm_py_b200.native import gemm_tc
+    from fastllm_py_b200.weights import write_model_folder
+    from fastllm_py_b200 import Model
+
+    cfg = LlamaConfig(architecture="LlamaForCausalLM", num_layers=2, hidden_size=256, num_heads=2,
+                      num_kv_heads=1, head_dim=128, intermediate_size=9640, vocab_size=1000,
+                      rope_theta=10000.0, rope_scaling=None, rms_norm_eps=1e-5,
+                      max_position_embeddings=1024, tie_word_embeddings=True)
+    for m in (1, 4, 300):
+        assert gemm_tc.plan(m, 2 * cfg.intermediate_size, cfg.hidden_size, 148)[1] == 1
+    folder = write_model_folder(cfg, tmp_path / "wide", seed=8, std=0.03, norm_std=0.05)
+    rng = np.random.default_rng(21)
+    requests = {"w0": rng.integers(0, 1000, size=330).tolist(), "w1": rng.integers(0, 1000, size=90).tolist()}
+    weights, config = plain.load_folder(folder)
+    ref = {r: plain.forward(weights, config, t, store=plain.store_bf16) for r, t in requests.items()}
+    exact = {r: plain.forward(weights, config, t) for r, t in requests.items()}
+    tol = 2.0 * max(float((ref[r] - exact[r]).abs().max()) for r in ref) + 1e-3
+    model = Model.load(folder, dtype="bfloat16", page_size=16, max_tokens=1024, max_requests=4,
+                       max_batched_tokens=512, max_model_len=512, cuda_graph=False)
+    for cut in ("whole", "tail", "portions", "mixed"):
+        got = replay.run_in_process(model.engine, CUTS[cut](requests))
+        compare(got, ref, tol, f"wide {cut}")
+
+
 def test_medium_model_reaches_the_large_shape_kernels(tmp_path):
     """A model with head size 128, grouped heads and widths in the hundreds, so that whole prompts of
     several hundred tokens go through the persistent tensor-core product and the tcgen05 attention,
