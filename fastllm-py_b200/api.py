@@ -112,8 +112,10 @@ class Model:
         self.sampler = Sampler(self.decoder.ctx.device, ec.max_requests)
 
     # ------------------------------------------------------------ generation
-    def scheduler(self, token_budget: int | None = None) -> Scheduler:
-        return Scheduler(self.engine, self.sampler, token_budget)
+    def scheduler(self, token_budget: int | None = None, run_ahead: bool = True) -> Scheduler:
+        """`run_ahead`: launch a decode step before the host has read the tokens of the one
+        before it (they are taken from the sampler's output on the device); same tokens out."""
+        return Scheduler(self.engine, self.sampler, token_budget, run_ahead)
 
     def generate(self, token_ids, max_new_tokens: int = 32, temperature: float = 0.0,
                  use_graph: bool = True, stop_ids=None, top_p: float = 1.0, top_k: int = 0,

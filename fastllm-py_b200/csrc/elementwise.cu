@@ -31,15 +31,18 @@ static inline bool vec4_ok(int dim, const void* base, long ld, size_t elem) {
 // ------------------------------------------------------------------ embedding
 // out[t, :] = table[ids[t], :] as float (the residual stream is float in both
 // precisions).  An id outside [0, vocab) writes zeros and records 1 + t in
-// *status; it never reads outside the table.
+// *status; it never reads outside the table.  A negative id -1 - r, when `fed`
+// is given, stands for fed[r]: a token that an earlier kernel of the stream
+// chose (the sampler's output row r) and the host has not read yet.
 template <typename TT>
 __global__ void embed_kernel(const TT* __restrict__ table, long table_ld, const int* __restrict__ ids,
                              float* __restrict__ out, long out_ld, int hidden, int vocab,
-                             int* __restrict__ status, int vec_ok) {
+                             int* __restrict__ status, int vec_ok, const int* __restrict__ fed, int n_fed) {
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x;
-    const int id = ids[t];
+    int id = ids[t];
+    if (id < 0 && fed != nullptr && -1 - id < n_fed) id = fed[-1 - id];
     float* o = out + (long)t * out_ld;
     if (id < 0 || id >= vocab) {
         if (threadIdx.x == 0) atomicCAS(status, 0, t + 1);
@@ -59,13 +62,13 @@ __global__ void embed_kernel(const TT* __restrict__ table, long table_ld, const 
 }
 
 FL_API int fl_embed(const void* table, int table_dtype, long table_ld, const int* ids, float* out,
-                    long out_ld, int n_tokens, int hidden, int vocab, int* status,
+                    long out_ld, int n_tokens, int hidden, int vocab, int* status, const int* fed, int n_fed,
                     cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const int vec = vec4_ok(hidden, table, table_ld, table_dtype == FL_F32 ? 4 : 2) && vec4_ok(hidden, out, out_ld, 4);
     FL_DISPATCH(table_dtype, TT,
                 return fl_launch(embed_kernel<TT>, dim3(n_tokens), dim3(256), 0, stream, (const TT*)table,
-                                 table_ld, ids, out, out_ld, hidden, vocab, status, vec));
+                                 table_ld, ids, out, out_ld, hidden, vocab, status, vec, fed, n_fed));
     return 0;
 }
 

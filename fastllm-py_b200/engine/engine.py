@@ -48,6 +48,9 @@ class Engine:
         self.no_rotation = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.vocab = decoder.vocab
         self.steps_run = 0
+        # An int32 device tensor (the sampler's output) from which the embedding takes tokens that
+        # the host has not read yet: a step may name such a token as -1 - row.  None: not offered.
+        self.token_feed = None
         self.use_graph = bool(config.cuda_graph)
         self._graphs: dict = {}          # step shape -> (graph, logits view, kernels in it)
         self._warmed: set = set()
@@ -94,7 +97,15 @@ class Engine:
             if rc.seq_len + len(e.tokens) > self.max_model_len:
                 raise ValueError(f"request {e.request_id!r} would reach {rc.seq_len + len(e.tokens)} "
                                  f"tokens; the engine's longest sequence is {self.max_model_len}")
-            if min(e.tokens) < 0 or max(e.tokens) >= self.vocab:
+            lowest = min(e.tokens)
+            if lowest < 0 and self.token_feed is not None:
+                # -1 - r: the token the sampler chose in row r of its last launch, not read back yet
+                lowest = -1 - lowest
+                if lowest >= self.token_feed.numel():
+                    raise ValueError(f"request {e.request_id!r}: fed-token row {lowest} is outside the "
+                                     f"feed's {self.token_feed.numel()} rows")
+                lowest = 0
+            if lowest < 0 or max(e.tokens) >= self.vocab:
                 raise ValueError(f"request {e.request_id!r}: a token id is outside the "
                                  f"vocabulary of {self.vocab}")
             for w in e.want:
@@ -165,7 +176,7 @@ class Engine:
             status=self.status, workspace=self.workspace, no_rotation=self.no_rotation,
             q_lens=q_lens, ctx_lens=ctx_lens, slots_host=slots_host,
             max_q_len=max(q_lens), max_seq_len=max(c + q for c, q in zip(ctx_lens, q_lens)),
-            n_decode_tokens=n_dec,
+            n_decode_tokens=n_dec, token_feed=self.token_feed,
             rows_identity=(m == n_tokens and bool((rows[:m] == np.arange(m)).all())))
         step.decode_splits = self._decode_splits(step)
         step._views = build_views(cache, buf, n_tokens, n)
@@ -207,7 +218,8 @@ class Engine:
         inside the graph."""
         from ..native import ops
 
-        key = (step.n_tokens, step.decode_splits, self.decoder.graph_key(step))
+        feed = None if self.token_feed is None else self.token_feed.data_ptr()
+        key = (step.n_tokens, step.decode_splits, self.decoder.graph_key(step), feed)
         entry = self._graphs.get(key)
         if entry is None:
             if key not in self._warmed:

@@ -20,6 +20,19 @@ queue, and when it is admitted again its prompt and the tokens it already
 produced are recomputed as one prompt (its output so far is kept; with a fixed
 seed its sampling continues where it stopped, because the generator is kept
 too).  While any request was pushed out in a step, no new request is admitted.
+
+Running ahead.  In the steady state (every running request decoding, nobody
+waiting, pages at hand) the next step does not need the host to know the tokens
+just chosen: they sit in the sampler's output on the device, and the embedding
+kernel can take them from there.  The scheduler then launches step n + 1 before
+it reads the tokens of step n, so the host's share of a step (reading tokens,
+finishing requests, building and uploading the next batch) runs while the GPU
+works, instead of between two steps.  A request that ends by its length is
+left out of step n + 1 beforehand; one that ends by a stop token is found out
+one step late: its row of step n + 1 is computed for nothing and dropped.
+`step()` returns the tokens of the step it collected, which is then the one
+launched a call earlier.  Requests with penalties (which need the tokens on the
+host) and engines or samplers without the device path run without it.
 """
 from __future__ import annotations
 
@@ -62,8 +75,16 @@ class StepOutput:
     finished: bool
 
 
+@dataclass
+class _InFlight:
+    """A launched step whose chosen tokens the host has not read yet."""
+    sampled: list                      # requests with a logits row, in row order
+    handle: object                     # what the sampler's collect() takes; None: tokens already here
+    tokens: list | None = None
+
+
 class Scheduler:
-    def __init__(self, engine, sampler, token_budget: int | None = None):
+    def __init__(self, engine, sampler, token_budget: int | None = None, run_ahead: bool = True):
         self.engine = engine
         self.sampler = sampler
         self.cache = engine.cache
@@ -72,7 +93,15 @@ class Scheduler:
         self.running: list = []                    # in order of admission
         self.requests: dict = {}
         self._next_id = 0
-        self.stats = {"steps": 0, "pushed_out": 0, "prefill_tokens": 0, "decode_tokens": 0}
+        self.stats = {"steps": 0, "pushed_out": 0, "prefill_tokens": 0, "decode_tokens": 0,
+                      "steps_ahead": 0, "rows_dropped": 0}
+        self._flight: _InFlight | None = None
+        # the device path for tokens: the engine's embedding reads the sampler's output
+        feed = getattr(sampler, "out", None)
+        self.run_ahead = bool(run_ahead and feed is not None and hasattr(engine, "token_feed")
+                              and hasattr(sampler, "launch") and hasattr(sampler, "collect"))
+        if self.run_ahead:
+            engine.token_feed = feed
 
     # ------------------------------------------------------------- requests
     def add_request(self, prompt, max_new_tokens: int = 32, sampling: SamplingParams | None = None,
@@ -104,7 +133,7 @@ class Scheduler:
         return request_id
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting or self.running or self._flight is not None)
 
     # ------------------------------------------------------------- planning
     def _push_out(self, req: Request) -> None:
@@ -163,12 +192,24 @@ class Scheduler:
 
     # ----------------------------------------------------------------- step
     def step(self) -> list:
-        """Run one step of the engine; returns a StepOutput for each token produced."""
-        planned = self.plan()
-        if not planned:
-            if self.has_work():
-                raise RuntimeError("the scheduler has requests but can run none of them")
-            return []
+        """Launch what can be launched, read one step's tokens; returns a StepOutput for
+        each token read.  Without running ahead the step launched is the step read."""
+        if self._flight is None:
+            planned = self.plan()
+            if not planned:
+                if self.has_work():
+                    raise RuntimeError("the scheduler has requests but can run none of them")
+                return []
+            self._flight = self._launch(planned)
+        flight, self._flight = self._flight, None
+        if self.run_ahead:
+            ahead = self._plan_ahead(flight)
+            if ahead:
+                self._flight = self._launch_ahead(flight, ahead)
+        return self._collect(flight)
+
+    def _launch(self, planned) -> _InFlight:
+        """A step whose tokens are all known to the host."""
         entries, sampled = [], []
         for req, n in planned:
             lp = len(req.prompt)
@@ -189,9 +230,51 @@ class Scheduler:
         logits = self.engine.step(entries)
         for req, n in planned:
             req.computed += n
-        tokens = self.sampler.sample(logits, [r.sampling_state for r in sampled])
+        states = [r.sampling_state for r in sampled]
+        if hasattr(self.sampler, "launch"):
+            return _InFlight(sampled, self.sampler.launch(logits, states))
+        return _InFlight(sampled, None, self.sampler.sample(logits, states))
+
+    def _plan_ahead(self, flight: _InFlight) -> list:
+        """The requests of the step after `flight`, if that step can be launched before
+        `flight`'s tokens are read: [(request, its row in flight)], or [] to wait."""
+        if self.waiting or not flight.sampled or len(flight.sampled) != len(self.running):
+            return []
+        row_of = {id(r): i for i, r in enumerate(flight.sampled)}
+        ahead, taken = [], 0
+        for req in self.running:                       # every running request must be one just sampled
+            row = row_of.get(id(req))
+            if row is None or req.sampling.penalized:
+                return []
+            produced = len(req.output) + 1             # with the token that is still on the device
+            if produced >= req.max_new_tokens or len(req.prompt) + produced >= self.engine.max_model_len:
+                continue                               # ends with that token: no next step for it
+            rc = self.cache.live[req.request_id]
+            if not self.cache.can_extend(rc, 1, spare=taken):
+                return []                              # pages are short: decide with all tokens at hand
+            taken += self.cache.pages_missing(rc, 1)
+            ahead.append((req, row))
+        return ahead
+
+    def _launch_ahead(self, flight: _InFlight, ahead) -> _InFlight:
+        """The next decode step of `ahead`'s requests; each one's token is named by its row
+        in the sampler's last output (-1 - row), where the embedding kernel finds it."""
+        entries = [StepEntry(req.request_id, [-1 - row], [0]) for req, row in ahead]
+        logits = self.engine.step(entries)
+        sampled = [req for req, _ in ahead]
+        for req in sampled:
+            req.computed += 1
+        self.stats["decode_tokens"] += len(sampled)
+        self.stats["steps_ahead"] += 1
+        return _InFlight(sampled, self.sampler.launch(logits, [r.sampling_state for r in sampled]))
+
+    def _collect(self, flight: _InFlight) -> list:
+        tokens = flight.tokens if flight.handle is None else self.sampler.collect(flight.handle)
         outputs = []
-        for req, tok in zip(sampled, tokens):
+        for req, tok in zip(flight.sampled, tokens):
+            if req.finished:                           # ended by a stop token while this step was under way
+                self.stats["rows_dropped"] += 1
+                continue
             req.output.append(tok)
             done = None
             if tok in req.stop_ids:

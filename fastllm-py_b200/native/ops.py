@@ -85,15 +85,17 @@ def _fn(lib_name: str, fn_name: str, argtypes, defines=None):
 
 # ---------------------------------------------------------------- elementwise
 
-def embed(table, ids, out, status):
-    """out[t] = table[ids[t]] as float32; an id outside the table sets status[0] = t + 1."""
-    _require_cuda(table, ids, out, status)
+def embed(table, ids, out, status, fed=None):
+    """out[t] = table[ids[t]] as float32; an id outside the table sets status[0] = t + 1.
+    With `fed` (int32 on the device), an id -1 - r is replaced by fed[r]."""
+    _require_cuda(table, ids, out, status, fed)
     fn = _fn("elementwise", "fl_embed", [c_void_p, c_int, c_long, c_void_p, c_void_p, c_long, c_int,
-                                         c_int, c_int, c_void_p, c_void_p])
-    if out.dtype != torch.float32 or ids.dtype != torch.int32:
-        raise KernelError("embed: out must be float32 and ids int32")
+                                         c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+    if out.dtype != torch.float32 or ids.dtype != torch.int32 or (fed is not None and fed.dtype != torch.int32):
+        raise KernelError("embed: out must be float32, ids (and fed) int32")
     _check(fn(_ptr(table), dtype_code(table), _ld(table), _ptr(ids), _ptr(out), _ld(out),
-              ids.numel(), table.shape[1], table.shape[0], _ptr(status), _stream()), "embed")
+              ids.numel(), table.shape[1], table.shape[0], _ptr(status), _ptr(fed),
+              0 if fed is None else fed.numel(), _stream()), "embed")
 
 
 def rmsnorm(x, weight, out, eps, rows=None):

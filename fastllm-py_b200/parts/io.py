@@ -30,7 +30,7 @@ class Embedding(Part):
         self.table = tensors["weight"]
 
     def forward(self, step, out):
-        ops.embed(self.table, step.token_ids, out, step.status)
+        ops.embed(self.table, step.token_ids, out, step.status, getattr(step, "token_feed", None))
 
 
 @register_part("head", "linear")

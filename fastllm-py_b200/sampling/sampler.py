@@ -76,7 +76,10 @@ class Sampler:
         self.host_np = self.host.numpy()
         self.dev = torch.zeros(self.nbytes, dtype=torch.uint8, device=device)
         self.out = torch.zeros(max_rows, dtype=torch.int32, device=device)
-        self.out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin)
+        # two host buffers: a launch may follow before the one before it was collected
+        self.out_host = [torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self._launches = 0
+        self._params_uploaded = None                     # event: the staging area may be rewritten after it
 
     def _host(self, name):
         off, dt = self.offsets[name]
@@ -91,16 +94,25 @@ class Sampler:
         """`logits` [m, vocab] float32 on the device (modified in place by
         penalties); `states` the m requests' SamplingState.  Returns m token ids
         and records them in the states."""
+        return self.collect(self.launch(logits, states))
+
+    def launch(self, logits: torch.Tensor, states: list):
+        """Enqueues the choice of one token per row and its copy to the host; returns
+        a handle for `collect`.  The chosen ids also stay in `self.out[:m]` on the
+        device until the next launch.  Penalties use the tokens recorded so far, so
+        a request with penalties must be collected before it is launched again."""
         m = logits.shape[0]
         if m != len(states):
             raise ValueError(f"{m} logits rows for {len(states)} requests")
         if m == 0:
-            return []
+            return (None, None, states)
         if m > self.max_rows:
             raise ValueError(f"{m} rows to sample; the sampler was made for {self.max_rows}")
         any_penalty = any(s.params.penalized and s.counts for s in states)
         any_random = any(not s.params.greedy for s in states)
         if any_penalty or any_random:
+            if self._params_uploaded is not None:
+                self._params_uploaded.synchronize()      # the last upload has left the staging area
             u, t = self._host("uniform"), self._host("temperature")
             tp, mp, tk = self._host("top_p"), self._host("min_p"), self._host("top_k")
             rep, fr, pr = self._host("repetition"), self._host("frequency"), self._host("presence")
@@ -111,6 +123,9 @@ class Sampler:
                 tp[i], mp[i], tk[i] = p.top_p, p.min_p, p.top_k
                 rep[i], fr[i], pr[i] = p.repetition_penalty, p.frequency_penalty, p.presence_penalty
             self.dev.copy_(self.host, non_blocking=True)
+            if self._params_uploaded is None:
+                self._params_uploaded = torch.cuda.Event()
+            self._params_uploaded.record()
         if any_penalty:
             items = [(i, tok, cnt) for i, s in enumerate(states) if s.params.penalized
                      for tok, cnt in s.counts.items()]
@@ -123,9 +138,20 @@ class Sampler:
                        self._dev("top_p", m), self._dev("min_p", m), self._dev("uniform", m))
         else:
             ops.sample(logits, out)
-        self.out_host[:m].copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        tokens = self.out_host[:m].tolist()
+        host = self.out_host[self._launches & 1]
+        self._launches += 1
+        host[:m].copy_(out, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return (host, done, states)
+
+    def collect(self, handle) -> list:
+        """Waits for a launch's token ids, records them in the states and returns them."""
+        host, done, states = handle
+        if host is None:
+            return []
+        done.synchronize()
+        tokens = host[:len(states)].tolist()
         for s, tok in zip(states, tokens):
             s.record(tok)
         return tokens

@@ -232,3 +232,43 @@ def test_sampling_options_through_generate(model_folders):
         want.append(tok)
         ids.append(tok)
     assert got == want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_ahead_changes_no_token(dtype, model_folders):
+    """Decode steps launched before the tokens of the step before were read (the embedding
+    takes them from the sampler's output on the device): same tokens as step by step, with
+    requests of different lengths, one ended by a stop token in mid-flight (its row of the
+    step under way is dropped), a late arrival, greedy and seeded sampling side by side."""
+    from fastllm_py_b200.sampling import SamplingParams
+
+    name = "tiny_b"
+    model = model_for(name, model_folders[name], dtype)
+    prompts = prompts_of(name, [7, 21, 40, 12, 3], seed=14)
+    lengths = [30, 9, 22, 30, 17]
+    params = [SamplingParams(), SamplingParams(temperature=0.8, seed=5), SamplingParams(),
+              SamplingParams(temperature=1.1, top_k=20, seed=6), SamplingParams()]
+    def run(run_ahead, stop=None):
+        sched = model.scheduler(run_ahead=run_ahead)
+        ids = [sched.add_request(p, n, s, stop_ids=[stop] if (i == 3 and stop is not None) else ())
+               for i, (p, n, s) in enumerate(zip(prompts[:4], lengths, params))]
+        steps = 0
+        while sched.has_work():
+            sched.step()
+            steps += 1
+            if steps == 24:                                # a late arrival breaks the steady state
+                ids.append(sched.add_request(prompts[4], lengths[4], params[4]))
+        return [sched.requests[i].output for i in ids], dict(sched.stats)
+
+    free = run(False)[0][3]                                # the sampled request, run to its length
+    at = next(k for k in range(8, 22) if free.index(free[k]) == k)
+    stop = free[at]                                        # it ends by this token, in the steady state
+
+    want, plain_stats = run(False, stop)
+    got, stats = run(True, stop)
+    assert plain_stats["steps_ahead"] == 0
+    assert stats["steps_ahead"] >= 10 and stats["rows_dropped"] >= 1
+    assert got == want
+    assert want[3] == free[:at + 1]
+    model.engine.cache.check()
+    assert not model.engine.cache.live
