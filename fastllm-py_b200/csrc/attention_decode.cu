@@ -349,8 +349,9 @@ __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_mma_kernel(
     int page_shift, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req,
     const int* __restrict__ positions, const int* __restrict__ tok_list, int n_heads, int n_kv_heads,
     int window, float scale_log2e, int n_splits, float* __restrict__ partial) {
-    pdl_wait();
-    pdl_trigger();
+    // What follows up to pdl_wait() reads nothing that the preceding kernels of the step write: the
+    // step's tables, and keys and values of EARLIER positions (the kernel before this one writes the
+    // cache at the tokens' own positions only).  It runs while that kernel is still at work.
     extern __shared__ __align__(16) unsigned char atm_raw[];
     const int li = blockIdx.x;
     const int t = tok_list ? tok_list[li] : li;
@@ -409,8 +410,18 @@ __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_mma_kernel(
             atm_cp16(vd + r * ATM_DP + ch * 8, v_cache + a + ch * 8, real);
         }
     };
+    // the first chunks: those that end before the token's own position may be asked for at once
+    int st = 0;
 #pragma unroll
-    for (int st = 0; st < ATM_STAGES; ++st) {
+    for (; st < ATM_STAGES; ++st) {
+        const int c = c_begin + st;
+        if (c >= c_end || warp_begin + c * ATM_CHUNK + ATM_CHUNK - 1 >= pos) break;
+        fetch(c);
+        atm_commit();
+    }
+    pdl_wait();
+    pdl_trigger();
+    for (; st < ATM_STAGES; ++st) {
         if (c_begin + st < c_end) fetch(c_begin + st);
         atm_commit();
     }
