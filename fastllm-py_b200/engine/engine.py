@@ -53,7 +53,8 @@ class Engine:
         self.token_feed = None
         self.use_graph = bool(config.cuda_graph)
         self._graphs: dict = {}          # step shape -> (graph, logits view, kernels in it)
-        self._warmed: set = set()
+        self._warmed: dict = {}          # step shape -> times seen before its capture
+        self.max_graphs = 64
         self._bt_rows: list = [None] * config.max_requests   # (request uid, table version) last written per row
 
     # -------------------------------------------------------------- requests
@@ -199,8 +200,8 @@ class Engine:
         engine buffer and is overwritten by the next step."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         step = self.prepare(entries)
-        if self.use_graph and step.max_q_len == 1 and step.n_wanted == step.n_tokens:
-            logits = self._decode_with_graph(step)
+        if self.use_graph and self.decoder.graph_safe:
+            logits = self._with_graph(step)
         else:
             logits = self.decoder.forward(step)
         for e in entries:
@@ -208,23 +209,43 @@ class Engine:
         self.steps_run += 1
         return logits
 
-    def _decode_with_graph(self, step: StepContext) -> torch.Tensor:
-        """A decode-only step (one token per request, every row wanted) replays a
-        CUDA graph captured for its shape.  The first step of a shape runs
-        eagerly (it sizes every buffer), the second is captured, later ones are
-        replayed: the step's inputs already sit in fixed device buffers, so a
-        replay needs nothing but the upload that `prepare` did.  This is the
+    def _with_graph(self, step: StepContext) -> torch.Tensor:
+        """A step replays a CUDA graph captured for its shape.  The first step of
+        a shape runs eagerly (it sizes every buffer), a later one is captured,
+        the ones after it are replayed: the step's inputs already sit in fixed
+        device buffers, so a replay needs nothing but the upload that `prepare`
+        did.  The shape is everything that the launches depend on: the numbers
+        of tokens, requests, single-token requests and wanted rows, the split
+        count of the decode attention, and what the mixers add.  A capture
+        costs about as much as twenty steps save, so it is made where a shape
+        is sure to come again: decode-only steps (hundreds alike; this is the
         captured decode step of fastllm_py/batched.py:230-275 with the LM head
-        inside the graph."""
+        inside the graph) at their second occurrence, a lone request's prompt
+        portion (equal portions of long prompts) at its third; other mixed
+        steps run eagerly.  The least recently used graphs are dropped beyond
+        `max_graphs`."""
         from ..native import ops
 
         feed = None if self.token_feed is None else self.token_feed.data_ptr()
-        key = (step.n_tokens, step.decode_splits, self.decoder.graph_key(step), feed)
-        entry = self._graphs.get(key)
+        key = (step.n_tokens, step.n_requests, step.n_decode_tokens, step.n_wanted, step.rows_identity,
+               step.decode_splits, self.decoder.graph_key(step), feed)
+        entry = self._graphs.pop(key, None)
+        if entry is not None:
+            self._graphs[key] = entry                       # most recently used last
         if entry is None:
-            if key not in self._warmed:
-                self._warmed.add(key)
+            if step.max_q_len == 1 and step.n_wanted == step.n_tokens:
+                capture_at = 2
+            elif step.n_requests == 1:
+                capture_at = 3
+            else:
                 return self.decoder.forward(step)
+            if len(self._warmed) > 4096:
+                self._warmed.clear()
+            seen = self._warmed[key] = self._warmed.get(key, 0) + 1
+            if seen < capture_at:
+                return self.decoder.forward(step)
+            while len(self._graphs) >= self.max_graphs:
+                self._graphs.pop(next(iter(self._graphs)))
             graph = torch.cuda.CUDAGraph()
             before = ops.counter.launches
             with torch.cuda.graph(graph):

@@ -94,6 +94,12 @@ class Decoder:
                     needs[i] = need
         return needs
 
+    @property
+    def graph_safe(self) -> bool:
+        """False when some part says that its forward decides things on the host from the
+        step's host copies (attribute `graph_safe = False`): its steps are never captured."""
+        return all(getattr(p, "graph_safe", True) for p in self.all_parts())
+
     def graph_key(self, step):
         """What, beside the number of tokens, fixes the launch shapes of a
         decode-only step: each mixer may add its own (a bucket of the longest

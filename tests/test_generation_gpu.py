@@ -135,6 +135,41 @@ def test_graph_replay_equals_eager_bit_for_bit(model_folders):
             assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graph_replay_of_prompt_portions(dtype, model_folders):
+    """Equal portions of a long prompt are captured at their third occurrence and replayed;
+    mixed steps run eagerly; bit for bit as without graphs either way."""
+    from fastllm_py_b200 import StepEntry
+
+    name = "tiny_c"
+    cfg = tiny.CONFIGS[name]["config"]
+    rng = np.random.default_rng(31)
+    long_a = rng.integers(0, cfg.vocab_size, size=160).tolist()
+    long_b = rng.integers(0, cfg.vocab_size, size=160).tolist()
+    rows = {}
+    for use_graph in (False, True):
+        model = model_for(name, model_folders[name], dtype, cuda_graph=use_graph, max_tokens=2048)
+        eng = model.engine
+        eng.use_graph = use_graph
+        got = []
+        eng.begin("a")
+        eng.begin("b")
+        for k in range(5):                                  # five equal portions of 32 tokens: eager x2, capture, replay x2
+            got.append(eng.step([StepEntry("a", long_a[32 * k:32 * k + 32], [31, 0])]).to("cpu", copy=True))
+        if use_graph:
+            assert len(eng._graphs) == 1
+        for k in range(4):                                  # a portion of b beside one decoded token of a: always eager
+            got.append(eng.step([StepEntry("b", long_b[24 * k:24 * k + 24], [23]),
+                                 StepEntry("a", [(k * 11) % cfg.vocab_size], [0])]).to("cpu", copy=True))
+        if use_graph:
+            assert len(eng._graphs) == 1
+        eng.end("a")
+        eng.end("b")
+        rows[use_graph] = got
+    for a, b in zip(rows[False], rows[True]):
+        assert torch.equal(a, b)
+
+
 # ------------------------------------------------------------------- sampler
 
 def test_sampler_matches_plain_sampler():

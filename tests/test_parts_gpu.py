@@ -191,6 +191,7 @@ def register_toy():
         """out_t = W . mean(h_0 .. h_t) over the request's own tokens.  The state
         (sum of inputs, count) lives in the request's fixed-size state slot."""
         category = "mixer"
+        graph_safe = False                 # its forward loops over the step's requests on the host
 
         def __init__(self, spec, ctx):
             super().__init__(spec, ctx)
@@ -401,6 +402,7 @@ def register_toy2():
         logits); its output is scaled by the sigmoid of that logit.  Tokens are grouped
         by expert and each group runs the framework's Linear and SwiGLU kernels."""
         category = "feed_forward"
+        graph_safe = False                 # it reads the routing back to the host
 
         def __init__(self, spec, ctx):
             super().__init__(spec, ctx)
