@@ -49,7 +49,9 @@ def token_ids(name, vocab, n):
 
 
 def main():
-    ref = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py PATH_TO_A_CHECKOUT_OF_fastllm-py")
+    ref = Path(sys.argv[1])
     sys.path.insert(0, str(ref))
     sys.modules["cupy"] = cupy_stand_in()
     from fastllm_py import DeviceMap, Model
