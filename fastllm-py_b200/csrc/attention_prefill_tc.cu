@@ -142,6 +142,29 @@ __device__ __forceinline__ void ft_ld32(uint32_t taddr, uint32_t* r) {
         : "memory");
 }
 __device__ __forceinline__ void ft_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void ft_st32(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
+        "%23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void ft_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows in the lanes, 16 bfloat16 of K as 8 columns) comes
+// from tensor memory
+__device__ __forceinline__ void ft_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 
 // K-major operand, rows of 128 bytes in the 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t ft_desc_kmajor(uint32_t saddr) {
@@ -170,13 +193,12 @@ __device__ __forceinline__ float ft_weight(float a, float b) { return (a == -CUD
 struct FtSmem {
     static constexpr int Q_BYTES = FT_ATOMS * FT_ATOM_BYTES;
     static constexpr int KV_BYTES = FT_ATOMS * FT_ATOM_BYTES;          // one of K or V, one stage
-    static constexpr int P_BYTES = 2 * FT_ATOM_BYTES;                  // 128 rows x 128 keys, one of two buffers
-    static constexpr int TILES = Q_BYTES + 2 * FT_STAGES * KV_BYTES + 2 * P_BYTES;
+    static constexpr int TILES = Q_BYTES + 2 * FT_STAGES * KV_BYTES;
     static constexpr int BARS = 24 * 8 + 2 * FT_PARTS * 128 * 4;       // barriers, then the parts' maxima (two rounds)
-    // The tiles want a 1024-byte boundary.  With 128-wide heads they fill the SM's shared memory
-    // to within a KB, so there is no room to round up to one: the kernel then counts on the
-    // dynamic shared memory starting on such a boundary (it has no static shared memory) and
-    // reports FT_ERR_SMEM instead of running if it does not.
+    // The tiles want a 1024-byte boundary.  Where they fill the SM's shared memory to within a KB
+    // there is no room to round up to one: the kernel then counts on the dynamic shared memory
+    // starting on such a boundary (it has no static shared memory) and reports FT_ERR_SMEM instead
+    // of running if it does not.
     static constexpr int SLACK = (TILES + BARS + 1024 <= 232448) ? 1024 : 0;
     static constexpr int TOTAL = TILES + BARS + SLACK;
 };
@@ -196,20 +218,17 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
     unsigned char* q_s = base;
     unsigned char* k_s = q_s + FtSmem::Q_BYTES;                        // [stage][atom][128 rows][128 B]
     unsigned char* v_s = k_s + FT_STAGES * FtSmem::KV_BYTES;
-    unsigned char* p_s = v_s + FT_STAGES * FtSmem::KV_BYTES;           // [buffer][atom][128 rows][128 B]
     uint64_t* bars = (uint64_t*)(base + FtSmem::TILES);
     uint64_t* q_full = bars + 0;
     uint64_t* k_full = bars + 1;                                       // [2]
     uint64_t* k_empty = bars + 3;                                      // [2]
     uint64_t* s_full = bars + 5;                                       // [2]
-    uint64_t* s_empty = bars + 7;                                      // [2]
     uint64_t* p_full = bars + 9;                                       // [2]
-    uint64_t* o_full = bars + 11;                                      // [2]
+    uint64_t* o_done = bars + 11;
     uint32_t* tmem_slot = (uint32_t*)(bars + 13);
     uint64_t* x_bar = bars + 14;                                       // the softmax threads' exchange point
     uint64_t* v_full = bars + 16;                                      // [2]
     uint64_t* v_empty = bars + 18;                                     // [2]
-    uint64_t* o_empty = bars + 20;                                     // [2]
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     // which request and which 128-row tile: blockIdx.y counts tiles, a request's last (longest) tile first
@@ -243,13 +262,9 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
             ft_bar_init(&v_full[s], 1);
             ft_bar_init(&v_empty[s], 1);
             ft_bar_init(&s_full[s], 1);
-            ft_bar_init(&s_empty[s], FT_SOFTMAX_WARPS);
-        }
-        for (int s = 0; s < 2; ++s) {
             ft_bar_init(&p_full[s], FT_SOFTMAX_WARPS);
-            ft_bar_init(&o_full[s], 1);
-            ft_bar_init(&o_empty[s], FT_SOFTMAX_WARPS);
         }
+        ft_bar_init(o_done, 1);
         ft_bar_init(x_bar, FT_SOFTMAX_WARPS);
         *abort_flag = (*(volatile int*)status != 0) ? 1 : 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -266,7 +281,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
     ft_fence_after();
     const uint32_t tmem = *tmem_slot;
     const uint32_t tmem_s = tmem;                                      // two S buffers: columns 0 and 128
-    const uint32_t tmem_o = tmem + 256;                                // two O_blk buffers of HEAD_DIM columns
+    const uint32_t tmem_o = tmem + 256;                                // O: HEAD_DIM columns, accumulated over the blocks
 
 #define FT_GIVE_UP()                                                             \
     {                                                                            \
@@ -316,13 +331,13 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
         }
     } else if (warp == FT_MMA_WARP) {
         if (lane == 0 && !*abort_flag) {
-            // ---- MMA issuer
+            // ---- MMA issuer.  The tensor core runs what this thread issues in order, so S(i + 2),
+            // which goes where S(i) and then P(i) were, follows P V of block i without a barrier.
             constexpr uint32_t idesc_s = ft_idesc(FT_BM, FT_BN, 0);
             constexpr uint32_t idesc_o = ft_idesc(FT_BM, HEAD_DIM, 1);
             auto issue_s = [&](int i) -> bool {                        // S(i) = Q K(i)^T into S buffer i & 1
                 const int s = i & 1;
                 if (!ft_wait(&k_full[s], (uint32_t)(i >> 1) & 1u, abort_flag)) return false;
-                if (!ft_wait(&s_empty[s], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag)) return false;
                 ft_fence_after();
                 const uint32_t qa = ft_smem(q_s), ka = ft_smem(k_s + s * FtSmem::KV_BYTES);
 #pragma unroll
@@ -338,61 +353,42 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
             bool ok = ft_wait(q_full, 0, abort_flag);
             if (ok) ok = issue_s(0);
             for (int i = 0; i < n_blocks && ok; ++i) {
+                // S(i + 1) overwrites buffer (i + 1) & 1, which held S(i - 1) and P(i - 1): the wait on
+                // p_full of block i - 1 (a round ago) says the softmax has read that S, and P V of block
+                // i - 1 was issued before this
                 if (i + 1 < n_blocks && !issue_s(i + 1)) { ok = false; break; }
-                if (!ft_wait(&v_full[i & 1], (uint32_t)(i >> 1) & 1u, abort_flag)) { ok = false; break; }
-                const int b = i & 1;                                   // P and O_blk buffer of this block
-                const uint32_t ph = (uint32_t)(i >> 1) & 1u;
-                if (!ft_wait(&p_full[b], ph, abort_flag)) { ok = false; break; }
-                if (!ft_wait(&o_empty[b], ph ^ 1u, abort_flag)) { ok = false; break; }
+                const int b = i & 1;
+                if (!ft_wait(&v_full[b], (uint32_t)(i >> 1) & 1u, abort_flag)) { ok = false; break; }
+                if (!ft_wait(&p_full[b], (uint32_t)(i >> 1) & 1u, abort_flag)) { ok = false; break; }
                 ft_fence_after();
-                const uint32_t pa = ft_smem(p_s + b * FtSmem::P_BYTES), va = ft_smem(v_s + b * FtSmem::KV_BYTES);
+                // O (+)= P(i) V(i): A = P from tensor memory (rows in the lanes, 16 keys = 8 columns of
+                // bfloat16 pairs, at the start of S buffer b); B = V: MN-major, 16 keys = two 8-row groups
+                const uint32_t pa = tmem_s + (uint32_t)(b * FT_BN), va = ft_smem(v_s + b * FtSmem::KV_BYTES);
 #pragma unroll
-                for (int k = 0; k < FT_BN / 16; ++k) {
-                    // A = P: K-major, keys are its K axis; B = V: MN-major, 16 keys = two 8-row groups
-                    const uint32_t a_off = (uint32_t)((k >> 2) * FT_ATOM_BYTES + (k & 3) * 32);
-                    ft_mma(tmem_o + (uint32_t)(b * HEAD_DIM), ft_desc_kmajor(pa + a_off),
-                           ft_desc_mnmajor(va + (uint32_t)(k * 16 * 128)),
-                           idesc_o, k > 0 ? 1u : 0u);
-                }
-                ft_commit(&v_empty[i & 1]);
-                ft_commit(&o_full[b]);              // O_blk(i) is ready; P's buffer is free again
+                for (int k = 0; k < FT_BN / 16; ++k)
+                    ft_mma_ts(tmem_o, pa + (uint32_t)(k * 8), ft_desc_mnmajor(va + (uint32_t)(k * 16 * 128)), idesc_o,
+                              (i > 0 || k > 0) ? 1u : 0u);
+                ft_commit(&v_empty[b]);
+                ft_commit(o_done);                  // phase i: O holds the blocks up to i
             }
             if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, FT_ERR_WAIT); }
         }
     } else {
         // ---- softmax: FT_PARTS threads (r, r + 128, ...) share query row r; `part` says which
-        // FT_KP keys of a block and which FT_OD output columns a thread owns
+        // FT_KP keys of a block and which FT_OD output columns a thread owns.  P goes back into
+        // tensor memory, over the first half of the S it was made from, as the A operand of P V,
+        // and O stays in tensor memory, where P V accumulates; it is rescaled (read, multiplied,
+        // written back by these threads) only when a row's maximum has grown by more than 2^8
+        // since the scale in use was set: until then the exponentials simply use the older maximum
+        // (they stay below 2^8, well inside bfloat16 and float), and no thread waits for P V.
         const int r = threadIdx.x & 127;
         const int part = threadIdx.x >> 7;
         const int pos_r = ctx + row0 + r;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         // [round parity][part][row]: a round's values stay untouched while the next round's are written
         float* part_max_all = reinterpret_cast<float*>(bars + 24);
-        float m_run = -CUDART_INF_F, l_run = 0.0f;
-        float o_reg[FT_OD];
-#pragma unroll
-        for (int d = 0; d < FT_OD; ++d) o_reg[d] = 0.0f;
+        float m_run = -CUDART_INF_F, l_run = 0.0f;           // m_run: the maximum the scale in use is based on
         bool ok = !*abort_flag;
-        // P and O_blk have two buffers each, so the softmax of block i does not wait for P V of
-        // block i - 1: that product is collected after P(i) is handed over, and the correction it
-        // needs is the one of the round before: out = out * corr(i - 1) + O_blk(i - 1).
-        float corr_prev = 0.0f;
-        auto collect = [&](int i_done, float corr_of) -> bool {          // adds O_blk(i_done) into the row
-            const int b = i_done & 1;
-            if (!ft_warp_wait(&o_full[b], (uint32_t)(i_done >> 1) & 1u, abort_flag)) return false;
-            ft_fence_after();
-#pragma unroll
-            for (int c = 0; c < FT_OD; c += 32) {
-                uint32_t w[32];
-                ft_ld32(tmem_o + lane_base + (uint32_t)(b * HEAD_DIM + part * FT_OD + c), w);
-                ft_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) o_reg[c + j] = fmaf(o_reg[c + j], corr_of, __uint_as_float(w[j]));
-            }
-            ft_fence_before();
-            ft_warp_arrive(&o_empty[b]);
-            return true;
-        };
         for (int i = 0; i < n_blocks && ok; ++i) {
             const int sb = i & 1;
             if (!ft_warp_wait(&s_full[sb], (uint32_t)(i >> 1) & 1u, abort_flag)) FT_GIVE_UP();
@@ -404,8 +400,6 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
 #pragma unroll
             for (int c = 0; c < FT_KP; c += 32) ft_ld32(s_addr + (uint32_t)c, v + c);
             ft_ld_wait();
-            ft_fence_before();
-            ft_warp_arrive(&s_empty[sb]);                                  // S(i) is in registers
             if (!all_seen) {
 #pragma unroll
                 for (int j = 0; j < FT_KP; ++j) {
@@ -420,7 +414,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
                 for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], __uint_as_float(v[j + e]));
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            // exchange the parts' maxima (one barrier among the softmax warps per block)
+            // exchange the parts' maxima (one barrier among the softmax warps per block); past it
+            // every softmax thread has its S in registers, so the S buffer may take P
             float* part_max = part_max_all + (i & 1) * (FT_PARTS * 128);
             part_max[part * 128 + r] = mx;
             ft_warp_arrive(x_bar);                                        // (an mbarrier: its wait can give up)
@@ -429,8 +424,33 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
 #pragma unroll
             for (int q = 1; q < FT_PARTS; ++q) mx_row = fmaxf(mx_row, part_max[q * 128 + r]);
             const float m_new = fmaxf(m_run, mx_row * scale_log2e);
-            const float corr = ft_weight(m_run, m_new);
-            const float neg_m = (m_new == -CUDART_INF_F) ? 0.0f : -m_new;      // an empty row: every p below is 0
+            // the row's threads decide alike: they see the same maxima
+            const bool rescale = m_new > m_run + 8.0f || (m_run == -CUDART_INF_F && m_new != -CUDART_INF_F);
+            const bool any_rescale = __any_sync(0xffffffffu, rescale);
+            float corr = 1.0f;
+            if (rescale) {
+                corr = ft_weight(m_run, m_new);
+                l_run *= corr;
+                m_run = m_new;
+            }
+            if (any_rescale && i > 0) {
+                // O holds blocks 0 .. i - 1 once P V of block i - 1 is complete.  The whole warp reads,
+                // scales and writes its rows back (rows that keep their scale by 1): the loads and
+                // stores of tensor memory are warp-wide instructions.
+                if (!ft_warp_wait(o_done, (uint32_t)(i - 1) & 1u, abort_flag)) FT_GIVE_UP();
+                ft_fence_after();
+#pragma unroll
+                for (int c = 0; c < FT_OD; c += 32) {
+                    uint32_t w[32];
+                    const uint32_t o_addr = tmem_o + lane_base + (uint32_t)(part * FT_OD + c);
+                    ft_ld32(o_addr, w);
+                    ft_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) w[j] = __float_as_uint(__uint_as_float(w[j]) * corr);
+                    ft_st32(o_addr, w);
+                }
+            }
+            const float neg_m = (m_run == -CUDART_INF_F) ? 0.0f : -m_run;      // an empty row: every p below is 0
             float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             uint32_t packed[FT_KP / 2];
 #pragma unroll
@@ -441,29 +461,21 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
                 const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
                 packed[c] = *reinterpret_cast<const uint32_t*>(&b);
             }
-            l_run = l_run * corr + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
-            m_run = m_new;
-            // P(i) goes into the buffer that P V of block i - 2 read; that product was collected in
-            // the round before, so the buffer is free.  Then the product of block i - 1 is taken
-            // out of tensor memory, while the tensor core already has block i's P to work on.
+            l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+            // P(i): this thread's FT_KP keys as FT_KP / 2 columns of bfloat16 pairs
 #pragma unroll
-            for (int c = 0; c < FT_KP / 8; ++c) {                          // 8 keys = one 16-byte chunk
-                const int chunk = part * (FT_KP / 8) + c;                 // of the row's 16 chunks
-                unsigned char* dst = p_s + sb * FtSmem::P_BYTES + (chunk >> 3) * FT_ATOM_BYTES + r * 128 +
-                                     (((chunk & 7) ^ (r & 7)) << 4);
-                *reinterpret_cast<uint4*>(dst) =
-                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
+            for (int c = 0; c < FT_KP / 2; c += 32)
+                ft_st32(tmem_s + (uint32_t)(sb * FT_BN + part * (FT_KP / 2) + c) + lane_base, packed + c);
+            ft_st_wait();
+            ft_fence_before();
             ft_warp_arrive(&p_full[sb]);
-            if (i > 0 && !collect(i - 1, corr_prev)) FT_GIVE_UP();
-            corr_prev = corr;
         }
-        if (ok && n_blocks > 0 && !collect(n_blocks - 1, corr_prev)) {
-            ok = false;
-            if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, FT_ERR_WAIT); }
+        // the whole of O, then the row's sum: the parts' sums (all relative to the same maximum)
+        if (ok && n_blocks > 0) {
+            ok = ft_warp_wait(o_done, (uint32_t)(n_blocks - 1) & 1u, abort_flag);
+            if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, FT_ERR_WAIT); }
+            ft_fence_after();
         }
-        // the row's sum is the parts' sums (all relative to the same maximum)
         float* part_sum = part_max_all + (n_blocks & 1) * (FT_PARTS * 128);
         part_sum[part * 128 + r] = l_run;
         ft_warp_arrive(x_bar);
@@ -471,17 +483,26 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
         float l_row = part_sum[r];
 #pragma unroll
         for (int q = 1; q < FT_PARTS; ++q) l_row += part_sum[q * 128 + r];
-        if (met && ok && !*abort_flag && r < rows_here) {
+        if (met && ok && !*abort_flag && n_blocks > 0) {
             const float inv = 1.0f / l_row;
             bf16* dst = out + (long)(tok0 + r) * out_ld + (long)h * HEAD_DIM + part * FT_OD;
 #pragma unroll
-            for (int d = 0; d < FT_OD; d += 8) {
-                uint4 w;
-                __nv_bfloat162* wp = reinterpret_cast<__nv_bfloat162*>(&w);
+            for (int c = 0; c < FT_OD; c += 32) {
+                uint32_t w[32];
+                ft_ld32(tmem_o + lane_base + (uint32_t)(part * FT_OD + c), w);      // all lanes of the warp take part
+                ft_ld_wait();
+                if (r < rows_here) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    wp[e] = __floats2bfloat162_rn(o_reg[d + 2 * e] * inv, o_reg[d + 2 * e + 1] * inv);
-                *reinterpret_cast<uint4*>(dst + d) = w;
+                    for (int d = 0; d < 32; d += 8) {
+                        uint4 o4;
+                        __nv_bfloat162* wp = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            wp[e] = __floats2bfloat162_rn(__uint_as_float(w[d + 2 * e]) * inv,
+                                                          __uint_as_float(w[d + 2 * e + 1]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c + d) = o4;
+                    }
+                }
             }
         }
     }
