@@ -40,7 +40,9 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "the tcgen05 prefill kernel tak
 
 #define FT_BM 128                          // query rows per CTA
 #define FT_BN 128                          // keys per block
-#define FT_STAGES 2
+#ifndef FT_STAGES
+#define FT_STAGES 3                        // key and value ring depth (each)
+#endif
 #ifndef FT_PARTS
 #define FT_PARTS 2                         // softmax threads per query row
 #endif
@@ -194,7 +196,8 @@ struct FtSmem {
     static constexpr int Q_BYTES = FT_ATOMS * FT_ATOM_BYTES;
     static constexpr int KV_BYTES = FT_ATOMS * FT_ATOM_BYTES;          // one of K or V, one stage
     static constexpr int TILES = Q_BYTES + 2 * FT_STAGES * KV_BYTES;
-    static constexpr int BARS = 24 * 8 + 2 * FT_PARTS * 128 * 4;       // barriers, then the parts' maxima (two rounds)
+    static constexpr int BAR_SLOTS = 24 + 4 * FT_STAGES;               // 8-byte slots: barriers and the like
+    static constexpr int BARS = BAR_SLOTS * 8 + 2 * FT_PARTS * 128 * 4; // ... then the parts' maxima (two rounds)
     // The tiles want a 1024-byte boundary.  Where they fill the SM's shared memory to within a KB
     // there is no room to round up to one: the kernel then counts on the dynamic shared memory
     // starting on such a boundary (it has no static shared memory) and reports FT_ERR_SMEM instead
@@ -220,15 +223,15 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
     unsigned char* v_s = k_s + FT_STAGES * FtSmem::KV_BYTES;
     uint64_t* bars = (uint64_t*)(base + FtSmem::TILES);
     uint64_t* q_full = bars + 0;
-    uint64_t* k_full = bars + 1;                                       // [2]
-    uint64_t* k_empty = bars + 3;                                      // [2]
+    uint64_t* k_full = bars + 24;                                      // [FT_STAGES]
+    uint64_t* k_empty = k_full + FT_STAGES;
     uint64_t* s_full = bars + 5;                                       // [2]
     uint64_t* p_full = bars + 9;                                       // [2]
     uint64_t* o_done = bars + 11;
     uint32_t* tmem_slot = (uint32_t*)(bars + 13);
     uint64_t* x_bar = bars + 14;                                       // the softmax threads' exchange point
-    uint64_t* v_full = bars + 16;                                      // [2]
-    uint64_t* v_empty = bars + 18;                                     // [2]
+    uint64_t* v_full = k_empty + FT_STAGES;
+    uint64_t* v_empty = v_full + FT_STAGES;
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     // which request and which 128-row tile: blockIdx.y counts tiles, a request's last (longest) tile first
@@ -256,11 +259,13 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
 
     if (threadIdx.x == 0) {
         ft_bar_init(q_full, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < FT_STAGES; ++s) {
             ft_bar_init(&k_full[s], 1);
             ft_bar_init(&k_empty[s], 1);
             ft_bar_init(&v_full[s], 1);
             ft_bar_init(&v_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
             ft_bar_init(&s_full[s], 1);
             ft_bar_init(&p_full[s], FT_SOFTMAX_WARPS);
         }
@@ -309,8 +314,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
             const int* bt = block_table + (long)req * bt_stride;
             const int n_ops = (FT_BN / page_size) * FT_ATOMS;
             for (int i = 0; i < n_blocks; ++i) {
-                const int s = i & 1;
-                if (!ft_warp_wait(&empty[s], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag)) FT_GIVE_UP();
+                const int s = i % FT_STAGES;
+                if (!ft_warp_wait(&empty[s], ((uint32_t)(i / FT_STAGES) & 1u) ^ 1u, abort_flag)) FT_GIVE_UP();
                 if (lane == 0) ft_bar_expect(&full[s], FtSmem::KV_BYTES);
                 __syncwarp();
                 const int key0 = (kb_begin + i) * FT_BN;
@@ -336,17 +341,17 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
             constexpr uint32_t idesc_s = ft_idesc(FT_BM, FT_BN, 0);
             constexpr uint32_t idesc_o = ft_idesc(FT_BM, HEAD_DIM, 1);
             auto issue_s = [&](int i) -> bool {                        // S(i) = Q K(i)^T into S buffer i & 1
-                const int s = i & 1;
-                if (!ft_wait(&k_full[s], (uint32_t)(i >> 1) & 1u, abort_flag)) return false;
+                const int s = i & 1, ks = i % FT_STAGES;
+                if (!ft_wait(&k_full[ks], (uint32_t)(i / FT_STAGES) & 1u, abort_flag)) return false;
                 ft_fence_after();
-                const uint32_t qa = ft_smem(q_s), ka = ft_smem(k_s + s * FtSmem::KV_BYTES);
+                const uint32_t qa = ft_smem(q_s), ka = ft_smem(k_s + ks * FtSmem::KV_BYTES);
 #pragma unroll
                 for (int k = 0; k < HEAD_DIM / 16; ++k) {
                     const uint32_t off = (uint32_t)((k >> 2) * FT_ATOM_BYTES + (k & 3) * 32);
                     ft_mma(tmem_s + (uint32_t)(s * FT_BN), ft_desc_kmajor(qa + off), ft_desc_kmajor(ka + off),
                            idesc_s, k > 0 ? 1u : 0u);
                 }
-                ft_commit(&k_empty[s]);             // the key stage is free once these MMAs have read it
+                ft_commit(&k_empty[ks]);            // the key stage is free once these MMAs have read it
                 ft_commit(&s_full[s]);
                 return true;
             };
@@ -357,18 +362,18 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
                 // p_full of block i - 1 (a round ago) says the softmax has read that S, and P V of block
                 // i - 1 was issued before this
                 if (i + 1 < n_blocks && !issue_s(i + 1)) { ok = false; break; }
-                const int b = i & 1;
-                if (!ft_wait(&v_full[b], (uint32_t)(i >> 1) & 1u, abort_flag)) { ok = false; break; }
+                const int b = i & 1, vs = i % FT_STAGES;
+                if (!ft_wait(&v_full[vs], (uint32_t)(i / FT_STAGES) & 1u, abort_flag)) { ok = false; break; }
                 if (!ft_wait(&p_full[b], (uint32_t)(i >> 1) & 1u, abort_flag)) { ok = false; break; }
                 ft_fence_after();
                 // O (+)= P(i) V(i): A = P from tensor memory (rows in the lanes, 16 keys = 8 columns of
                 // bfloat16 pairs, at the start of S buffer b); B = V: MN-major, 16 keys = two 8-row groups
-                const uint32_t pa = tmem_s + (uint32_t)(b * FT_BN), va = ft_smem(v_s + b * FtSmem::KV_BYTES);
+                const uint32_t pa = tmem_s + (uint32_t)(b * FT_BN), va = ft_smem(v_s + vs * FtSmem::KV_BYTES);
 #pragma unroll
                 for (int k = 0; k < FT_BN / 16; ++k)
                     ft_mma_ts(tmem_o, pa + (uint32_t)(k * 8), ft_desc_mnmajor(va + (uint32_t)(k * 16 * 128)), idesc_o,
                               (i > 0 || k > 0) ? 1u : 0u);
-                ft_commit(&v_empty[b]);
+                ft_commit(&v_empty[vs]);
                 ft_commit(o_done);                  // phase i: O holds the blocks up to i
             }
             if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, FT_ERR_WAIT); }
@@ -386,7 +391,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1) attention_prefill_tc_kernel(
         const int pos_r = ctx + row0 + r;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         // [round parity][part][row]: a round's values stay untouched while the next round's are written
-        float* part_max_all = reinterpret_cast<float*>(bars + 24);
+        float* part_max_all = reinterpret_cast<float*>(bars + FtSmem::BAR_SLOTS);
         float m_run = -CUDART_INF_F, l_run = 0.0f;           // m_run: the maximum the scale in use is based on
         bool ok = !*abort_flag;
         for (int i = 0; i < n_blocks && ok; ++i) {
