@@ -3,7 +3,7 @@
 // One query token per request attends to hundreds or thousands of cached keys:
 // the work is reading the cache, so the kernel is built to keep many 16-byte
 // loads in flight on every SM.  The keys of a token are cut at fixed absolute
-// positions (every ATD_SPLIT keys); one CTA of four warps handles one
+// positions (every `split_keys` keys, chosen per launch); one CTA of four warps handles one
 // (token, query head, split), each warp a quarter of the split.  Inside a warp a
 // key row is spread over HEAD_DIM / 8 lanes (8 bfloat16 = 16 bytes each), so a
 // warp covers 32 / lanes-per-key keys per load and eight loads (four keys' worth
@@ -25,13 +25,9 @@
 #ifndef HEAD_DIM
 #define HEAD_DIM 128
 #endif
-#ifndef ATD_SPLIT
-#define ATD_SPLIT 256                      // keys per split
-#endif
 #ifndef ATD_WARPS
 #define ATD_WARPS 4
 #endif
-#define ATD_KEYS_PER_WARP (ATD_SPLIT / ATD_WARPS)
 #ifndef ATD_UNROLL
 #define ATD_UNROLL 4
 #endif
@@ -142,7 +138,7 @@ __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_kernel(
     const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, long page_stride, int page_size,
     int page_shift, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req,
     const int* __restrict__ positions, const int* __restrict__ tok_list, int n_heads, int n_kv_heads,
-    int window, float scale_log2e, int n_splits, float* __restrict__ partial) {
+    int window, float scale_log2e, int n_splits, int split_keys, float* __restrict__ partial) {
     pdl_wait();
     pdl_trigger();
     const int li = blockIdx.x;                              // index into the list of decode tokens
@@ -150,8 +146,8 @@ __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_kernel(
     const int h = blockIdx.y, split = blockIdx.z;
     const int pos = positions[t];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int split_begin = split * ATD_SPLIT;
-    if (split_begin > pos || split_begin + ATD_SPLIT <= lo) return;       // nothing of this split is visible
+    const int split_begin = split * split_keys;
+    if (split_begin > pos || split_begin + split_keys <= lo) return;       // nothing of this split is visible
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = lane / LPK;                           // which of the warp's KPW keys per load
@@ -177,16 +173,17 @@ __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_kernel(
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i] = 0.0f;
 
-    const int warp_begin = split_begin + warp * ATD_KEYS_PER_WARP;
+    const int keys_per_warp = split_keys / ATD_WARPS;
+    const int warp_begin = split_begin + warp * keys_per_warp;
 #pragma unroll 1
-    for (int base = warp_begin; base < warp_begin + ATD_KEYS_PER_WARP; base += KPW * ATD_UNROLL) {
+    for (int base = warp_begin; base < warp_begin + keys_per_warp; base += KPW * ATD_UNROLL) {
         if (base > pos) break;
         Bf16x8 kv[ATD_UNROLL], vv[ATD_UNROLL];
         bool valid[ATD_UNROLL];
 #pragma unroll
         for (int u = 0; u < ATD_UNROLL; ++u) {
             const int j = base + u * KPW + group;
-            valid[u] = (j >= lo) && (j <= pos);
+            valid[u] = (j >= lo) && (j <= pos) && (j < warp_begin + keys_per_warp);   // (a round may reach past the warp's keys)
             if (valid[u] && dim_ok) {
                 const int pg = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
                 const int off = page_shift >= 0 ? (j & (page_size - 1)) : (j - pg * page_size);
@@ -294,7 +291,7 @@ __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_kernel(
 // are read once for all its heads, and the dot products, their reductions and
 // the weighted sum of the values cost a few dozen warp instructions per 16 keys
 // instead of several hundred.  What is left is the stream of the cache: every
-// warp owns ATD_KEYS_PER_WARP consecutive keys of the split and brings them in
+// warp owns a quarter of the split's keys, consecutive, and brings them in
 // 16 at a time with cp.async through a ring of its own in shared memory (two
 // lanes per key row, one page lookup each), so there is no CTA-wide barrier in
 // the loop.  Scores, maxima and sums are float; P is rounded to bfloat16 as the
@@ -348,7 +345,7 @@ __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_mma_kernel(
     const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, long page_stride, int page_size,
     int page_shift, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req,
     const int* __restrict__ positions, const int* __restrict__ tok_list, int n_heads, int n_kv_heads,
-    int window, float scale_log2e, int n_splits, float* __restrict__ partial) {
+    int window, float scale_log2e, int n_splits, int split_keys, float* __restrict__ partial) {
     // What follows up to pdl_wait() reads nothing that the preceding kernels of the step write: the
     // step's tables, and keys and values of EARLIER positions (the kernel before this one writes the
     // cache at the tokens' own positions only).  It runs while that kernel is still at work.
@@ -360,8 +357,8 @@ __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_mma_kernel(
     const int h0 = kvh * group;
     const int pos = positions[t];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int split_begin = split * ATD_SPLIT;
-    if (split_begin > pos || split_begin + ATD_SPLIT <= lo) return;       // nothing of this split is visible
+    const int split_begin = split * split_keys;
+    if (split_begin > pos || split_begin + split_keys <= lo) return;       // nothing of this split is visible
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gq = lane >> 2, tq = lane & 3;                // fragment coordinates: row (and row + 8), column pair
@@ -370,8 +367,9 @@ __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_mma_kernel(
     bf16* ring = reinterpret_cast<bf16*>(atm_raw) + warp * ATM_WARP_ELEMS;      // [stage][K | V][16][DP]
 
     // this warp's keys, clipped to what the token sees, in chunks of 16 from the warp's first key
-    const int warp_begin = split_begin + warp * ATD_KEYS_PER_WARP;
-    const int first = max(warp_begin, lo), last = min(warp_begin + ATD_KEYS_PER_WARP - 1, pos);
+    const int keys_per_warp = split_keys / ATD_WARPS;
+    const int warp_begin = split_begin + warp * keys_per_warp;
+    const int first = max(warp_begin, lo), last = min(warp_begin + keys_per_warp - 1, pos);
     const int c_begin = first > last ? 0 : (first - warp_begin) / ATM_CHUNK;
     const int c_end = first > last ? 0 : (last - warp_begin) / ATM_CHUNK + 1;
 
@@ -584,26 +582,27 @@ __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_mma_kernel(
 // The merge kernel: one CTA per (token, head).
 __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_merge_kernel(
     const float* __restrict__ partial, bf16* __restrict__ out, long out_ld, const int* __restrict__ positions,
-    const int* __restrict__ tok_list, int n_heads, int window, int n_splits) {
+    const int* __restrict__ tok_list, int n_heads, int window, int n_splits, int split_keys) {
     pdl_wait();
     pdl_trigger();
     const int li = blockIdx.x, h = blockIdx.y;
     const int t = tok_list ? tok_list[li] : li;
     const int pos = positions[t];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    merge_splits(partial + ((long)li * n_heads + h) * n_splits * ATD_ROW, lo / ATD_SPLIT, pos / ATD_SPLIT,
+    merge_splits(partial + ((long)li * n_heads + h) * n_splits * ATD_ROW, lo / split_keys, pos / split_keys,
                  out + (long)t * out_ld + (long)h * HEAD_DIM);
 }
 
 FL_API int fl_attention_decode_head_dim() { return HEAD_DIM; }
-FL_API int fl_attention_decode_split() { return ATD_SPLIT; }
+FL_API int fl_attention_decode_split_unit() { return ATD_WARPS * 16; }    // split sizes are multiples of this
 FL_API long fl_attention_decode_workspace_floats(int n_list, int n_heads, int n_splits) {
     return n_splits > 1 ? (long)n_list * n_heads * n_splits * ATD_ROW : 0;
 }
 
 // Tokens tok_list[0..n_list) (or 0..n_list when tok_list is null) of q attend to
 // their requests' cached keys.  n_splits must cover the longest sequence among
-// them: n_splits * ATD_SPLIT > largest position.  `partial` holds
+// them: n_splits * split_keys > largest position (split_keys: keys per split, a multiple
+// of 64; larger splits stream longer per CTA, smaller ones give more CTAs).  `partial` holds
 // fl_attention_decode_workspace_floats(...) floats when n_splits > 1.  `variant`:
 // 0 chooses (the tensor-core form when a key/value head serves at most 16 query
 // heads), 1 forces the CUDA-core form.
@@ -611,10 +610,11 @@ FL_API int fl_attention_decode(const void* q, long q_ld, void* out, long out_ld,
                                const void* v_cache, long page_stride, int page_size,
                                const int* block_table, int bt_stride, const int* tok_req,
                                const int* positions, const int* tok_list, int n_list, int n_heads,
-                               int n_kv_heads, int window, float scale, int n_splits, float* partial,
-                               int variant, cudaStream_t stream) {
+                               int n_kv_heads, int window, float scale, int n_splits, int split_keys,
+                               float* partial, int variant, cudaStream_t stream) {
     if (n_list <= 0) return 0;
     if (n_heads > 65535 || n_splits < 1 || n_splits > 65535 || n_heads % n_kv_heads) return (int)cudaErrorInvalidValue;
+    if (split_keys < ATD_WARPS * 16 || split_keys % (ATD_WARPS * 16)) return (int)cudaErrorInvalidValue;
     if (HEAD_DIM % 16 != 0) variant = 1;
     if ((q_ld % 8) || (out_ld % 8) || (page_stride % 8)) return (int)cudaErrorMisalignedAddress;
     if (n_splits > 1 && partial == nullptr) return (int)cudaErrorInvalidValue;
@@ -640,16 +640,16 @@ FL_API int fl_attention_decode(const void* q, long q_ld, void* out, long out_ld,
         rc = fl_launch(attention_decode_mma_kernel, grid, dim3(ATD_WARPS * 32), smem, stream, (const bf16*)q, q_ld,
                        (bf16*)out, out_ld, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, page_size,
                        page_shift, block_table, bt_stride, tok_req, positions, tok_list, n_heads, n_kv_heads,
-                       window, scale * 1.4426950408889634f, n_splits, partial);
+                       window, scale * 1.4426950408889634f, n_splits, split_keys, partial);
     } else {
         dim3 grid(n_list, n_heads, n_splits);
         rc = fl_launch(attention_decode_kernel, grid, dim3(ATD_WARPS * 32), 0, stream, (const bf16*)q, q_ld,
                        (bf16*)out, out_ld, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, page_size,
                        page_shift, block_table, bt_stride, tok_req, positions, tok_list, n_heads, n_kv_heads,
-                       window, scale * 1.4426950408889634f, n_splits, partial);
+                       window, scale * 1.4426950408889634f, n_splits, split_keys, partial);
     }
     if (rc || n_splits == 1) return rc;
     dim3 mgrid(n_list, n_heads);
     return fl_launch(attention_decode_merge_kernel, mgrid, dim3(ATD_WARPS * 32), 0, stream, (const float*)partial,
-                     (bf16*)out, out_ld, positions, tok_list, n_heads, window, n_splits);
+                     (bf16*)out, out_ld, positions, tok_list, n_heads, window, n_splits, split_keys);
 }

@@ -117,6 +117,7 @@ class StepContext:
     rows_identity: bool = False    # the wanted rows are all rows, in order
     n_decode_tokens: int = 0       # tokens of requests that bring exactly one token
     decode_splits: int = 1         # key splits the decode attention kernel is launched with
+    decode_split_keys: int = 256   # ... and the keys in each
     token_feed: object = None      # int32 device tensor: a token id -1 - r stands for token_feed[r]
     _views: dict = field(default_factory=dict)
 

@@ -40,6 +40,8 @@ class Engine:
         self.cache = CacheManager(decoder.cache_needs(), self.page_size, num_pages,
                                   config.max_requests, bt_stride)
         self.cache.allocate(self.device, self.dtype)
+        # the most key/value heads of any paged cache: how many CTAs a decode token gives the attention kernel
+        self._kv_heads = max([getattr(need, "kv_heads", 1) for need in decoder.cache_needs().values()] or [1])
         self.workspace = Workspace(self.device, self.max_tokens)
         self.buffers = StepBuffers(self.device, self.max_tokens, config.max_requests,
                                    len(self.cache.groups), bt_stride)
@@ -179,20 +181,21 @@ class Engine:
             max_q_len=max(q_lens), max_seq_len=max(c + q for c, q in zip(ctx_lens, q_lens)),
             n_decode_tokens=n_dec, token_feed=self.token_feed,
             rows_identity=(m == n_tokens and bool((rows[:m] == np.arange(m)).all())))
-        step.decode_splits = self._decode_splits(step)
+        step.decode_split_keys, step.decode_splits = self._decode_splits(step)
         step._views = build_views(cache, buf, n_tokens, n)
         return step
 
-    def _decode_splits(self, step: StepContext) -> int:
-        """Key splits for the decode attention kernel: enough for the longest
-        sequence of the step.  Under graph replay the count is part of the
-        graph's key, so it moves in buckets of 1024 keys instead of every 256."""
-        from ..native.attention import DECODE_SPLIT, decode_splits
+    def _decode_splits(self, step: StepContext):
+        """(keys per split, splits) for the decode attention kernel: enough splits
+        for the longest sequence of the step.  Under graph replay both are part of
+        the graph's key, so the length moves in buckets of 1024 keys."""
+        from ..native.attention import decode_split_keys, decode_splits
 
         longest = step.max_seq_len
         if self.use_graph and step.max_q_len == 1:
             longest = -(-longest // 1024) * 1024
-        return decode_splits(longest)
+        keys = decode_split_keys(max(step.n_decode_tokens, 1), self._kv_heads, longest)
+        return keys, decode_splits(longest, keys)
 
     def step(self, entries) -> torch.Tensor:
         """Run one step; returns float32 logits [wanted places, vocab] on the
@@ -228,7 +231,7 @@ class Engine:
 
         feed = None if self.token_feed is None else self.token_feed.data_ptr()
         key = (step.n_tokens, step.n_requests, step.n_decode_tokens, step.n_wanted, step.rows_identity,
-               step.decode_splits, self.decoder.graph_key(step), feed)
+               step.decode_splits, step.decode_split_keys, self.decoder.graph_key(step), feed)
         entry = self._graphs.pop(key, None)
         if entry is not None:
             self._graphs[key] = entry                       # most recently used last

@@ -15,7 +15,7 @@ import torch
 from . import ops
 from .build import load_library
 
-DECODE_SPLIT = 256          # keys per split of the decode kernel (ATD_SPLIT in attention_decode.cu)
+DECODE_SPLIT = 256          # the smallest split of the decode kernel, in keys (larger ones are multiples)
 _libs: dict = {}
 _state: dict = {}
 
@@ -48,10 +48,10 @@ def _decode_lib(head_dim: int):
         lib = load_library("attention_decode", {"HEAD_DIM": head_dim})
         lib.fl_attention_decode.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_long,
                                             c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                            c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p]
+                                            c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_void_p]
         lib.fl_attention_decode.restype = c_int
         assert lib.fl_attention_decode_head_dim() == head_dim
-        assert lib.fl_attention_decode_split() == DECODE_SPLIT
+        assert DECODE_SPLIT % lib.fl_attention_decode_split_unit() == 0
         _libs[key] = lib
     return lib
 
@@ -97,12 +97,24 @@ def _partials(device, floats: int) -> torch.Tensor:
     return ws
 
 
-def decode_splits(max_seq_len: int) -> int:
-    return max(1, -(-max_seq_len // DECODE_SPLIT))
+def decode_splits(max_seq_len: int, split_keys: int = DECODE_SPLIT) -> int:
+    return max(1, -(-max_seq_len // split_keys))
+
+
+def decode_split_keys(n_tokens: int, kv_heads: int, max_seq_len: int) -> int:
+    """Keys per split for a launch: a CTA streams better the longer its stretch of keys
+    (1024-key splits reach 6.5 TB/s where 256-key ones reach 6.0), but only while there are
+    CTAs enough for several rounds over the GPU; with few tokens or short sequences the
+    smallest split gives the most CTAs."""
+    for split in (1024, 512):
+        if n_tokens * kv_heads * -(-max_seq_len // split) >= 2048:
+            return split
+    return DECODE_SPLIT
 
 
 def decode_attention(q, out, cache_tensor, block_table, tok_req, positions, tok_list, n_list, heads,
-                     kv_heads, head_dim, window, scale, page_size, n_splits, variant=0):
+                     kv_heads, head_dim, window, scale, page_size, n_splits, variant=0,
+                     split_keys=DECODE_SPLIT):
     """Split-key attention for the tokens in tok_list (None: tokens 0..n_list).
     variant 0 chooses (tensor cores when a key/value head serves at most 16 query heads
     and the head size is a multiple of 16), 1 forces the CUDA-core kernel."""
@@ -116,7 +128,7 @@ def decode_attention(q, out, cache_tensor, block_table, tok_req, positions, tok_
                                  cache_tensor.stride(0), page_size, ops._ptr(block_table),
                                  block_table.stride(0), ops._ptr(tok_req), ops._ptr(positions),
                                  ops._ptr(tok_list), n_list, heads, kv_heads, int(window or 0),
-                                 float(scale), n_splits, ops._ptr(ws), int(variant), ops._stream())
+                                 float(scale), n_splits, int(split_keys), ops._ptr(ws), int(variant), ops._stream())
     ops._check(rc, "attention_decode", 2 if n_splits > 1 else 1)
 
 
@@ -158,7 +170,7 @@ def paged_attention(q, out, cache, step, heads, kv_heads, head_dim, window, scal
         tok_list = None if n_dec == step.n_tokens else step.decode_tokens
         decode_attention(q, out, cache.tensor, cache.block_table, step.tok_req, step.positions, tok_list,
                          n_dec, heads, kv_heads, head_dim, window, scale, cache.page_size,
-                         step.decode_splits)
+                         step.decode_splits, 0, step.decode_split_keys)
     if n_dec < step.n_tokens:
         prefill_attention(q, out, cache.tensor, cache.block_table, step.req_start, step.req_ctx,
                           step.req_qlen, step.n_requests, step.n_tokens, False, heads, kv_heads,

@@ -164,7 +164,7 @@ def run_simt(case, window=None):
     return out.float().cpu()
 
 
-def run_fast(case, window=None, prefill_variant=0, decode_variant=0):
+def run_fast(case, window=None, prefill_variant=0, decode_variant=0, split_keys=256):
     from fastllm_py_b200.native import attention as fast
 
     out = torch.zeros_like(case.q)
@@ -175,7 +175,7 @@ def run_fast(case, window=None, prefill_variant=0, decode_variant=0):
         fast.decode_attention(case.q, out, case.cache, case.block_table, case.tok_req, case.positions,
                               None if n_dec == case.n_tokens else case.decode_tokens, n_dec, case.heads,
                               case.kv_heads, case.head_dim, window, scale, case.page_size,
-                              fast.decode_splits(longest), decode_variant)
+                              fast.decode_splits(longest, split_keys), decode_variant, split_keys)
     if n_dec < case.n_tokens:
         fast.prefill_attention(case.q, out, case.cache, case.block_table, case.req_start, case.req_ctx,
                                case.req_qlen, len(case.q_lens), case.n_tokens, False, case.heads,
@@ -227,10 +227,12 @@ DECODE_SHAPES = [
 @pytest.mark.parametrize("shape", DECODE_SHAPES)
 @pytest.mark.parametrize("window", [None, 37, 300])
 @pytest.mark.parametrize("variant", [0, 1])
-def test_decode_attention_both_kernels(shape, window, variant):
-    """variant 0: mma.sync over the heads of a group (where it applies); variant 1: CUDA cores."""
+@pytest.mark.parametrize("split_keys", [256, 64, 1024])
+def test_decode_attention_both_kernels(shape, window, variant, split_keys):
+    """variant 0: mma.sync over the heads of a group (where it applies); variant 1: CUDA cores;
+    with the smallest split, the usual one and a large one."""
     case = AttentionCase(*shape, torch.bfloat16, seed=11)
-    diff = (run_fast(case, window, 0, variant) - case.reference(window)).abs().max()
+    diff = (run_fast(case, window, 0, variant, split_keys) - case.reference(window)).abs().max()
     assert float(diff) <= case.tolerance()
 
 
