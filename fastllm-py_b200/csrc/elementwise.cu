@@ -158,12 +158,69 @@ FL_API int fl_rmsnorm(const void* x, int x_dtype, long x_ld, const void* w, int 
     return 0;
 }
 
+// resid += delta; out = rmsnorm(resid) * w for rows of 4-element chunks, each row by one CTA of 256
+// threads that keeps its KEEP chunks per thread in registers across the reduction: every byte is read
+// once and written once, all loads of a thread are issued before the first use, and with eight CTAs to
+// an SM many rows are in flight.  (The general kernel above reads the row a second time.)
+template <typename TD, typename TW, typename TO, int KEEP>
+__global__ void __launch_bounds__(256) add_rmsnorm_rows_kernel(float* __restrict__ resid, long resid_ld,
+                                                               const TD* __restrict__ delta, long delta_ld,
+                                                               const TW* __restrict__ w, TO* __restrict__ out,
+                                                               long out_ld, int dim, float eps) {
+    pdl_wait();
+    pdl_trigger();
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    float* xr = resid + (long)r * resid_ld;
+    const TD* dr = delta + (long)r * delta_ld;
+    TO* o = out + (long)r * out_ld;
+    float4 keep[KEEP], gain[KEEP];
+    float ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < KEEP; ++c) {
+        const int i = (threadIdx.x + c * 256) * 4;
+        if (i < dim) {
+            float4 v = *reinterpret_cast<const float4*>(xr + i), d;
+            load4(dr + i, d);
+            load4(w + i, gain[c]);
+            v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+            *reinterpret_cast<float4*>(xr + i) = v;
+            keep[c] = v;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+#pragma unroll
+    for (int c = 0; c < KEEP; ++c) {
+        const int i = (threadIdx.x + c * 256) * 4;
+        if (i < dim)
+            store4(o + i, make_float4(keep[c].x * inv * gain[c].x, keep[c].y * inv * gain[c].y,
+                                      keep[c].z * inv * gain[c].z, keep[c].w * inv * gain[c].w));
+    }
+}
+
 FL_API int fl_add_rmsnorm(float* resid, long resid_ld, const void* delta, int delta_dtype,
                           long delta_ld, const void* w, int w_dtype, void* out, int out_dtype,
                           long out_ld, int n_rows, int dim, float eps, const int* rows,
                           cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const int write_back = rows ? 0 : 1;
+    if (write_back && dim <= 8 * 1024 && vec4_ok(dim, resid, resid_ld, 4) &&
+        vec4_ok(dim, delta, delta_ld, delta_dtype == FL_F32 ? 4 : 2) && vec4_ok(dim, w, 4, w_dtype == FL_F32 ? 4 : 2) &&
+        vec4_ok(dim, out, out_ld, out_dtype == FL_F32 ? 4 : 2)) {
+        const int chunks = (dim / 4 + 255) / 256;                      // per thread
+#define FL_ROWS_LAUNCH(KEEP)                                                                              \
+    FL_DISPATCH(delta_dtype, TD, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,                      \
+        return fl_launch(add_rmsnorm_rows_kernel<TD, TW, TO, KEEP>, dim3(n_rows), dim3(256), 0, stream,   \
+                         resid, resid_ld, (const TD*)delta, delta_ld, (const TW*)w, (TO*)out, out_ld, dim, \
+                         eps))))
+        if (chunks <= 1) { FL_ROWS_LAUNCH(1); }
+        else if (chunks <= 2) { FL_ROWS_LAUNCH(2); }
+        else if (chunks <= 4) { FL_ROWS_LAUNCH(4); }
+        else { FL_ROWS_LAUNCH(8); }
+#undef FL_ROWS_LAUNCH
+    }
     const bool vec = vec4_ok(dim, resid, resid_ld, 4) && vec4_ok(dim, delta, delta_ld, delta_dtype == FL_F32 ? 4 : 2) &&
                      vec4_ok(dim, w, 4, w_dtype == FL_F32 ? 4 : 2) && vec4_ok(dim, out, out_ld, out_dtype == FL_F32 ? 4 : 2);
     const int threads = norm_threads(dim, vec);
