@@ -583,12 +583,12 @@ __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_mma_kernel(
 __global__ void __launch_bounds__(ATD_WARPS * 32) attention_decode_merge_kernel(
     const float* __restrict__ partial, bf16* __restrict__ out, long out_ld, const int* __restrict__ positions,
     const int* __restrict__ tok_list, int n_heads, int window, int n_splits, int split_keys) {
-    pdl_wait();
-    pdl_trigger();
     const int li = blockIdx.x, h = blockIdx.y;
-    const int t = tok_list ? tok_list[li] : li;
+    const int t = tok_list ? tok_list[li] : li;            // the step's tables: no kernel writes them
     const int pos = positions[t];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    pdl_wait();
+    pdl_trigger();
     merge_splits(partial + ((long)li * n_heads + h) * n_splits * ATD_ROW, lo / split_keys, pos / split_keys,
                  out + (long)t * out_ld + (long)h * HEAD_DIM);
 }

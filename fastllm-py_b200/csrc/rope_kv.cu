@@ -175,8 +175,9 @@ __global__ void rope_kv_partial_kernel(const float* __restrict__ partial, int sp
                                        const int* __restrict__ positions, const int* __restrict__ slots,
                                        T* __restrict__ k_cache, T* __restrict__ v_cache, long page_stride,
                                        int page_size) {
-    pdl_wait();
-    pdl_trigger();
+    // Where the token goes and by what angle it turns comes from the step's tables, which no
+    // kernel writes: that chain of loads (position -> row of the cos/sin table, slot -> page)
+    // runs before the wait for the product, whose partial sums are then all that is left to read.
     const int t = blockIdx.x, head = blockIdx.y;
     const int half = rot_dim >> 1;
     const float* x = partial + (long)t * ld + (long)head * head_dim;
@@ -204,14 +205,21 @@ __global__ void rope_kv_partial_kernel(const float* __restrict__ partial, int sp
         const long pos = positions[t];
         const float* cs = cos_table + pos * half;
         const float* sn = sin_table + pos * half;
-        for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        const int j0 = threadIdx.x;
+        float c0 = 1.0f, s0 = 0.0f;                        // this thread's first angle, fetched ahead
+        if (j0 < half) { c0 = cs[j0]; s0 = sn[j0]; }
+        pdl_wait();
+        pdl_trigger();
+        for (int j = j0; j < half; j += blockDim.x) {
             const float x1 = in(j), x2 = in(j + half);
-            const float c = cs[j], s = sn[j];
+            const float c = j == j0 ? c0 : cs[j], s = j == j0 ? s0 : sn[j];
             dst[j] = from_f32<T>(x1 * c - x2 * s);
             dst[j + half] = from_f32<T>(x2 * c + x1 * s);
         }
         for (int j = rot_dim + threadIdx.x; j < head_dim; j += blockDim.x) dst[j] = from_f32<T>(in(j));
     } else {
+        pdl_wait();
+        pdl_trigger();
         for (int j = threadIdx.x; j < head_dim; j += blockDim.x) dst[j] = from_f32<T>(in(j));
     }
 }
