@@ -296,3 +296,119 @@ def test_random_workloads_finish_with_clean_books(seed):
 def test_sampling_params():
     assert SamplingParams().greedy and not SamplingParams(temperature=0.5).greedy
     assert SamplingParams(presence_penalty=0.1).penalized and not SamplingParams().penalized
+
+
+# ------------------------------------------------- running one decode step ahead
+
+class FeedingEngine(StandInEngine):
+    """A stand-in for the device path: a token named -1 - row is taken from the sampler's last
+    output, as the embedding kernel does; the logits depend on the tokens a request was fed,
+    so a wrongly fed token changes every later one."""
+
+    def __init__(self, *a, **k):
+        super().__init__(*a, **k)
+        self.token_feed = None
+        self.fed = {}                                  # request -> running sum of the tokens fed
+
+    def step(self, entries):
+        rows = []
+        self.steps.append([(e.request_id, len(e.tokens), list(e.want)) for e in entries])
+        for e in entries:
+            toks = [int(self.token_feed[-1 - t]) if t < 0 else t for t in e.tokens]
+            rc = self.cache.live[e.request_id]
+            self.cache.extend(rc, len(toks))
+            self.cache.commit(rc, len(toks))
+            self.fed[e.request_id] = self.fed.get(e.request_id, 0) + sum(toks)
+            for _ in e.want:
+                row = torch.zeros(self.vocab)
+                row[(self.fed[e.request_id] * 7 + rc.seq_len) % self.vocab] = 1.0
+                rows.append(row)
+        self.cache.check()
+        return torch.stack(rows) if rows else torch.zeros(0, self.vocab)
+
+    def end(self, rid):
+        super().end(rid)
+        self.fed.pop(rid, None)
+
+
+class LaunchingSampler:
+    """launch() leaves the chosen ids in `out` (the feed) and hands them over at collect()."""
+
+    def __init__(self, rows=8):
+        self.out = torch.zeros(rows, dtype=torch.int32)
+        self.launched = self.collected = 0
+
+    def launch(self, logits, states):
+        toks = logits.argmax(-1).to(torch.int32)
+        self.out[:len(states)] = toks
+        self.launched += 1
+        return (toks.tolist(), states)
+
+    def collect(self, handle):
+        toks, states = handle
+        self.collected += 1
+        for s, t in zip(states, toks):
+            s.record(t)
+        return toks
+
+    def sample(self, logits, states):
+        return self.collect(self.launch(logits, states))
+
+
+def _run_both(add_requests, late=None, **engine_opts):
+    outs = []
+    for ahead in (False, True):
+        eng = FeedingEngine(**engine_opts)
+        s = Scheduler(eng, LaunchingSampler(), run_ahead=ahead)
+        assert s.run_ahead == ahead
+        ids = add_requests(s)
+        steps = 0
+        while s.has_work():
+            s.step()
+            steps += 1
+            if late is not None and steps == late[0]:
+                ids.append(late[1](s))
+        assert not eng.cache.live and eng.cache.groups[0].pool.free_pages == engine_opts["pages"]
+        outs.append(([s.requests[i].output for i in ids], dict(s.stats), eng.steps))
+    return outs
+
+
+def test_running_ahead_gives_the_same_tokens():
+    def add(s):
+        return [s.add_request([3, 4, 5], 9), s.add_request([6] * 7, 4), s.add_request([1], 12)]
+
+    (want, plain_stats, _), (got, stats, steps) = _run_both(add, pages=32, max_tokens=16)
+    assert got == want and all(len(o) == n for o, n in zip(got, (9, 4, 12)))
+    assert plain_stats["steps_ahead"] == 0 and stats["steps_ahead"] >= 8
+    # a request that ends by its length is left out of the step launched ahead: no row of it is dropped
+    assert stats["rows_dropped"] == 0
+
+
+def test_running_ahead_drops_the_row_of_a_request_stopped_in_mid_flight():
+    probe = FeedingEngine(pages=32, max_tokens=16)
+    s = Scheduler(probe, LaunchingSampler(), run_ahead=False)
+    rid = s.add_request([2, 9, 4], 12)
+    free = s.run()[rid]
+    at = next(k for k in range(4, 12) if free.index(free[k]) == k)
+    stop = free[at]
+
+    def add(s):
+        return [s.add_request([2, 9, 4], 12, stop_ids=[stop]), s.add_request([8, 8], 12)]
+
+    (want, _, _), (got, stats, _) = _run_both(add, pages=32, max_tokens=16)
+    assert got == want and got[0] == free[:at + 1]
+    assert stats["rows_dropped"] == 1
+
+
+def test_running_ahead_pauses_for_arrivals_and_short_pages():
+    def add(s):
+        return [s.add_request([1, 2, 3, 4, 5], 14), s.add_request([7, 7, 7], 14)]
+
+    late = (6, lambda s: s.add_request([9, 9, 9, 9], 6))
+    (want, _, _), (got, stats, steps) = _run_both(add, late, pages=32, max_tokens=16)
+    assert got == want
+    # the arrival's prompt went in beside decoded tokens, in a step planned with all tokens at hand
+    assert any(any(n > 1 for _, n, _ in st) and any(n == 1 for _, n, _ in st) for st in steps)
+    # with pages too few for everybody the ahead path stands back and the push-out logic decides
+    (want, plain_stats, _), (got, stats, _) = _run_both(add, pages=8, max_tokens=16)
+    assert got == want and stats["pushed_out"] >= 1 and stats["pushed_out"] == plain_stats["pushed_out"]
