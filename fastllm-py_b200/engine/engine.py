@@ -41,6 +41,8 @@ class Engine:
                                   config.max_requests, bt_stride)
         self.cache.allocate(self.device, self.dtype)
         # the most key/value heads of any paged cache: how many CTAs a decode token gives the attention kernel
+        self._num_sms = (torch.cuda.get_device_properties(self.device).multi_processor_count
+                         if self.device.type == "cuda" else 148)
         self._kv_heads = max([getattr(need, "kv_heads", 1) for need in decoder.cache_needs().values()] or [1])
         self.workspace = Workspace(self.device, self.max_tokens)
         self.buffers = StepBuffers(self.device, self.max_tokens, config.max_requests,
@@ -194,7 +196,7 @@ class Engine:
         longest = step.max_seq_len
         if self.use_graph and step.max_q_len == 1:
             longest = -(-longest // 1024) * 1024
-        keys = decode_split_keys(max(step.n_decode_tokens, 1), self._kv_heads, longest)
+        keys = decode_split_keys(max(step.n_decode_tokens, 1), self._kv_heads, longest, self._num_sms)
         return keys, decode_splits(longest, keys)
 
     def step(self, entries) -> torch.Tensor:

@@ -101,13 +101,13 @@ def decode_splits(max_seq_len: int, split_keys: int = DECODE_SPLIT) -> int:
     return max(1, -(-max_seq_len // split_keys))
 
 
-def decode_split_keys(n_tokens: int, kv_heads: int, max_seq_len: int) -> int:
+def decode_split_keys(n_tokens: int, kv_heads: int, max_seq_len: int, num_sms: int = 148) -> int:
     """Keys per split for a launch: a CTA streams better the longer its stretch of keys
     (1024-key splits reach 6.5 TB/s where 256-key ones reach 6.0), but only while there are
-    CTAs enough for several rounds over the GPU; with few tokens or short sequences the
-    smallest split gives the most CTAs."""
+    CTAs enough for four or five rounds over the GPU (three CTAs fit an SM); with few tokens
+    or short sequences the smallest split gives the most CTAs."""
     for split in (1024, 512):
-        if n_tokens * kv_heads * -(-max_seq_len // split) >= 2048:
+        if n_tokens * kv_heads * -(-max_seq_len // split) >= 14 * num_sms:
             return split
     return DECODE_SPLIT
 
