@@ -614,12 +614,48 @@ static int launch_tc_persistent(const CUtensorMap& map_w, const CUtensorMap& map
 //     leader's accumulator-empty barrier.
 // No load is multicast.  The two CTAs meet at a cluster barrier after set-up and
 // before they leave, so neither touches the other's barriers outside its life.
-#define TC2_STAGES 6
-#define TC2_STAGE_BYTES (2 * TC_BM * TC_BK * 2)             // 128 weight rows + 128 token rows
-#define TC2_TILE_BYTES (TC2_STAGES * TC2_STAGE_BYTES)
-#define TC2_SMEM (TC2_TILE_BYTES + 256 + 1024)
+// The token side of a pair's tile is BNT = 256, 128 or 64 wide (each CTA holds half of it), so that
+// steps of a few hundred tokens do not compute on padding; a narrower tile leaves room for a deeper
+// ring.  K may be split: a pair's units of work are (tile, K range) pairs, and with more than one
+// split every unit writes its float partial sums to partial[split][token][feature] for the consumer
+// (or the reduce kernel) to add, exactly as the one-tile kernel does.
+template <int BNT>
+struct Tc2 {
+    static constexpr int W_BYTES = TC_BM * TC_BK * 2;              // 128 weight rows of a stage
+    static constexpr int A_BYTES = (BNT / 2) * TC_BK * 2;          // this CTA's half of the token rows
+    static constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
+    static constexpr int STAGES = BNT == 256 ? 6 : (BNT == 128 ? 8 : 9);
+    static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int SMEM = TILE_BYTES + 256 + 1024;        // + the epilogue's area below
+};
 #define TC2_XCH_BYTES (2 * 32 * 64 * 4)                      // GATED: two rounds of 32 tokens x 64 up values
-#define TC2_SMEM_GATED (TC2_SMEM + TC2_XCH_BYTES)
+#define TC2_GATED_OUT_BYTES (2 * 32 * 64 * 4)                // GATED: two rounds of 32 tokens x 64 results
+#define TC2_OUT_BYTES (2 * 32 * 128 * 4)                     // two rounds of 32 tokens x 128 features on their way out
+
+// Rows of 128 (or fewer) values from the epilogue's staging area to global memory, 16 bytes per
+// thread where the destination allows it: `e` is the thread's index among the 128 epilogue threads,
+// `cols` how many of the 128 columns exist.  Written this way a warp stores whole rows of 256 or 512
+// bytes; one value per lane and row (what the accumulator's layout gives) took 40 ns per token.
+template <typename T, int WIDTH>
+__device__ __forceinline__ void tc_copy_rows(T* __restrict__ dst, long ld, const T* __restrict__ src, int rows,
+                                             int cols, int e, bool vec_ok) {
+    constexpr int V = 16 / (int)sizeof(T);                  // values per 16 bytes
+    constexpr int TPR = WIDTH / V;                          // threads per row
+    constexpr int RPP = 128 / TPR;                          // rows per pass
+    const int rr = e / TPR, cc = (e % TPR) * V;
+#pragma unroll
+    for (int p = 0; p < 32 / RPP; ++p) {
+        const int row = p * RPP + rr;
+        if (row >= rows || cc >= cols) continue;
+        T* d = dst + (long)row * ld + cc;
+        const T* s_ = src + row * WIDTH + cc;
+        if (vec_ok && cc + V <= cols) {
+            *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(s_);
+        } else {
+            for (int v = 0; v < V && cc + v < cols; ++v) d[v] = s_[v];
+        }
+    }
+}
 #define TC2_PEER_MASK 0xFEFFFFFFu                          // clears the CTA-rank bit of a shared::cluster address
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -660,30 +696,36 @@ __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {    // arrive
 }
 
 // GATED as in gemm_tc_kernel: each CTA's 128 weight rows are 64 gate rows and the 64 up rows of the
-// same features, a pair's tile is 128 features wide, and the epilogue writes silu(gate) * up.
-template <typename OutT, bool GATED>
+// same features, a pair's tile is 128 features wide, and the epilogue writes silu(gate) * up
+// (whole K only: `splits` is 1 then).
+template <int BNT, typename OutT, bool GATED>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
     OutT* __restrict__ C, long ldc, int M, int N, int K, int tiles_n, int num_tiles,
-    int* __restrict__ status, int gate_rows) {
+    int* __restrict__ status, int gate_rows, int splits, int kb_per_split, float* __restrict__ partial,
+    long ld_partial) {
+    using L = Tc2<BNT>;
+    static_assert(!GATED || BNT == 256, "the gated epilogue is written for 256-token tiles");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full_bar = (uint64_t*)(tiles + TC2_TILE_BYTES);
-    uint64_t* empty_bar = full_bar + TC2_STAGES;
-    uint64_t* acc_full = empty_bar + TC2_STAGES;
+    uint64_t* full_bar = (uint64_t*)(tiles + L::TILE_BYTES);
+    uint64_t* empty_bar = full_bar + L::STAGES;
+    uint64_t* acc_full = empty_bar + L::STAGES;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    float* xch = reinterpret_cast<float*>(tiles + TC2_TILE_BYTES + 256);     // GATED only
+    float* xch = reinterpret_cast<float*>(tiles + L::TILE_BYTES + 256);      // GATED only
+    unsigned char* staged = tiles + L::TILE_BYTES + 256;                      // plain epilogue only
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();                   // 0: leader
     const int pair = (int)blockIdx.x >> 1, num_pairs = (int)gridDim.x >> 1;
     const int num_kb = (K + TC_BK - 1) / TC_BK;
-    const int my_tiles = (pair < num_tiles) ? (num_tiles - 1 - pair) / num_pairs + 1 : 0;
+    const int num_units = num_tiles * splits;
+    const int my_units = (pair < num_units) ? (num_units - 1 - pair) / num_pairs + 1 : 0;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < TC2_STAGES; ++s) {
+        for (int s = 0; s < L::STAGES; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
@@ -710,8 +752,13 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
     // (no programmatic launch attribute, no pdl_trigger): with either, runs in which a CTA pair shared
     // the GPU with another kernel that also allocates tensor memory stalled for good now and then.
 
-    auto tile_coords = [&](int i, int& tn, int& tm) {
-        tc_raster(pair + i * num_pairs, tiles_n, num_tiles / tiles_n, tn, tm);
+    // unit i of this pair: its tile (tn: features, tm: tokens), its split and that split's k-blocks
+    auto unit = [&](int i, int& tn, int& tm, int& split, int& kb0, int& kb1) {
+        const int u = pair + i * num_pairs;
+        split = u / num_tiles;
+        tc_raster(u - split * num_tiles, tiles_n, num_tiles / tiles_n, tn, tm);
+        kb0 = split * kb_per_split;
+        kb1 = min(num_kb, kb0 + kb_per_split);
     };
 
     // this CTA's 128 weight rows of a stage (GATED: 64 gate rows and the 64 up rows of the same features)
@@ -719,56 +766,48 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
         if (GATED) {
             const int f0 = tn * 128 + (int)rank * 64;
             tma_load_2d_pair(dst, &map_w, bar, kb * TC_BK, f0);
-            tma_load_2d_pair(dst + TC2_STAGE_BYTES / 4, &map_w, bar, kb * TC_BK, gate_rows + f0);
+            tma_load_2d_pair(dst + L::W_BYTES / 2, &map_w, bar, kb * TC_BK, gate_rows + f0);
         } else {
             tma_load_2d_pair(dst, &map_w, bar, kb * TC_BK, tn * 256 + (int)rank * TC_BM);
         }
     };
 
     if (warp == 0) {
-        if (lane == 0) {
-            // ---- producer (both CTAs): this CTA's 128 weight rows and 128 token rows of each stage
-            const int total = my_tiles * num_kb;
-            const int ahead = *abort_flag ? 0 : (total < TC2_STAGES ? total : TC2_STAGES);
-            int tn, tm, ti = 0, kb = 0;
-            tile_coords(0, tn, tm);
-            for (int it = 0; it < ahead; ++it) {           // weights first: no kernel writes them
-                if (rank == 0) mbar_expect_tx(&full_bar[it], 2 * TC2_STAGE_BYTES);
-                load_weights(tiles + it * TC2_STAGE_BYTES, &full_bar[it], kb, tn);
-                if (++kb == num_kb) { kb = 0; tile_coords(++ti, tn, tm); }
-            }
+        if (lane == 0 && !*abort_flag) {
+            // ---- producer (both CTAs): this CTA's 128 weight rows and BNT/2 token rows of each stage,
+            // unit after unit, k-block after k-block, through the ring
             pdl_wait();
-            ti = 0; kb = 0;
-            tile_coords(0, tn, tm);
-            for (int it = 0; it < ahead; ++it) {
-                tma_load_2d_pair(tiles + it * TC2_STAGE_BYTES + TC2_STAGE_BYTES / 2, &map_a, &full_bar[it],
-                                 kb * TC_BK, tm * 256 + (int)rank * TC_BM);
-                if (++kb == num_kb) { kb = 0; tile_coords(++ti, tn, tm); }
-            }
-            int s = ahead % TC2_STAGES;
-            uint32_t ph = (uint32_t)(ahead / TC2_STAGES) & 1u;
-            for (int it = ahead; it < total && !*abort_flag; ++it) {
-                if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
-                    if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_EMPTY_WAIT); }
-                    break;
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int i = 0; i < my_units && ok; ++i) {
+                int tn, tm, split, kb0, kb1;
+                unit(i, tn, tm, split, kb0, kb1);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_EMPTY_WAIT); }
+                        ok = false;
+                        break;
+                    }
+                    unsigned char* dst = tiles + s * L::STAGE_BYTES;
+                    if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * L::STAGE_BYTES);
+                    load_weights(dst, &full_bar[s], kb, tn);
+                    tma_load_2d_pair(dst + L::W_BYTES, &map_a, &full_bar[s], kb * TC_BK,
+                                     tm * BNT + (int)rank * (BNT / 2));
+                    if (++s == L::STAGES) { s = 0; ph ^= 1u; }
                 }
-                unsigned char* a_dst = tiles + s * TC2_STAGE_BYTES;
-                if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * TC2_STAGE_BYTES);
-                load_weights(a_dst, &full_bar[s], kb, tn);
-                tma_load_2d_pair(a_dst + TC2_STAGE_BYTES / 2, &map_a, &full_bar[s], kb * TC_BK,
-                                 tm * 256 + (int)rank * TC_BM);
-                if (++kb == num_kb) { kb = 0; tile_coords(++ti, tn, tm); }
-                if (++s == TC2_STAGES) { s = 0; ph ^= 1u; }
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
-            // ---- MMA issuer (leader only): one 256 x 256 x 16 MMA per 16 columns of K, for both CTAs
-            constexpr uint32_t idesc = instr_desc_bf16(256, 256);
+            // ---- MMA issuer (leader only): one 256 x BNT x 16 MMA per 16 columns of K, for both CTAs
+            constexpr uint32_t idesc = instr_desc_bf16(256, BNT);
             int s = 0;
             uint32_t ph = 0;
             bool ok = !*abort_flag;
-            for (int i = 0; i < my_tiles && ok; ++i) {
+            for (int i = 0; i < my_units && ok; ++i) {
+                int tn, tm, split, kb0, kb1;
+                unit(i, tn, tm, split, kb0, kb1);
                 const int buf = i & 1;
                 const uint32_t use = (uint32_t)(i >> 1);
                 if (!mbar_wait(&acc_empty[buf], (use & 1u) ^ 1u, abort_flag)) {
@@ -778,22 +817,22 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
                 }
                 tc_fence_after();
                 const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * 256);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(&full_bar[s], ph, abort_flag)) {
                         if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_FULL_WAIT); }
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(tiles + s * TC2_STAGE_BYTES);
-                    const uint64_t adesc = smem_desc_sw128(a_addr);
-                    const uint64_t bdesc = smem_desc_sw128(a_addr + TC2_STAGE_BYTES / 2);
+                    const uint32_t w_addr = smem_u32(tiles + s * L::STAGE_BYTES);
+                    const uint64_t adesc = smem_desc_sw128(w_addr);
+                    const uint64_t bdesc = smem_desc_sw128(w_addr + L::W_BYTES);
 #pragma unroll
                     for (int k = 0; k < TC_BK / 16; ++k)
                         umma_bf16_pair(tmem_acc, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                                       (kb > 0 || k > 0) ? 1u : 0u);
+                                       (kb > kb0 || k > 0) ? 1u : 0u);
                     umma_commit_pair(&empty_bar[s]);
-                    if (++s == TC2_STAGES) { s = 0; ph ^= 1u; }
+                    if (++s == L::STAGES) { s = 0; ph ^= 1u; }
                 }
                 if (ok) umma_commit_pair(&acc_full[buf]);
             }
@@ -801,25 +840,24 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
     } else {
         // ---- epilogue warps 2..5 of both CTAs: this CTA's 128 output features of the pair's tile
         const int quarter = warp & 3;
-        bool ok = GATED ? true : !*abort_flag;
+        bool ok = true;
+        uint32_t rounds_out = 0;                            // 32-token rounds written so far: picks the staging half
         pdl_wait();
-        for (int i = 0; i < my_tiles && ok; ++i) {
+        for (int i = 0; i < my_units && ok; ++i) {
             const int buf = i & 1;
             const uint32_t use = (uint32_t)(i >> 1);
             bool got = mbar_wait(&acc_full[buf], use & 1u, abort_flag);
             if (!got && !*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_ACC_WAIT); }
-            if (GATED) {                                    // the four warps decide together (they share a barrier below)
-                epilogue_sync();
-                got = !*abort_flag;
-            }
+            epilogue_sync();                                // the four warps decide together (they share barriers below)
+            got = !*abort_flag;
             if (!got) {
                 ok = false;
                 break;
             }
             tc_fence_after();
-            int tn, tm;
-            tile_coords(i, tn, tm);
-            const int t0 = tm * 256;
+            int tn, tm, split, kb0, kb1;
+            unit(i, tn, tm, split, kb0, kb1);
+            const int t0 = tm * BNT;
             const uint32_t t_base = tmem_base + (uint32_t)(buf * 256) + ((uint32_t)(quarter * 32) << 16);
             if (GATED) {
                 // accumulator lanes 0..63: gate features, 64..127: the same features' up values; the
@@ -827,47 +865,71 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
                 // the other side needs through shared memory, 32 tokens at a time
                 const bool is_up = quarter >= 2;
                 const int col = (quarter & 1) * 32 + lane;
-                const int f = tn * 128 + (int)rank * 64 + col;
+                const int f0 = tn * 128 + (int)rank * 64;   // first of this CTA's 64 features
+                const bool vec_ok = (((uintptr_t)C | (uintptr_t)(ldc * (long)sizeof(OutT))) & 15) == 0;
 #pragma unroll 1
-                for (int c = 0; c < 256; c += 32) {
+                for (int c = 0; c < BNT; c += 32) {
                     if (t0 + c >= M) break;                 // uniform over the four warps
                     uint32_t r[32];
                     tmem_ld16(t_base + (uint32_t)c, r);
                     tmem_ld16(t_base + (uint32_t)c + 16u, r + 16);
                     tmem_ld_wait();
-                    float* x = xch + ((c >> 5) & 1) * (32 * 64);
+                    const uint32_t half = rounds_out++ & 1u;
+                    float* x = xch + half * (32 * 64);
+                    OutT* st = reinterpret_cast<OutT*>(staged + TC2_XCH_BYTES) + half * (32 * 64);
                     const int mine = is_up ? 1 : 0;         // parity of the tokens this warp finishes
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         if ((j & 1) != mine)
                             x[j * 64 + col] = to_f32<OutT>(from_f32<OutT>(__uint_as_float(r[j])));
                     epilogue_sync();
-                    if (f < N) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if ((j & 1) != mine) continue;
-                            const int t = t0 + c + j;
-                            const float own = to_f32<OutT>(from_f32<OutT>(__uint_as_float(r[j])));
-                            const float other = x[j * 64 + col];
-                            if (t < M) C[(long)t * ldc + f] = from_f32<OutT>(is_up ? gated_act(other, own) : gated_act(own, other));
-                        }
+                    for (int j = 0; j < 32; ++j) {
+                        if ((j & 1) != mine) continue;
+                        const float own = to_f32<OutT>(from_f32<OutT>(__uint_as_float(r[j])));
+                        const float other = x[j * 64 + col];
+                        st[j * 64 + col] = from_f32<OutT>(is_up ? gated_act(other, own) : gated_act(own, other));
                     }
+                    epilogue_sync();                        // the 32 x 64 results leave as whole rows
+                    if (f0 < N)
+                        tc_copy_rows<OutT, 64>(C + (long)(t0 + c) * ldc + f0, ldc, st, min(32, M - (t0 + c)),
+                                               min(N - f0, 64), quarter * 32 + lane, vec_ok);
                 }
             } else {
-                const int o = tn * 256 + (int)rank * TC_BM + quarter * 32 + lane;
+                // each thread holds one feature's values of 32 tokens at a time: they go through shared memory
+                // ([token][feature], alternating halves so that one barrier per round is enough) and leave as
+                // whole rows
+                const int e = quarter * 32 + lane;              // this thread's feature among the CTA's 128
+                const int o0 = tn * 256 + (int)rank * TC_BM;
+                const int cols = N - o0;                        // features of this CTA that exist (may be <= 0)
+                float* slab = splits > 1 ? partial + (long)split * M * ld_partial : nullptr;
+                const bool vec_ok = slab ? ((((uintptr_t)slab | (uintptr_t)(ld_partial * 4)) & 15) == 0)
+                                         : ((((uintptr_t)C | (uintptr_t)(ldc * (long)sizeof(OutT))) & 15) == 0);
 #pragma unroll 1
-                for (int c = 0; c < 256; c += 32) {
-                    if (t0 + c >= M) break;
+                for (int c = 0; c < BNT; c += 32) {
+                    if (t0 + c >= M) break;                     // uniform over the four warps
                     uint32_t r[32];
                     tmem_ld16(t_base + (uint32_t)c, r);
                     tmem_ld16(t_base + (uint32_t)c + 16u, r + 16);
                     tmem_ld_wait();
-                    if (o < N) {
+                    unsigned char* half = staged + (rounds_out++ & 1u) * (TC2_OUT_BYTES / 2);
+                    const int rows = min(32, M - (t0 + c));
+                    if (slab) {
+                        float* st = reinterpret_cast<float*>(half);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const int t = t0 + c + j;
-                            if (t < M) C[(long)t * ldc + o] = from_f32<OutT>(__uint_as_float(r[j]));
-                        }
+                        for (int j = 0; j < 32; ++j) st[j * 128 + e] = __uint_as_float(r[j]);
+                        epilogue_sync();
+                        if (cols > 0)
+                            tc_copy_rows<float, 128>(slab + (long)(t0 + c) * ld_partial + o0, ld_partial, st, rows,
+                                                     min(cols, 128), e, vec_ok);
+                    } else {
+                        OutT* st = reinterpret_cast<OutT*>(half);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) st[j * 128 + e] = from_f32<OutT>(__uint_as_float(r[j]));
+                        epilogue_sync();
+                        if (cols > 0)
+                            tc_copy_rows<OutT, 128>(C + (long)(t0 + c) * ldc + o0, ldc, st, rows, min(cols, 128), e,
+                                                    vec_ok);
                     }
                 }
             }
@@ -889,37 +951,51 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
     cluster_sync_all();
 }
 
-template <typename OutT, bool GATED = false>
+template <int BNT, typename OutT, bool GATED = false>
 static int launch_tc_pair(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C, long ldc, int M, int N,
-                          int K, int num_sms, int* status, cudaStream_t stream, int gate_rows = 0) {
+                          int K, int num_sms, int* status, cudaStream_t stream, int gate_rows = 0, int splits = 1,
+                          int kb_per_split = 0, float* partial = nullptr, long ld_partial = 0) {
     static bool configured = false;
-    auto kernel = gemm_tc_pair_kernel<OutT, GATED>;
-    constexpr int smem = GATED ? TC2_SMEM_GATED : TC2_SMEM;
+    auto kernel = gemm_tc_pair_kernel<BNT, OutT, GATED>;
+    constexpr int smem = Tc2<BNT>::SMEM + (GATED ? TC2_XCH_BYTES + TC2_GATED_OUT_BYTES : TC2_OUT_BYTES);
+    static_assert(smem <= 232448, "more shared memory than a CTA can have");
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const int tiles_n = GATED ? (N + 127) / 128 : (N + 255) / 256;
-    const int num_tiles = tiles_n * ((M + 255) / 256);
-    const int pairs = num_tiles < num_sms / 2 ? num_tiles : num_sms / 2;
+    const int num_tiles = tiles_n * ((M + BNT - 1) / BNT);
+    const long num_units = (long)num_tiles * splits;
+    const int pairs = num_units < num_sms / 2 ? (int)num_units : num_sms / 2;
+    if (splits == 1) kb_per_split = (K + TC_BK - 1) / TC_BK;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs);
     cfg.blockDim = dim3(TC_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
+    cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     // Launched in plain stream order (no programmatic overlap with its neighbours): see the note in the kernel.
     cfg.numAttrs = 1;
     return (int)cudaLaunchKernelEx(&cfg, kernel, map_w, map_a, (OutT*)C, ldc, M, N, K, tiles_n, num_tiles, status,
-                                   gate_rows);
+                                   gate_rows, splits, kb_per_split, partial, ld_partial);
+}
+
+template <typename OutT>
+static int dispatch_tc_pair(int bnt, const CUtensorMap& map_w, const CUtensorMap& map_a, void* C, long ldc, int M,
+                            int N, int K, int num_sms, int* status, cudaStream_t stream, int splits,
+                            int kb_per_split, float* partial, long ld_partial) {
+    switch (bnt) {
+        case 64: return launch_tc_pair<64, OutT>(map_w, map_a, C, ldc, M, N, K, num_sms, status, stream, 0, splits, kb_per_split, partial, ld_partial);
+        case 128: return launch_tc_pair<128, OutT>(map_w, map_a, C, ldc, M, N, K, num_sms, status, stream, 0, splits, kb_per_split, partial, ld_partial);
+        case 256: return launch_tc_pair<256, OutT>(map_w, map_a, C, ldc, M, N, K, num_sms, status, stream, 0, splits, kb_per_split, partial, ld_partial);
+    }
+    return (int)cudaErrorInvalidValue;
 }
 
 // C[t, o] = sum over splits of partial[z][t][o], added in the order z = 0, 1, ...
@@ -1001,11 +1077,11 @@ static int dispatch_tc(int bn, const CUtensorMap& map_w, const CUtensorMap& map_
     return (int)cudaErrorInvalidValue;
 }
 
-// Token-tile width and K splits for a problem: the smallest tile that holds the
-// tokens (up to 256), and as many splits as it takes to give every SM a CTA or two.
-// Products of more than 128 tokens that need no split go to the CTA-pair kernel,
-// reported as width 512.
-FL_API void fl_gemm_tc_plan(int M, int N, int K, int num_sms, int* bn_out, int* splits_out) {
+// Token-tile width and K splits of the one-tile kernel for a problem: the smallest
+// tile that holds the tokens (up to 256), and as many splits as it takes to give
+// every SM a CTA or two.  Products of more than 128 tokens that need no split go to
+// the CTA-pair kernel, reported as width 512.
+static void plan_one_tile(int M, int N, int K, int num_sms, int* bn_out, int* splits_out) {
     int bn = 16;
     while (bn < 256 && bn < M) bn *= 2;
     const int tiles = ((N + TC_BM - 1) / TC_BM) * ((M + bn - 1) / bn);
@@ -1027,6 +1103,40 @@ FL_API void fl_gemm_tc_plan(int M, int N, int K, int num_sms, int* bn_out, int* 
     if (bn == 256 && splits == 1 && num_sms >= 2) bn = 512;     // 512 stands for the CTA-pair kernel (256 x 256 tiles)
     *bn_out = bn;
     *splits_out = splits;
+}
+
+// The plan for a product: up to 64 tokens the one-tile kernel (it overlaps with its
+// neighbours in the stream, which counts most for the short kernels of a decode step);
+// above that the CTA-pair kernel, reported as 512 + its token-tile width (640: 128
+// tokens wide) or plain 512 for 256 tokens.  Its K splits come from a small cost model
+// in microseconds, fitted to measurements on B200: a pair spends 0.28 us on a 64-deep
+// K step of either tile width and about 1 us between units; partial sums cost their
+// bytes once out and once back in at about 3 TB/s.
+FL_API void fl_gemm_tc_plan(int M, int N, int K, int num_sms, int* bn_out, int* splits_out) {
+    if (M <= 64 || num_sms < 2) {
+        plan_one_tile(M, N, K, num_sms, bn_out, splits_out);
+        return;
+    }
+    const int bnt = M <= 128 ? 128 : 256;
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const long tiles = (long)((N + 255) / 256) * ((M + bnt - 1) / bnt);
+    const int pairs = num_sms / 2;
+    int best = 1;
+    double best_cost = 0.0;
+    for (int sp = 1; sp <= 16; ++sp) {
+        const int per = (num_kb + sp - 1) / sp;
+        if ((num_kb + per - 1) / per != sp) continue;           // no empty split
+        if (sp > 1 && per < 4) break;
+        const long rounds = (tiles * sp + pairs - 1) / pairs;
+        double cost = (double)rounds * (0.28 * per + 1.0);
+        if (sp > 1) cost += (double)sp * M * N * 4.0 / 3.0e6;
+        if (sp == 1 || cost < best_cost * 0.95) {               // a split has to pay for the trouble
+            best = sp;
+            best_cost = cost;
+        }
+    }
+    *bn_out = bnt == 256 ? 512 : 512 + bnt;
+    *splits_out = best;
 }
 
 // A: [M, K] bfloat16 with lda elements between rows; W: [N, K] bfloat16 with ldw;
@@ -1051,26 +1161,30 @@ static int gemm_tc_impl(const void* A, long lda, const void* W, long ldw, void* 
     CUtensorMap map_w, map_a;
     int rc = make_map(&map_w, W, N, K, ldw, TC_BM);
     if (rc) return rc;
-    rc = make_map(&map_a, A, M, K, lda, bn > 256 ? TC_BM : bn);
+    const bool paired = bn >= 512;                           // 512, 640, 576: pair kernel, 256 / 128 / 64 tokens wide
+    const int bnt = bn == 512 ? 256 : bn - 512;
+    if (paired && (num_sms < 2 || (bnt != 64 && bnt != 128 && bnt != 256))) return (int)cudaErrorInvalidValue;
+    rc = make_map(&map_a, A, M, K, lda, paired ? bnt / 2 : bn);
     if (rc) return rc;
-    if (bn == 512 && splits == 1 && num_sms >= 2) {          // the pair kernel: both operands in 128-row boxes
-        rc = make_map(&map_a, A, M, K, lda, TC_BM);
-        if (rc) return rc;
-        if (c_dtype == FL_BF16) return launch_tc_pair<bf16>(map_w, map_a, C, ldc, M, N, K, num_sms, status, stream);
-        if (c_dtype == FL_F32) return launch_tc_pair<float>(map_w, map_a, C, ldc, M, N, K, num_sms, status, stream);
-        return (int)cudaErrorInvalidValue;
-    }
-    if (bn == TCP_BN && splits == 1 && num_sms > 0) {
+    if (paired) {                                            // each CTA of a pair loads half of the token rows
+        float* part = splits > 1 ? workspace : nullptr;
+        if (c_dtype == FL_BF16)
+            rc = dispatch_tc_pair<bf16>(bnt, map_w, map_a, C, ldc, M, N, K, num_sms, status, stream, splits, kb_per_split, part, ld_partial);
+        else if (c_dtype == FL_F32)
+            rc = dispatch_tc_pair<float>(bnt, map_w, map_a, C, ldc, M, N, K, num_sms, status, stream, splits, kb_per_split, part, ld_partial);
+        else
+            return (int)cudaErrorInvalidValue;
+    } else if (bn == TCP_BN && splits == 1 && num_sms > 0) {
         if (c_dtype == FL_BF16) return launch_tc_persistent<bf16>(map_w, map_a, C, ldc, M, N, K, num_sms, status, stream);
         if (c_dtype == FL_F32) return launch_tc_persistent<float>(map_w, map_a, C, ldc, M, N, K, num_sms, status, stream);
         return (int)cudaErrorInvalidValue;
-    }
-    if (c_dtype == FL_BF16)
+    } else if (c_dtype == FL_BF16) {
         rc = dispatch_tc<bf16>(bn, map_w, map_a, C, ldc, workspace, ld_partial, M, N, K, splits, kb_per_split, status, stream);
-    else if (c_dtype == FL_F32)
+    } else if (c_dtype == FL_F32) {
         rc = dispatch_tc<float>(bn, map_w, map_a, C, ldc, workspace, ld_partial, M, N, K, splits, kb_per_split, status, stream);
-    else
+    } else {
         return (int)cudaErrorInvalidValue;
+    }
     if (rc || splits == 1 || skip_reduce) return rc;
     dim3 grid((N + 255) / 256, M);
     if (c_dtype == FL_BF16)
@@ -1106,7 +1220,7 @@ FL_API int fl_gemm_tc_swiglu(const void* A, long lda, const void* W, long ldw, v
     if (M <= 0 || I <= 0) return 0;
     if (K <= 0) return (int)cudaErrorInvalidValue;
     int bn = 0, splits = 0;
-    fl_gemm_tc_plan(M, 2 * I, K, num_sms, &bn, &splits);
+    plan_one_tile(M, 2 * I, K, num_sms, &bn, &splits);          // (the pair kernel's narrower tiles have no gated form)
     if (splits != 1 || bn == 256) return -1;
     if ((M + (bn > 256 ? 256 : bn) - 1) / (bn > 256 ? 256 : bn) > 65535) return (int)cudaErrorInvalidValue;
     CUtensorMap map_w, map_a;
@@ -1114,7 +1228,7 @@ FL_API int fl_gemm_tc_swiglu(const void* A, long lda, const void* W, long ldw, v
     if (rc) return rc;
     rc = make_map(&map_a, A, M, K, lda, bn > 256 ? TC_BM : bn);
     if (rc) return rc;
-    if (bn == 512) return launch_tc_pair<bf16, true>(map_w, map_a, C, ldc, M, I, K, num_sms, status, stream, I);
+    if (bn == 512) return launch_tc_pair<256, bf16, true>(map_w, map_a, C, ldc, M, I, K, num_sms, status, stream, I);
     const int kb = (K + TC_BK - 1) / TC_BK;
     switch (bn) {
         case 16: return launch_tc<16, 6, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I);

@@ -61,6 +61,54 @@ def test_tensor_core_gemm_every_tile_and_split(bn, splits):
     assert float((out.cpu() - ref).abs().max()) <= 1e-3 * math.sqrt(k)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("bn, splits, m", [(576, 1, 90), (576, 3, 33), (640, 1, 150), (640, 4, 261), (512, 1, 300),
+                                           (512, 2, 517), (512, 6, 40)])
+def test_tensor_core_gemm_in_cta_pairs_every_tile_and_split(bn, splits, m, out_dtype):
+    """The CTA-pair kernel, forced, with token tiles of 64, 128 and 256 (codes 576, 640, 512), whole K and
+    split K, token and feature counts that end inside a tile, an output pitch wider than the
+    product and, for one case, an output that is not 16-byte aligned (its rows then leave one
+    value at a time); and the same product left as partial sums."""
+    from fastllm_py_b200.native import gemm_tc
+
+    n, k = 300 + 256 * (splits % 2), 64 * 11 + 24
+    g = torch.Generator(device="cpu").manual_seed(bn + splits + m)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = torch.randn(n, k, generator=g).to(torch.bfloat16)
+    ref = a.float() @ w.float().t()
+    tol = 1e-3 * math.sqrt(k) if out_dtype == torch.float32 else 2 ** -8 * float(ref.abs().max()) + 1e-3
+    for shift in (0, 1):
+        pitch = n + 8 + shift                               # shift 1: rows no longer start on 16 bytes
+        out = torch.full((m, pitch), -5.0, dtype=out_dtype, device=DEV)
+        gemm_tc.gemm(a.to(DEV), w.to(DEV), out[:, shift:shift + n], bn=bn, splits=splits)
+        torch.cuda.synchronize()
+        assert int(gemm_tc.status_word(torch.device(DEV)).item()) == 0
+        assert torch.all(out[:, shift + n:] == -5.0) and torch.all(out[:, :shift] == -5.0), "wrote outside the output"
+        assert float((out[:, shift:shift + n].float().cpu() - ref).abs().max()) <= tol
+    if splits > 1:
+        out = torch.full((m, n), -5.0, dtype=out_dtype, device=DEV)
+        part = gemm_tc.gemm(a.to(DEV), w.to(DEV), out, bn=bn, splits=splits, defer=True)
+        torch.cuda.synchronize()
+        assert part is not None and part.splits == splits and torch.all(out == -5.0)
+        slabs = part.data[:splits * part.split_stride].view(splits, m, part.ld)[:, :, :n]
+        assert float((slabs.sum(0).cpu() - ref).abs().max()) <= 1e-3 * math.sqrt(k)
+
+
+def test_tensor_core_gemm_plan_is_launchable():
+    """What the plan answers for many problem sizes is a kernel the launcher has, with no empty split."""
+    from fastllm_py_b200.native import gemm_tc
+
+    for m in (1, 7, 64, 65, 128, 129, 300, 1000, 5000):
+        for n, k in ((64, 64), (300, 1000), (4096, 4096), (12288, 4096), (4096, 11008), (102400, 4096)):
+            bn, splits = gemm_tc.plan(m, n, k, 148)
+            assert bn in (16, 32, 64, 128, 256, 512, 576, 640)
+            kb = -(-k // 64)
+            per = -(-kb // splits)
+            assert 1 <= splits <= 16 and (splits - 1) * per < kb
+            if m > 64:
+                assert bn == (640 if m <= 128 else 512)
+
+
 @pytest.mark.parametrize("a_dt, w_dt, c_dt", [(torch.float32, torch.float32, torch.float32),
                                               (torch.float32, torch.bfloat16, torch.float32),
                                               (torch.bfloat16, torch.float32, torch.bfloat16),
