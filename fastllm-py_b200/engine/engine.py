@@ -44,6 +44,7 @@ class Engine:
         self._num_sms = (torch.cuda.get_device_properties(self.device).multi_processor_count
                          if self.device.type == "cuda" else 148)
         self._kv_heads = max([getattr(need, "kv_heads", 1) for need in decoder.cache_needs().values()] or [1])
+        self._head_dim = max([getattr(need, "head_dim", 128) for need in decoder.cache_needs().values()] or [128])
         self.workspace = Workspace(self.device, self.max_tokens)
         self.buffers = StepBuffers(self.device, self.max_tokens, config.max_requests,
                                    len(self.cache.groups), bt_stride)
@@ -190,13 +191,17 @@ class Engine:
     def _decode_splits(self, step: StepContext):
         """(keys per split, splits) for the decode attention kernel: enough splits
         for the longest sequence of the step.  Under graph replay both are part of
-        the graph's key, so the length moves in buckets of 1024 keys."""
-        from ..native.attention import decode_split_keys, decode_splits
+        the graph's key: the keys per split change with the length every 256 tokens at
+        most, and the splits cover the length rounded up to 1024 (CTAs of splits beyond
+        a sequence's end leave at once)."""
+        from ..native.attention import DECODE_SPLIT, decode_split_keys, decode_splits
 
+        if step.n_decode_tokens == 0:                       # no launch of that kernel: one answer, one graph key
+            return DECODE_SPLIT, 1
         longest = step.max_seq_len
+        keys = decode_split_keys(step.n_decode_tokens, self._kv_heads, longest, self._num_sms, self._head_dim)
         if self.use_graph and step.max_q_len == 1:
             longest = -(-longest // 1024) * 1024
-        keys = decode_split_keys(max(step.n_decode_tokens, 1), self._kv_heads, longest, self._num_sms)
         return keys, decode_splits(longest, keys)
 
     def step(self, entries) -> torch.Tensor:

@@ -8,6 +8,8 @@ the other two are tested against.
 """
 from __future__ import annotations
 
+import functools
+
 from ctypes import c_float, c_int, c_long, c_void_p
 
 import torch
@@ -15,7 +17,7 @@ import torch
 from . import ops
 from .build import load_library
 
-DECODE_SPLIT = 256          # the smallest split of the decode kernel, in keys (larger ones are multiples)
+DECODE_SPLIT = 256          # keys per split of the decode kernel when nothing chooses (any multiple of 64 will do)
 _libs: dict = {}
 _state: dict = {}
 
@@ -101,15 +103,51 @@ def decode_splits(max_seq_len: int, split_keys: int = DECODE_SPLIT) -> int:
     return max(1, -(-max_seq_len // split_keys))
 
 
-def decode_split_keys(n_tokens: int, kv_heads: int, max_seq_len: int, num_sms: int = 148) -> int:
-    """Keys per split for a launch: a CTA streams better the longer its stretch of keys
-    (1024-key splits reach 6.5 TB/s where 256-key ones reach 6.0), but only while there are
-    CTAs enough for four or five rounds over the GPU (three CTAs fit an SM); with few tokens
-    or short sequences the smallest split gives the most CTAs."""
-    for split in (1024, 512):
-        if n_tokens * kv_heads * -(-max_seq_len // split) >= 14 * num_sms:
-            return split
-    return DECODE_SPLIT
+def _decode_time(groups: int, length: int, split: int, slots: int, head_dim: int) -> float:
+    """Modelled microseconds of the decode kernel and its merge for `groups` (token, key/value
+    head) pairs of `length` keys each, cut every `split` keys: the larger of the time to stream
+    the keys and values (6.9 TB/s at best, a little less with short splits, and a last split that
+    leaves warps of its CTA idle streams that much slower) and the time the CTAs take in rounds
+    of `slots` (a CTA by itself: 4 us and 22 ns a key; a last split shorter than the others is
+    as long as its busiest warp, a quarter of a split), plus the merge, which reads split after
+    split."""
+    scale = head_dim / 128.0
+    n = -(-length // split)
+    last = length - (n - 1) * split
+    busy = min(1.0, -(-4 * last // split) / 4.0)            # share of its four warps that a last, shorter split keeps busy
+    stream = groups * ((n - 1) * split + last / busy) * 4.0 * head_dim / (6.9e6 * split / (split + 16.0))
+    alone = 4.0 + split * 0.022 * scale
+    short = 4.0 + min(split, 4 * last) * 0.022 * scale
+    whole = groups * (n - 1)                                # CTAs of whole splits, in rounds of `slots`
+    rounds = -(-whole // slots)
+    left = max(0, groups - (rounds * slots - whole))        # short CTAs that find no place beside them
+    in_rounds = rounds * alone + -(-left // slots) * short
+    return max(stream, in_rounds) + 0.2 * n
+
+
+@functools.lru_cache(maxsize=4096)
+def decode_split_keys(n_tokens: int, kv_heads: int, max_seq_len: int, num_sms: int = 148,
+                      head_dim: int = 128) -> int:
+    """Keys per split for a launch, a multiple of 64 up to 1024: the one a small model of the
+    kernel's time likes best.  One CTA serves one (token, key/value head, split); three CTAs
+    fit an SM, so CTAs run in rounds of 3 x SMs.  Constants fitted to measurements on B200
+    (batch 1 to 64, 300 to 4000 keys): the pick is within a few percent of the best there,
+    where a fixed 256 keys was 11 % off on average (few CTAs: a round and a bit of small ones
+    is worse than one round of larger ones; many: the longer the split the better it streams).
+
+    The answer is the same for all lengths of a stretch of 256 (the model is asked about both
+    ends of the stretch), so that a sequence that grows changes its split, and with it the
+    rounding of its result and the shape of a captured step, every 256 tokens at most."""
+    slots = 3 * num_sms
+    groups = n_tokens * kv_heads
+    high = -(-max(max_seq_len, 1) // 256) * 256
+    low = high - 255
+    best_split, best_time = DECODE_SPLIT, None
+    for split in range(64, 1025, 64):
+        t = _decode_time(groups, low, split, slots, head_dim) + _decode_time(groups, high, split, slots, head_dim)
+        if best_time is None or t < best_time:
+            best_split, best_time = split, t
+    return best_split
 
 
 def decode_attention(q, out, cache_tensor, block_table, tok_req, positions, tok_list, n_list, heads,

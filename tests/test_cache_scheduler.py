@@ -412,3 +412,20 @@ def test_running_ahead_pauses_for_arrivals_and_short_pages():
     # with pages too few for everybody the ahead path stands back and the push-out logic decides
     (want, plain_stats, _), (got, stats, _) = _run_both(add, pages=8, max_tokens=16)
     assert got == want and stats["pushed_out"] >= 1 and stats["pushed_out"] == plain_stats["pushed_out"]
+
+
+def test_keys_per_split_of_the_decode_kernel():
+    """The choice is a multiple of 64 the kernel takes, short for a lone short sequence (many small
+    CTAs), long when there are rounds of CTAs anyway, and the same for the same question."""
+    from fastllm_py_b200.native.attention import decode_split_keys, decode_splits
+
+    for n_tokens in (1, 3, 8, 64, 300):
+        for kv_heads in (1, 8, 32):
+            for longest in (1, 63, 64, 65, 500, 2049, 4096, 100000):
+                for head_dim in (16, 128, 256):
+                    keys = decode_split_keys(n_tokens, kv_heads, longest, 148, head_dim)
+                    assert keys % 64 == 0 and 64 <= keys <= 1024
+                    assert decode_splits(longest, keys) * keys >= longest
+    assert decode_split_keys(1, 32, 300) <= 128
+    assert decode_split_keys(64, 32, 2049) >= 512
+    assert decode_split_keys(8, 32, 2304) == decode_split_keys(8, 32, 2304)

@@ -422,14 +422,16 @@ def test_rope_and_cache_write(dtype, heads, kv_heads, head_dim, rot, page_size):
         assert float((cache2.float() - cache.float()).abs().max()) <= tol2
 
 
-@pytest.mark.parametrize("dim", [64, 70, 200, 4096, 5000])
-def test_partial_sum_consumers(dim):
-    """add+RMSNorm and SwiGLU reading split-K partial sums equal the same kernels on the summed input."""
+@pytest.mark.parametrize("n", [5, 40])
+@pytest.mark.parametrize("dim", [64, 70, 200, 1024, 1028, 4096, 5000, 9000])
+def test_partial_sum_consumers(dim, n):
+    """add+RMSNorm and SwiGLU reading split-K partial sums equal the same kernels on the summed input
+    (rows of up to 8192 values in 16-byte chunks stay in registers; wider or odd ones go element by element)."""
     from fastllm_py_b200.native import ops
     from fastllm_py_b200.native.gemm_tc import Partial
 
     g = torch.Generator().manual_seed(dim)
-    n, splits = 5, 4
+    splits = 4
     ld = -(-dim // 4) * 4
     parts = torch.randn(splits, n, ld, generator=g)
     total = parts[:, :, :dim].sum(0)
