@@ -152,6 +152,32 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
            ((uint32_t)(m >> 4) << 24);
 }
 
+// Rows of 128 (or fewer) values from the epilogue's staging area to global memory, 16 bytes per
+// thread where the destination allows it: `e` is the thread's index among the 128 epilogue threads,
+// `cols` how many of the 128 columns exist.  Written this way a warp stores whole rows of 256 or 512
+// bytes; one value per lane and row (what the accumulator's layout gives) took 40 ns per token.
+template <typename T, int WIDTH, int ROWS = 32>
+__device__ __forceinline__ void tc_copy_rows(T* __restrict__ dst, long ld, const T* __restrict__ src, int rows,
+                                             int cols, int e, bool vec_ok) {
+    constexpr int V = 16 / (int)sizeof(T);                  // values per 16 bytes
+    constexpr int TPR = WIDTH / V;                          // threads per row
+    constexpr int RPP = 128 / TPR;                          // rows per pass
+    const int rr = e / TPR, cc = (e % TPR) * V;
+#pragma unroll
+    for (int p = 0; p < (ROWS + RPP - 1) / RPP; ++p) {
+        const int row = p * RPP + rr;
+        if (row >= rows || cc >= cols) continue;
+        T* d = dst + (long)row * ld + cc;
+        const T* s_ = src + row * WIDTH + cc;
+        if (vec_ok && cc + V <= cols) {
+            *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(s_);
+        } else {
+            for (int v = 0; v < V && cc + v < cols; ++v) d[v] = s_[v];
+        }
+    }
+}
+#define TC2_PEER_MASK 0xFEFFFFFFu                          // clears the CTA-rank bit of a shared::cluster address
+
 template <int BN, int STAGES>
 struct TcSmem {
     static constexpr int A_BYTES = TC_BM * TC_BK * 2;
@@ -288,7 +314,6 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
     } else {
         // ---- epilogue: warps 2..5 own tensor-memory lanes 32 * (warp % 4) ..
         const int quarter = warp & 3;
-        const int o = tile_n * TC_BM + quarter * 32 + lane;         // output feature of this thread
         bool ok = !*abort_flag;
         pdl_wait();                                   // C may still be read by the preceding kernel
         if (ok && n_iters > 0) {
@@ -339,34 +364,48 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
                     }
                 }
             }
-        } else if (ok) {
+        } else {
+            // 16 tokens x 128 features at a time go through shared memory (the ring is idle once the
+            // accumulator is complete; two halves in turn, one barrier a round) and leave as whole rows.
+            // All four warps take the same decisions, so that the barrier below is always met.
+            if (!ok) *abort_flag = 1;
+            epilogue_sync();
+            ok = !*abort_flag;
             const uint32_t t_base = tmem_acc + ((uint32_t)(quarter * 32) << 16);
             const int t0 = tile_m * BN;
+            const int e = quarter * 32 + lane;                        // this thread's feature among the CTA's 128
+            const int o0 = tile_n * TC_BM;
+            const int cols = min(N - o0, TC_BM);
+            float* slab = gridDim.z > 1 ? partial + (long)blockIdx.z * M * ld_partial : nullptr;
+            const bool vec_ok = slab ? ((((uintptr_t)slab | (uintptr_t)(ld_partial * 4)) & 15) == 0)
+                                     : ((((uintptr_t)C | (uintptr_t)(ldc * (long)sizeof(OutT))) & 15) == 0);
+            if (ok) {
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
-                if (t0 + c >= M) break;                               // warp-uniform
-                uint32_t r[16];
-                if (n_iters > 0) {
-                    tmem_ld16(t_base + (uint32_t)c, r);
-                    tmem_ld_wait();
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) r[j] = 0u;
-                }
-                if (o < N) {
-                    if (gridDim.z == 1) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int t = t0 + c + j;
-                            if (t < M) C[(long)t * ldc + o] = from_f32<OutT>(__uint_as_float(r[j]));
-                        }
+                for (int c = 0; c < BN; c += 16) {
+                    if (t0 + c >= M) break;                           // uniform over the four warps
+                    uint32_t r[16];
+                    if (n_iters > 0) {
+                        tmem_ld16(t_base + (uint32_t)c, r);
+                        tmem_ld_wait();
                     } else {
-                        float* p = partial + (long)blockIdx.z * M * ld_partial;
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int t = t0 + c + j;
-                            if (t < M) p[(long)t * ld_partial + o] = __uint_as_float(r[j]);
-                        }
+                        for (int j = 0; j < 16; ++j) r[j] = 0u;
+                    }
+                    unsigned char* half = tiles + ((c >> 4) & 1) * (16 * TC_BM * 4);
+                    const int rows = min(16, M - (t0 + c));
+                    if (slab) {
+                        float* st = reinterpret_cast<float*>(half);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) st[j * TC_BM + e] = __uint_as_float(r[j]);
+                        epilogue_sync();
+                        tc_copy_rows<float, TC_BM, 16>(slab + (long)(t0 + c) * ld_partial + o0, ld_partial, st, rows,
+                                                       cols, e, vec_ok);
+                    } else {
+                        OutT* st = reinterpret_cast<OutT*>(half);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) st[j * TC_BM + e] = from_f32<OutT>(__uint_as_float(r[j]));
+                        epilogue_sync();
+                        tc_copy_rows<OutT, TC_BM, 16>(C + (long)(t0 + c) * ldc + o0, ldc, st, rows, cols, e, vec_ok);
                     }
                 }
             }
@@ -631,32 +670,6 @@ struct Tc2 {
 #define TC2_XCH_BYTES (2 * 32 * 64 * 4)                      // GATED: two rounds of 32 tokens x 64 up values
 #define TC2_GATED_OUT_BYTES (2 * 32 * 64 * 4)                // GATED: two rounds of 32 tokens x 64 results
 #define TC2_OUT_BYTES (2 * 32 * 128 * 4)                     // two rounds of 32 tokens x 128 features on their way out
-
-// Rows of 128 (or fewer) values from the epilogue's staging area to global memory, 16 bytes per
-// thread where the destination allows it: `e` is the thread's index among the 128 epilogue threads,
-// `cols` how many of the 128 columns exist.  Written this way a warp stores whole rows of 256 or 512
-// bytes; one value per lane and row (what the accumulator's layout gives) took 40 ns per token.
-template <typename T, int WIDTH>
-__device__ __forceinline__ void tc_copy_rows(T* __restrict__ dst, long ld, const T* __restrict__ src, int rows,
-                                             int cols, int e, bool vec_ok) {
-    constexpr int V = 16 / (int)sizeof(T);                  // values per 16 bytes
-    constexpr int TPR = WIDTH / V;                          // threads per row
-    constexpr int RPP = 128 / TPR;                          // rows per pass
-    const int rr = e / TPR, cc = (e % TPR) * V;
-#pragma unroll
-    for (int p = 0; p < 32 / RPP; ++p) {
-        const int row = p * RPP + rr;
-        if (row >= rows || cc >= cols) continue;
-        T* d = dst + (long)row * ld + cc;
-        const T* s_ = src + row * WIDTH + cc;
-        if (vec_ok && cc + V <= cols) {
-            *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(s_);
-        } else {
-            for (int v = 0; v < V && cc + v < cols; ++v) d[v] = s_[v];
-        }
-    }
-}
-#define TC2_PEER_MASK 0xFEFFFFFFu                          // clears the CTA-rank bit of a shared::cluster address
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
