@@ -184,7 +184,8 @@ struct TcSmem {
     static constexpr int B_BYTES = BN * TC_BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
-    static constexpr int BAR_BYTES = (2 * STAGES + 1) * 8 + 16;
+    static constexpr int MAX_STAGES = 12;                         // (the gated form makes its stages at run time)
+    static constexpr int BAR_BYTES = (2 * MAX_STAGES + 1) * 8 + 16;
     static constexpr int TOTAL = TILE_BYTES + BAR_BYTES + 1024;   // slack to align the tiles to 1024
 };
 
@@ -192,26 +193,36 @@ struct TcSmem {
 // splits == 1; with splits > 1 float partial sums go to `partial[z][M][ld_partial]`.
 //
 // GATED (the SwiGLU feed-forward's first product, no K split): W holds the gate rows and, `gate_rows`
-// further down, the up rows; a CTA's 128-row weight tile is 64 gate rows and the 64 up rows of the
-// same features (two TMA boxes of 64 rows: map_w has 64-row boxes then), N counts features, and the
-// epilogue writes silu(gate) * up: the product's 2 x N columns never go to memory.
+// further down, the up rows; a CTA serves `feat` features (a multiple of 8 up to 64): its weight tile
+// is `feat` gate rows and below them the `feat` up rows of the same features (two TMA boxes of `feat`
+// rows: map_w has such boxes then), N counts features, and the epilogue writes silu(gate) * up: the
+// product's 2 x N columns never go to memory.  The MMA still reads 128 rows: those past 2 x feat are
+// whatever lies behind the tile in shared memory and end in accumulator rows that nobody reads.  The
+// launcher picks `feat` so that all CTAs fit the SMs at once (two per SM); a stage is then smaller and
+// the ring has more of them, which is what keeps enough loads in flight: 172 CTAs of 64 features
+// streamed DeepSeek-7B's gate|up weights at 5.3 TB/s inside a decode step.
 template <int BN, int STAGES, typename OutT, bool GATED>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
     OutT* __restrict__ C, long ldc, float* __restrict__ partial, long ld_partial, int M, int N, int K,
-    int kb_per_split, int* __restrict__ status, int gate_rows) {
+    int kb_per_split, int* __restrict__ status, int gate_rows, int feat) {
     using L = TcSmem<BN, STAGES>;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full_bar = (uint64_t*)(tiles + L::TILE_BYTES);
-    uint64_t* empty_bar = full_bar + STAGES;
-    uint64_t* acc_bar = empty_bar + STAGES;
+    uint64_t* empty_bar = full_bar + L::MAX_STAGES;
+    uint64_t* acc_bar = empty_bar + L::MAX_STAGES;
     uint32_t* tmem_slot = (uint32_t*)(acc_bar + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    // a stage: the weight rows, then the token rows.  GATED: 2 x feat weight rows, and as many stages as
+    // leave the last one 128 rows of room for the MMA to read
+    const int w_bytes = GATED ? feat * 2 * TC_BK * 2 : L::A_BYTES;
+    const int stage_bytes = w_bytes + L::B_BYTES;
+    const int n_stages = GATED ? min(L::MAX_STAGES, (L::TILE_BYTES - L::A_BYTES - L::B_BYTES) / stage_bytes + 1) : STAGES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_n = blockIdx.x;            // which 128 output features (GATED: which 64)
+    const int tile_n = blockIdx.x;            // which 128 output features (GATED: which `feat`)
     const int tile_m = blockIdx.y;            // which BN tokens
     const int num_kb = (K + TC_BK - 1) / TC_BK;
     const int kb_begin = blockIdx.z * kb_per_split;
@@ -219,7 +230,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
     const int n_iters = kb_end - kb_begin;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < n_stages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
@@ -246,41 +257,37 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
             // The weights are written by no kernel, so the first ring of weight
             // tiles is fetched before waiting for the preceding kernel; the token
             // tiles (its output) follow after the wait.
-            const int ahead = *abort_flag ? 0 : min(n_iters, STAGES);
-            for (int it = 0; it < ahead; ++it) {
-                unsigned char* a_dst = tiles + it * L::STAGE_BYTES;
-                mbar_expect_tx(&full_bar[it], L::STAGE_BYTES);
+            const int ahead = *abort_flag ? 0 : min(n_iters, n_stages);
+            auto load_weights = [&](unsigned char* dst, uint64_t* bar, int k0) {
                 if (GATED) {
-                    tma_load_2d(a_dst, &map_w, &full_bar[it], (kb_begin + it) * TC_BK, tile_n * 64);
-                    tma_load_2d(a_dst + L::A_BYTES / 2, &map_w, &full_bar[it], (kb_begin + it) * TC_BK,
-                                gate_rows + tile_n * 64);
+                    tma_load_2d(dst, &map_w, bar, k0, tile_n * feat);
+                    tma_load_2d(dst + w_bytes / 2, &map_w, bar, k0, gate_rows + tile_n * feat);
                 } else {
-                    tma_load_2d(a_dst, &map_w, &full_bar[it], (kb_begin + it) * TC_BK, tile_n * TC_BM);
+                    tma_load_2d(dst, &map_w, bar, k0, tile_n * TC_BM);
                 }
+            };
+            for (int it = 0; it < ahead; ++it) {
+                mbar_expect_tx(&full_bar[it], stage_bytes);
+                load_weights(tiles + it * stage_bytes, &full_bar[it], (kb_begin + it) * TC_BK);
             }
             pdl_wait();
             for (int it = 0; it < ahead; ++it) {
-                unsigned char* b_dst = tiles + it * L::STAGE_BYTES + L::A_BYTES;
+                unsigned char* b_dst = tiles + it * stage_bytes + w_bytes;
                 tma_load_2d(b_dst, &map_a, &full_bar[it], (kb_begin + it) * TC_BK, tile_m * BN);
             }
+            int s = ahead % n_stages;
+            uint32_t ph = (uint32_t)(ahead / n_stages) & 1u;
             for (int it = ahead; it < n_iters && !*abort_flag; ++it) {
-                const int s = it % STAGES;
-                const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
                 if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
                     if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_EMPTY_WAIT); }
                     break;
                 }
-                unsigned char* a_dst = tiles + s * L::STAGE_BYTES;
-                unsigned char* b_dst = a_dst + L::A_BYTES;
-                mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+                unsigned char* a_dst = tiles + s * stage_bytes;
+                mbar_expect_tx(&full_bar[s], stage_bytes);
                 const int k0 = (kb_begin + it) * TC_BK;
-                if (GATED) {
-                    tma_load_2d(a_dst, &map_w, &full_bar[s], k0, tile_n * 64);
-                    tma_load_2d(a_dst + L::A_BYTES / 2, &map_w, &full_bar[s], k0, gate_rows + tile_n * 64);
-                } else {
-                    tma_load_2d(a_dst, &map_w, &full_bar[s], k0, tile_n * TC_BM);
-                }
-                tma_load_2d(b_dst, &map_a, &full_bar[s], k0, tile_m * BN);
+                load_weights(a_dst, &full_bar[s], k0);
+                tma_load_2d(a_dst + w_bytes, &map_a, &full_bar[s], k0, tile_m * BN);
+                if (++s == n_stages) { s = 0; ph ^= 1u; }
             }
         }
     } else if (warp == 1) {
@@ -288,17 +295,17 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
             // ---- MMA issuer
             constexpr uint32_t idesc = instr_desc_bf16(TC_BM, BN);
             bool ok = !*abort_flag;
+            int s = 0;
+            uint32_t ph = 0;
             for (int it = 0; it < n_iters && ok; ++it) {
-                const int s = it % STAGES;
-                const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
                 if (!mbar_wait(&full_bar[s], ph, abort_flag)) {
                     if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_FULL_WAIT); }
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(tiles + s * L::STAGE_BYTES);
-                const uint32_t b_addr = a_addr + L::A_BYTES;
+                const uint32_t a_addr = smem_u32(tiles + s * stage_bytes);
+                const uint32_t b_addr = a_addr + (uint32_t)w_bytes;
                 const uint64_t adesc = smem_desc_sw128(a_addr);
                 const uint64_t bdesc = smem_desc_sw128(b_addr);
 #pragma unroll
@@ -308,6 +315,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
                               (it > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(&empty_bar[s]);         // frees the stage once these MMAs have read it
+                if (++s == n_stages) { s = 0; ph ^= 1u; }
             }
             if (ok) umma_commit(acc_bar);           // accumulator complete
         }
@@ -322,19 +330,20 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
         }
         tc_fence_after();
         if (GATED) {
-            // Lanes 0..63 of the accumulator are gate features, 64..127 the same features' up
-            // values: the two sides trade values through shared memory (the ring is idle once the
-            // accumulator is complete), 16 tokens at a time.
+            // Rows 0 .. feat-1 of the accumulator are gate features, the next `feat` the same features'
+            // up values.  16 tokens at a time, every row's values (rounded to the activation type first,
+            // as the unfused route stores them) go to shared memory (the ring is idle once the accumulator
+            // is complete; two halves in turn, one barrier a round), and the threads share out the
+            // 16 x feat results, a token's features side by side.
             // All four warps take the same decisions, so that the barrier below is always met.
             if (!ok) *abort_flag = 1;
             epilogue_sync();
             ok = !*abort_flag;
-            const bool is_up = quarter >= 2;
-            const int col = (quarter & 1) * 32 + lane;               // feature within the CTA's 64
-            const int f = tile_n * 64 + col;
+            const int row = quarter * 32 + lane;
+            const int f0 = tile_n * feat;
             const uint32_t t_base = tmem_acc + ((uint32_t)(quarter * 32) << 16);
             const int t0 = tile_m * BN;
-            float* xch = reinterpret_cast<float*>(tiles);            // [2][16 tokens][64 features]
+            float* xch = reinterpret_cast<float*>(tiles);            // [2][16 tokens][128 rows]
             if (ok) {
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
@@ -342,25 +351,19 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
                     uint32_t r[16];
                     tmem_ld16(t_base + (uint32_t)c, r);
                     tmem_ld_wait();
-                    // the gate warps finish the even tokens, the up warps the odd ones: each side hands
-                    // over the values the other needs (both factors rounded to the activation type
-                    // first, as the unfused route stores them)
-                    float* x = xch + ((c >> 4) & 1) * (16 * 64);
-                    const int mine = is_up ? 1 : 0;                    // parity of the tokens this warp finishes
+                    float* x = xch + ((c >> 4) & 1) * (16 * TC_BM);
+                    if (row < 2 * feat) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if ((j & 1) != mine)
-                            x[j * 64 + col] = to_f32<OutT>(from_f32<OutT>(__uint_as_float(r[j])));
+                        for (int j = 0; j < 16; ++j)
+                            x[j * TC_BM + row] = to_f32<OutT>(from_f32<OutT>(__uint_as_float(r[j])));
+                    }
                     epilogue_sync();
-                    if (f < N) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            if ((j & 1) != mine) continue;
-                            const int t = t0 + c + j;
-                            const float own = to_f32<OutT>(from_f32<OutT>(__uint_as_float(r[j])));
-                            const float other = x[j * 64 + col];
-                            if (t < M) C[(long)t * ldc + f] = from_f32<OutT>(is_up ? gated_act(other, own) : gated_act(own, other));
-                        }
+                    const int rows = min(16, M - (t0 + c));
+                    for (int i = row; i < rows * feat; i += 128) {
+                        const int t = i / feat, f = i - t * feat;
+                        if (f0 + f < N)
+                            C[(long)(t0 + c + t) * ldc + f0 + f] =
+                                from_f32<OutT>(gated_act(x[t * TC_BM + f], x[t * TC_BM + feat + f]));
                     }
                 }
             }
@@ -1062,7 +1065,7 @@ static int make_map(CUtensorMap* map, const void* base, long rows, long cols, lo
 template <int BN, int STAGES, typename OutT, bool GATED = false>
 static int launch_tc(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C, long ldc,
                      float* partial, long ld_partial, int M, int N, int K, int splits,
-                     int kb_per_split, int* status, cudaStream_t stream, int gate_rows = 0) {
+                     int kb_per_split, int* status, cudaStream_t stream, int gate_rows = 0, int feat = 64) {
     using L = TcSmem<BN, STAGES>;
     static bool configured = false;
     auto kernel = gemm_tc_kernel<BN, STAGES, OutT, GATED>;
@@ -1071,9 +1074,9 @@ static int launch_tc(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(GATED ? (N + 63) / 64 : (N + TC_BM - 1) / TC_BM, (M + BN - 1) / BN, splits);
+    dim3 grid(GATED ? (N + feat - 1) / feat : (N + TC_BM - 1) / TC_BM, (M + BN - 1) / BN, splits);
     return fl_launch(kernel, grid, dim3(TC_THREADS), (size_t)L::TOTAL, stream, map_w, map_a, (OutT*)C, ldc,
-                     partial, ld_partial, M, N, K, kb_per_split, status, gate_rows);
+                     partial, ld_partial, M, N, K, kb_per_split, status, gate_rows, feat);
 }
 
 template <typename OutT>
@@ -1237,17 +1240,26 @@ FL_API int fl_gemm_tc_swiglu(const void* A, long lda, const void* W, long ldw, v
     if (splits != 1 || bn == 256) return -1;
     if ((M + (bn > 256 ? 256 : bn) - 1) / (bn > 256 ? 256 : bn) > 65535) return (int)cudaErrorInvalidValue;
     CUtensorMap map_w, map_a;
-    int rc = make_map(&map_w, W, 2L * I, K, ldw, 64);               // boxes of 64 weight rows
+    // features per CTA of the one-tile kernel: as few as still leave all CTAs a place on the SMs at
+    // once (two per SM), in steps of 8 up to 64
+    int feat = 64;
+    if (bn <= 128) {
+        const long token_tiles = (M + bn - 1) / bn;
+        const long places = 2L * num_sms;
+        feat = 8;
+        while (feat < 64 && (long)((I + feat - 1) / feat) * token_tiles > places) feat += 8;
+    }
+    int rc = make_map(&map_w, W, 2L * I, K, ldw, feat);             // boxes of `feat` weight rows
     if (rc) return rc;
     rc = make_map(&map_a, A, M, K, lda, bn > 256 ? TC_BM : bn);
     if (rc) return rc;
     if (bn == 512) return launch_tc_pair<256, bf16, true>(map_w, map_a, C, ldc, M, I, K, num_sms, status, stream, I);
     const int kb = (K + TC_BK - 1) / TC_BK;
     switch (bn) {
-        case 16: return launch_tc<16, 6, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I);
-        case 32: return launch_tc<32, 5, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I);
-        case 64: return launch_tc<64, 4, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I);
-        case 128: return launch_tc<128, 3, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I);
+        case 16: return launch_tc<16, 6, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I, feat);
+        case 32: return launch_tc<32, 5, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I, feat);
+        case 64: return launch_tc<64, 4, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I, feat);
+        case 128: return launch_tc<128, 3, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I, feat);
     }
     return -1;
 }
