@@ -485,11 +485,12 @@ def test_embedding_kernel_reports_bad_ids():
 
 
 @pytest.mark.parametrize("m", [1, 7, 16, 50, 100, 129, 300, 513])
-@pytest.mark.parametrize("inter, k", [(11048, 320), (9728, 72)])
+@pytest.mark.parametrize("inter, k", [(11048, 320), (9728, 72), (13004, 136), (16648, 72)])
 def test_gate_up_product_with_swiglu_epilogue(m, inter, k):
     """silu(a gate^T) * (a up^T) written by the product's epilogue (one-tile kernel for few
-    tokens, CTA pairs for many), against the product and the activation done apart; an
-    intermediate size that is no multiple of the 64-feature tiles; nothing written outside."""
+    tokens, with 40, 48 or 64 features per CTA depending on the intermediate size; CTA pairs for
+    many), against the product and the activation done apart; intermediate sizes that are no
+    multiple of the tiles; nothing written outside."""
     from fastllm_py_b200.native import gemm_tc
 
     g = torch.Generator(device="cpu").manual_seed(m + inter + k)
