@@ -149,6 +149,46 @@ def test_long_decoding(model_folders):
     _plain_cache.pop((name, False), None)
 
 
+def test_decoding_together_across_changes_of_the_split(model_folders):
+    """Three requests of different lengths decoded side by side for 450 steps with graph replay on:
+    their lengths pass 256 and 512, where the decode kernel's keys per split (and with them the
+    captured step) change, and one request ends on the way, which changes the batch."""
+    from fastllm_py_b200 import Model
+    from fastllm_py_b200.native.attention import decode_split_keys
+
+    name = "tiny_c"
+    cfg = tiny.CONFIGS[name]["config"]
+    kv, hd = cfg.num_kv_heads, cfg.head_dim
+    assert len({decode_split_keys(3, kv, n, 148, hd) for n in (200, 300, 600)}) > 1, "the choice never changes here"
+    rng = np.random.default_rng(77)
+    lengths = {"x": 640, "y": 520, "z": 470}
+    requests = {r: rng.integers(0, cfg.vocab_size, size=n).tolist() for r, n in lengths.items()}
+    weights, config = plain.load_folder(model_folders[name])
+    ref = {r: plain.forward(weights, config, t, store=plain.store_bf16) for r, t in requests.items()}
+    exact = {r: plain.forward(weights, config, t) for r, t in requests.items()}
+    tol = 2.0 * max(float((ref[r] - exact[r]).abs().max()) for r in ref) + 1e-3
+    model = Model.load(model_folders[name], dtype="bfloat16", page_size=tiny.CONFIGS[name]["page_size"],
+                       max_tokens=2048, max_requests=4, max_batched_tokens=512, max_model_len=704,
+                       cuda_graph=True)
+    tail = 450
+    steps = []
+    for r, toks in requests.items():                        # the heads, one request a step
+        steps.append({"step": len(steps), "end": [], "entries": [{"id": r, "tokens": toks[:len(toks) - tail], "want": []}]})
+    for k in range(tail):                                   # then one token of each, together
+        entries, end = [], []
+        for r, toks in requests.items():
+            at = len(toks) - tail + k
+            if r == "z" and k >= 200:                       # z stops early
+                continue
+            entries.append({"id": r, "tokens": [toks[at]], "want": [0]})
+            if k == tail - 1 or (r == "z" and k == 199):
+                end.append(r)
+        steps.append({"step": len(steps), "end": end, "entries": entries})
+    got = replay.run_in_process(model.engine, steps)
+    assert len(model.engine._graphs) >= 3
+    compare(got, ref, tol, "decoding together across split changes")
+
+
 def test_weights_stored_in_32_bit_stay_so(tmp_path):
     """A checkpoint stored in float32 run with bfloat16 activations: the matrices stay 32-bit
     (the CUDA-core product takes them), and the logits match the plain model."""
