@@ -241,6 +241,159 @@ def time_prefill(model, tokens, repeats, warmup):
     return statistics.median(times)
 
 
+MODEL_1B3 = dict(num_layers=24, hidden_size=2048, num_heads=16, num_kv_heads=16, head_dim=128,
+                 intermediate_size=5504, vocab_size=32256, rope_theta=100000.0, rms_norm_eps=1e-6,
+                 max_position_embeddings=16384)
+MODEL_67B = dict(num_layers=95, hidden_size=8192, num_heads=64, num_kv_heads=8, head_dim=128,
+                 intermediate_size=22016, vocab_size=102400, rope_theta=10000.0, rms_norm_eps=1e-6,
+                 max_position_embeddings=4096)
+
+
+def percentiles(values):
+    if not values:
+        return None
+    v = sorted(values)
+    pick = lambda q: round(v[min(len(v) - 1, int(q * len(v)))], 2)
+    return {"p50": pick(0.50), "p90": pick(0.90), "p99": pick(0.99)}
+
+
+def serving_workload(seed, n_requests, rate_per_s, vocab):
+    """[(arrival second, prompt ids, tokens to produce)]: prompt lengths uniform in [64, 8192], outputs
+    uniform in [32, 512], Poisson arrivals, all from one seed."""
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    at, out = 0.0, []
+    for _ in range(n_requests):
+        at += float(rng.exponential(1.0 / rate_per_s))
+        prompt = rng.integers(0, vocab, size=int(rng.integers(64, 8193))).tolist()
+        out.append((at, prompt, int(rng.integers(32, 513))))
+    return out
+
+
+def run_serving(args):
+    """Continuous batching of 128 requests at deepseek-coder-1.3b size through the scheduler: total
+    tokens a second, time to the first token and between tokens, and how often a request was pushed
+    out for want of pages (the pool holds a quarter of what all requests together would need)."""
+    import torch
+
+    from fastllm_py_b200 import LlamaConfig, Model
+    from fastllm_py_b200.config.llama import LinearRopeScaling
+
+    cfg = LlamaConfig(architecture="LlamaForCausalLM", rope_scaling=LinearRopeScaling(4.0),
+                      tie_word_embeddings=False, **dict(MODEL_1B3, num_layers=args.layers or MODEL_1B3["num_layers"]))
+    budget, pool, live = 2048, 256 * 1024, 64
+    model = Model.from_config(cfg, seed=0, dtype="bfloat16", page_size=16, max_tokens=pool, max_requests=live,
+                              max_batched_tokens=budget, max_model_len=16384, cuda_graph=not args.no_graph)
+    work = serving_workload(11, args.requests, args.rate, cfg.vocab_size)
+    # warm-up: the same kinds of steps (portions, mixed, decode) on a few short requests, untimed
+    warm = model.scheduler(token_budget=budget)
+    for i in range(4):
+        warm.add_request(work[i][1][:600 + 50 * i], max_new_tokens=24)
+    warm.run()
+    torch.cuda.synchronize()
+
+    sched = model.scheduler(token_budget=budget)
+    arrival, first, last, gaps, done_at = {}, {}, {}, [], {}
+    nxt, produced = 0, 0
+    sampler = ClockSampler()
+    sampler.__enter__()
+    t0 = time.perf_counter()
+    while nxt < len(work) or sched.has_work():
+        now = time.perf_counter() - t0
+        while nxt < len(work) and work[nxt][0] <= now:
+            rid = sched.add_request(work[nxt][1], max_new_tokens=work[nxt][2], arrival_time=work[nxt][0])
+            arrival[rid] = work[nxt][0]
+            nxt += 1
+        if not sched.has_work():
+            time.sleep(max(0.0, min(0.002, work[nxt][0] - now)))
+            continue
+        outs = sched.step()
+        now = time.perf_counter() - t0
+        for o in outs:
+            produced += 1
+            if o.request_id not in first:
+                first[o.request_id] = now
+            else:
+                gaps.append((now - last[o.request_id]) * 1e3)
+            last[o.request_id] = now
+            if o.finished:
+                done_at[o.request_id] = now
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - t0
+    sampler.__exit__()
+    model.engine.check_status()
+    model.engine.cache.check()
+    prompt_tokens = sum(len(w[1]) for w in work)
+    line = {
+        "metric": "continuous batching tok/s, deepseek-coder-1.3b size bf16, 128 requests, Poisson arrivals",
+        "value": round(produced / elapsed, 1), "unit": "generated tokens/s", "n_gpus": 1,
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "prompt_tokens_per_s": round(prompt_tokens / elapsed, 1), "seconds": round(elapsed, 2),
+        "ttft_ms": percentiles([(first[r] - arrival[r]) * 1e3 for r in first]),
+        "per_token_ms": percentiles(gaps),
+        "latency_s": percentiles([done_at[r] - arrival[r] for r in done_at]),
+        "pushed_out": sched.stats["pushed_out"], "steps": sched.stats["steps"],
+        "steps_ahead": sched.stats["steps_ahead"], "finished": len(done_at),
+        "config": {"model": "deepseek-coder-1.3b size, random weights", "layers": cfg.num_layers,
+                   "requests": len(work), "arrivals_per_s": args.rate, "prompt_tokens": prompt_tokens,
+                   "generated_tokens": produced, "token_budget": budget, "pool_tokens": pool,
+                   "live_requests_most": live, "page_size": 16, "context_limit": 16384,
+                   "cuda_graph": not args.no_graph},
+        "clocks": sampler.summary(),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def run_67b(args, warmup):
+    """deepseek-llm-67b size on one GPU (135 GB of bfloat16 weights): a 2048-token prompt step and
+    decode steps at batch 1, 8 and 16 with 4096-token contexts, device-timed, with their fractions of
+    the tensor peak and of the HBM roofline."""
+    import torch
+
+    from fastllm_py_b200 import LlamaConfig, Model
+
+    layers = args.layers or MODEL_67B["num_layers"]
+    cfg = LlamaConfig(architecture="LlamaForCausalLM", rope_scaling=None, tie_word_embeddings=False,
+                      **dict(MODEL_67B, num_layers=layers))
+    pk = peaks()
+    context, steps = 4000, max(8, min(args.steps, 32))      # (the model's limit is 4096 positions)
+    pool = 16 * (context + warmup + steps + 64)
+    t_load = time.time()
+    model = Model.from_config(cfg, seed=0, dtype="bfloat16", page_size=16, max_tokens=pool, max_requests=16,
+                              max_batched_tokens=PREFILL_TOKENS, max_model_len=4096, cuda_graph=not args.no_graph)
+    torch.cuda.synchronize()
+    load_s = time.time() - t_load
+    points = {}
+    clocks = None
+    for b in (8, 1, 16):
+        v, ms, _, ck = time_decode(model, b, steps, warmup, context, sample_clocks=(b == 8))
+        clocks = ck or clocks
+        nbytes = decode_bytes(cfg, b, context + warmup + (steps + 1) / 2)
+        points[f"decode_b{b}"] = {"value": round(v, 2), "ms_per_step": round(ms, 3),
+                                  "frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+    pms = time_prefill(model, PREFILL_TOKENS, 3, 2)
+    flops = prefill_flops(cfg, PREFILL_TOKENS)
+    line = {
+        "metric": "decode tok/s @ batch 8, 4000-token context, deepseek-llm-67b size bf16",
+        "value": points["decode_b8"]["value"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": points["decode_b8"]["ms_per_step"], "higher_is_better": True, "dtype": "bf16",
+        "data": "synthetic", "impl": "ours",
+        "config": {"model": "deepseek-llm-67b size, random weights", "layers": layers,
+                   "layers_of_config": MODEL_67B["num_layers"], "hidden": cfg.hidden_size, "heads": cfg.num_heads,
+                   "kv_heads": cfg.num_kv_heads, "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size,
+                   "vocab": cfg.vocab_size, "seq_len": context, "page_size": 16, "prefill_tokens": PREFILL_TOKENS,
+                   "cuda_graph": not args.no_graph, "peaks": pk["source"], "load_s": round(load_s, 1)},
+        "points": points,
+        "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / pms, 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
+                    "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -248,10 +401,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=MODEL_7B["num_layers"],
+    ap.add_argument("--layers", type=int, default=None,
                     help="run fewer layers of the same sizes (the line names both numbers)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "67b"],
+                    help="decode: the headline line (DeepSeek-LLM-7B size); serve: continuous batching at "
+                         "deepseek-coder-1.3b size; 67b: prompt and decode steps at deepseek-llm-67b size")
+    ap.add_argument("--requests", type=int, default=128, help="serve: how many requests")
+    ap.add_argument("--rate", type=float, default=16.0, help="serve: mean arrivals a second")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -263,6 +421,11 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     warmup = max(3, args.warmup)
+    if args.workload == "serve":
+        return run_serving(args)
+    if args.workload == "67b":
+        return run_67b(args, warmup)
+    args.layers = args.layers or MODEL_7B["num_layers"]
 
     import torch
 

@@ -35,8 +35,20 @@ def _ptr(t):
     return None if t is None else c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_device_index = None
+
+
 def _stream():
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current CUDA stream's handle for a launch.  `torch.cuda.current_stream()` asks the
+    driver how many devices there are on every call (20 us): a step launched kernel by kernel
+    spent more time there than on its kernels, so the raw handle is asked for instead."""
+    global _device_index
+    if _raw_stream is None:
+        return c_void_p(torch.cuda.current_stream().cuda_stream)
+    if _device_index is None:
+        _device_index = torch.cuda.current_device()
+    return c_void_p(_raw_stream(_device_index))
 
 
 def _ld(t: torch.Tensor) -> int:

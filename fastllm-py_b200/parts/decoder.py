@@ -98,7 +98,10 @@ class Decoder:
     def graph_safe(self) -> bool:
         """False when some part says that its forward decides things on the host from the
         step's host copies (attribute `graph_safe = False`): its steps are never captured."""
-        return all(getattr(p, "graph_safe", True) for p in self.all_parts())
+        safe = getattr(self, "_graph_safe", None)
+        if safe is None:                                    # (the parts are fixed once the decoder is built)
+            safe = self._graph_safe = all(getattr(p, "graph_safe", True) for p in self.all_parts())
+        return safe
 
     def graph_key(self, step):
         """What, beside the number of tokens, fixes the launch shapes of a

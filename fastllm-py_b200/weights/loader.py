@@ -9,6 +9,8 @@ that table before anything is read, and every mismatch is listed at once.
 from __future__ import annotations
 
 import json
+import weakref
+from collections.abc import Mapping
 from pathlib import Path
 
 import torch
@@ -58,10 +60,39 @@ def check_store(expected: dict, store, where="", ignorable=()) -> None:
         raise WeightError(missing, unexpected, wrong_shape, wrong_dtype, where)
 
 
-def load_tensors(expected: dict, store, device, where="", ignorable=()) -> dict:
-    """name -> device tensor for every expected name, after the check."""
+class _TensorsOnDemand(Mapping):
+    """name -> device tensor, fetched from the store when asked for and held only as long as
+    somebody else holds it: a part that stacks its matrices into one frees the originals on the
+    spot, so loading never needs much more memory than the model itself (a 135 GB model fits a
+    180 GB device), and two parts that ask for one tensor (tied embeddings) get the same one."""
+
+    def __init__(self, names, store, device):
+        self._names = list(names)
+        self._store = store
+        self._device = device
+        self._alive = weakref.WeakValueDictionary()
+
+    def __getitem__(self, name):
+        if name not in self._names:
+            raise KeyError(name)
+        t = self._alive.get(name)
+        if t is None:
+            t = self._store.get(name, self._device)
+            self._alive[name] = t
+        return t
+
+    def __iter__(self):
+        return iter(self._names)
+
+    def __len__(self):
+        return len(self._names)
+
+
+def load_tensors(expected: dict, store, device, where="", ignorable=()) -> Mapping:
+    """name -> device tensor for every expected name, after the check; tensors are read when
+    they are asked for."""
     check_store(expected, store, where, ignorable)
-    return {name: store.get(name, device) for name in expected}
+    return _TensorsOnDemand(expected, store, device)
 
 
 def write_model_folder(config, folder, seed: int, std: float = 0.02, norm_std: float = 0.02,
