@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
+                    [--workload decode|serve|67b]
 
 The default run is the DeepSeek-LLM-7B sized model (30 layers, hidden 4096,
 32 heads, head size 128, feed-forward 11008, vocabulary 102400) with random
@@ -25,6 +26,18 @@ prints ONE line of JSON:
 Weights (13.8 GB) and cache are far larger than the 126 MB L2, so no flush is
 needed between steps.  Peaks come from MEASURED_PEAKS.json when the driver
 wrote it, else from the fallback figures 6650 GB/s and 1590 TFLOP/s.
+
+Two more workloads, each printing one line of its own:
+
+  --workload serve   deepseek-coder-1.3b size (24 layers, hidden 2048, context 16384, linear
+             rotary scaling 4): 128 requests with prompts of 64 to 8192 tokens and 32 to 512
+             tokens to produce, Poisson arrivals (--rate a second), through the scheduler with a
+             token budget of 2048 and a cache pool that holds a quarter of what all requests
+             together would need; generated and prompt tokens a second, time to the first
+             token, time between tokens, how often a request was pushed out;
+  --workload 67b     deepseek-llm-67b size (95 layers, hidden 8192, 64 heads over 8 key/value
+             heads; 135 GB of weights on the one GPU): a 2048-token prompt step and decode
+             steps at batch 1, 8 and 16 with 4000-token contexts, with their roofline fractions.
 
 fastllm-py's counterpart is scripts/bench_one.py:27-100 (128-token prefill, 64
 decode steps, wall-clock per token); its lesson kept here is to time steady

@@ -1,0 +1,50 @@
+"""Host-side pieces behind the benchmark's workloads and the weight loader (no GPU)."""
+import gc
+import sys
+from pathlib import Path
+
+import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+
+def test_serving_workload_is_seeded_and_in_range():
+    import bench
+
+    a = bench.serving_workload(11, 40, 16.0, 1000)
+    b = bench.serving_workload(11, 40, 16.0, 1000)
+    assert a == b and a != bench.serving_workload(12, 40, 16.0, 1000)
+    times = [w[0] for w in a]
+    assert times == sorted(times) and times[0] > 0
+    assert all(64 <= len(w[1]) <= 8192 and 32 <= w[2] <= 512 for w in a)
+    assert all(0 <= t < 1000 for w in a for t in w[1][:50])
+    p = bench.percentiles([float(i) for i in range(100)])
+    assert p == {"p50": 50.0, "p90": 90.0, "p99": 99.0} and bench.percentiles([]) is None
+
+
+def test_tensors_are_fetched_on_demand_and_not_kept():
+    """The loader hands out a tensor when it is asked for, the same one to two askers while one of
+    them holds it, and holds none itself: stacking matrices never doubles the model."""
+    from fastllm_py_b200.weights import RandomStore, load_tensors
+
+    shapes = {"a.weight": (8, 4), "b.weight": (8, 4), "n.weight": (4,)}
+    store = RandomStore(shapes, 3, 0.02, 0.02, torch.bfloat16, on_device=False)
+    fetched = []
+    real_get = store.get
+    store.get = lambda name, device: (fetched.append(name), real_get(name, device))[1]
+    tensors = load_tensors(shapes, store, "cpu")
+    assert fetched == [] and set(tensors) == set(shapes) and len(tensors) == 3
+    first = tensors["a.weight"]
+    assert tensors["a.weight"] is first and fetched == ["a.weight"]          # shared while somebody holds it
+    stacked = torch.cat([first, tensors["b.weight"]])
+    del first
+    gc.collect()
+    again = tensors["a.weight"]
+    assert fetched == ["a.weight", "b.weight", "a.weight"]                    # fetched anew, equal content
+    assert torch.equal(again, stacked[:8])
+    try:
+        tensors["c.weight"]
+    except KeyError:
+        pass
+    else:
+        raise AssertionError("a name that is not expected must not be served")
