@@ -1229,26 +1229,29 @@ FL_API int fl_gemm_tc_partial(const void* A, long lda, const void* W, long ldw, 
 
 // The SwiGLU feed-forward's first product with its activation: W holds the gate matrix [I, K] and
 // below it the up matrix [I, K]; C[M, I] = silu(A gate^T) * (A up^T), bfloat16.  Returns 0 when the
-// fused kernel was launched, -1 when this problem is not taken (the plan for the [2 I, K] product
-// splits K, or has no fused kernel): the caller then runs the product and the activation apart.
+// fused kernel was launched, -1 when this problem is not taken (too few features to fill the GPU
+// without a K split, or many tokens and a plan that splits K): the caller then runs the product
+// and the activation apart.
 FL_API int fl_gemm_tc_swiglu(const void* A, long lda, const void* W, long ldw, void* C, long ldc, int M, int I,
                              int K, int num_sms, int* status, cudaStream_t stream) {
     if (M <= 0 || I <= 0) return 0;
     if (K <= 0) return (int)cudaErrorInvalidValue;
-    int bn = 0, splits = 0;
-    plan_one_tile(M, 2 * I, K, num_sms, &bn, &splits);          // (the pair kernel's narrower tiles have no gated form)
-    if (splits != 1 || bn == 256) return -1;
-    if ((M + (bn > 256 ? 256 : bn) - 1) / (bn > 256 ? 256 : bn) > 65535) return (int)cudaErrorInvalidValue;
-    CUtensorMap map_w, map_a;
-    // features per CTA of the one-tile kernel: as few as still leave all CTAs a place on the SMs at
-    // once (two per SM), in steps of 8 up to 64
-    int feat = 64;
-    if (bn <= 128) {
-        const long token_tiles = (M + bn - 1) / bn;
-        const long places = 2L * num_sms;
-        feat = 8;
-        while (feat < 64 && (long)((I + feat - 1) / feat) * token_tiles > places) feat += 8;
+    // Up to 128 tokens: the one-tile kernel with as few features per CTA (16 to 64 in steps of 8) as
+    // still leave every CTA a place on the SMs at once (two per SM); declined when even that gives too
+    // few CTAs to keep the memory busy (a split of K does that better, with the activation apart).
+    // Above: the CTA-pair kernel when the plan for the [2 I, K] product has no K split.
+    int bn = 16, feat = 64;
+    if (M <= 128) {
+        while (bn < M) bn *= 2;
+        feat = 16;
+        while (feat < 64 && (I + feat - 1) / feat > 2 * num_sms) feat += 8;
+        if ((I + feat - 1) / feat < (num_sms + 1) / 2) return -1;
+    } else {
+        int splits = 0;
+        plan_one_tile(M, 2 * I, K, num_sms, &bn, &splits);      // (the pair kernel's narrower tiles have no gated form)
+        if (splits != 1 || bn != 512) return -1;
     }
+    CUtensorMap map_w, map_a;
     int rc = make_map(&map_w, W, 2L * I, K, ldw, feat);             // boxes of `feat` weight rows
     if (rc) return rc;
     rc = make_map(&map_a, A, M, K, lda, bn > 256 ? TC_BM : bn);

@@ -485,10 +485,10 @@ def test_embedding_kernel_reports_bad_ids():
 
 
 @pytest.mark.parametrize("m", [1, 7, 16, 50, 100, 129, 300, 513])
-@pytest.mark.parametrize("inter, k", [(11048, 320), (9728, 72), (13004, 136), (16648, 72)])
+@pytest.mark.parametrize("inter, k", [(11048, 320), (9728, 72), (13004, 136), (16648, 72), (5512, 264), (1380, 520)])
 def test_gate_up_product_with_swiglu_epilogue(m, inter, k):
     """silu(a gate^T) * (a up^T) written by the product's epilogue (one-tile kernel for few
-    tokens, with 40, 48 or 64 features per CTA depending on the intermediate size; CTA pairs for
+    tokens, with 16 to 64 features per CTA depending on the intermediate size; CTA pairs for
     many), against the product and the activation done apart; intermediate sizes that are no
     multiple of the tiles; nothing written outside."""
     from fastllm_py_b200.native import gemm_tc
@@ -500,7 +500,11 @@ def test_gate_up_product_with_swiglu_epilogue(m, inter, k):
     ref = gu[:, :inter] / (1.0 + torch.exp(-gu[:, :inter])) * gu[:, inter:]
     out = torch.full((m, inter + 5), -5.0, dtype=torch.bfloat16, device=DEV)
     done = gemm_tc.gemm_swiglu(a.to(DEV), w.to(DEV), out[:, :inter])
-    assert done, "this size should be taken by the fused kernel"
+    if not done:                                                # many tokens, few features: the plan splits K
+        assert m > 128 and inter < 9000, "this size should be taken by the fused kernel"
+        torch.cuda.synchronize()
+        assert torch.all(out == -5.0)
+        return
     torch.cuda.synchronize()
     assert int(gemm_tc.status_word(torch.device(DEV)).item()) == 0
     assert torch.all(out[:, inter:] == -5.0), "wrote outside the output columns"
