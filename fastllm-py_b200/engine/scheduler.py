@@ -8,8 +8,10 @@ request per step, a request finished by a stop token (which is emitted) or by
   * a token budget per step; prompts are cut into portions under it and may
     span several steps, beside the decoded tokens of other requests (the
     reference prefills every prompt whole and alone, batched.py:372);
-  * admission needs a free request slot, budget left, and pages for the first
-    portion;
+  * admission needs a free request slot, budget left, and free pages for the
+    request's whole prompt and first token plus a page of growth for every
+    request already running (with nothing running: just the pages of the
+    first portion, the pool being all free);
   * bounds: a request whose prompt plus `max_new_tokens` exceeds the longest
     sequence, or the whole page pool, is refused when it is added.
 
@@ -180,6 +182,14 @@ class Scheduler:
             req = self.waiting[0]
             n = min(req.remaining, budget)
             pages = -(-n // self.cache.page_size)
+            # Room for its whole prompt and its first token, and a page of growth for every request
+            # already running: a request that is let in on the strength of its first portion alone is
+            # the one pushed out again a few steps later, its portions computed for nothing.  With
+            # nothing running the whole pool is free, and add_request has made sure that it fits.
+            whole = -(-(req.remaining + 1) // self.cache.page_size)
+            reserve = len(self.running)
+            if self.running and any(g.pool.free_pages < whole + taken + reserve for g in self.cache.groups):
+                break
             if any(g.pool.free_pages < pages + taken for g in self.cache.groups):
                 break
             self.waiting.popleft()

@@ -241,6 +241,28 @@ def test_admission_waits_for_slots_and_pages():
     assert eng.cache.groups[0].pool.free_pages == 6
 
 
+def test_admission_wants_room_for_the_whole_prompt():
+    """A long prompt is let in when the free pages hold all of it, its first token and a page of
+    growth for each running request, not on the strength of its first portion alone (it would be
+    the next one pushed out, its portions computed for nothing); with nothing running it is let
+    in whatever the budget cuts it into."""
+    eng = StandInEngine(pages=10, page_size=4, max_requests=4, max_model_len=64, max_tokens=8)
+    s = Scheduler(eng, ArgmaxSampler(), token_budget=8)
+    a = s.add_request([1] * 10, max_new_tokens=9)            # 3 pages now, up to 5
+    s.step()
+    s.step()                                                 # a's prompt is in: it decodes
+    b = s.add_request([2] * 29, max_new_tokens=2)            # 8 pages for prompt + first token
+    s.step()
+    assert [r.request_id for r in s.running] == [a], "7 free pages hold b's first portion, not b"
+    out = s.run()
+    assert len(out[a]) == 9 and len(out[b]) == 2 and s.stats["pushed_out"] == 0
+    assert eng.cache.groups[0].pool.free_pages == 10
+    lone = Scheduler(StandInEngine(pages=8, page_size=4, max_tokens=8), ArgmaxSampler(), token_budget=8)
+    c = lone.add_request([3] * 29, max_new_tokens=2)
+    lone.step()
+    assert [r.request_id for r in lone.running] == [c]
+
+
 def test_pages_run_out_last_admitted_is_pushed_out_and_recomputed():
     # 6 pages of 4 tokens; two requests of 7 prompt tokens (2 pages each) that decode
     # 8 more (up to 15 tokens = 4 pages each): together they need 8 pages, so one must go.

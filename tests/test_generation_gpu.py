@@ -93,14 +93,15 @@ def test_stop_token_is_emitted_and_ends(model_folders):
 
 
 def test_page_pressure_changes_no_output(model_folders):
-    """A pool so small that running requests are pushed out and recomputed."""
+    """A pool so small (seven pages) that requests which were let in with room for their prompts
+    outgrow it while they decode: the one admitted last is pushed out and recomputed."""
     name = "tiny_a"
     roomy = model_for(name, model_folders[name], "float32")
     tight = model_for(name, model_folders[name], "float32", max_tokens=112, max_requests=4)
     prompts = prompts_of(name, [30, 28, 33, 25], seed=8)
-    want = [roomy.generate(p, max_new_tokens=20) for p in prompts]
+    want = [roomy.generate(p, max_new_tokens=40) for p in prompts]
     sched = tight.scheduler()
-    ids = [sched.add_request(p, 20) for p in prompts]
+    ids = [sched.add_request(p, 40) for p in prompts]
     out = sched.run()
     assert sched.stats["pushed_out"] >= 1
     assert [out[i] for i in ids] == want
