@@ -48,3 +48,27 @@ def test_tensors_are_fetched_on_demand_and_not_kept():
         pass
     else:
         raise AssertionError("a name that is not expected must not be served")
+
+
+def test_product_plans_without_a_gpu():
+    """The host-side choice of kernel, token tile and K splits for a product needs no GPU (the library
+    is compiled, not run): every answer is a kernel the launcher has, with no empty split; up to 64
+    tokens the one-tile kernel, above it CTA pairs; small products get their K split, large ones not."""
+    import shutil
+
+    import pytest
+
+    if shutil.which("nvcc") is None:
+        pytest.skip("no CUDA compiler here")
+    from fastllm_py_b200.native import gemm_tc
+
+    for m in (1, 7, 64, 65, 128, 129, 300, 1000, 5000):
+        for n, k in ((64, 64), (300, 1000), (4096, 4096), (12288, 4096), (4096, 11008), (102400, 4096)):
+            bn, splits = gemm_tc.plan(m, n, k, 148)
+            assert bn in (16, 32, 64, 128, 256, 512, 576, 640)
+            kb = -(-k // 64)
+            per = -(-kb // splits)
+            assert 1 <= splits <= 16 and (splits - 1) * per < kb
+            assert (bn >= 512) == (m > 64)
+    assert gemm_tc.plan(256, 4096, 4096, 148)[1] > 1 and gemm_tc.plan(2048, 4096, 4096, 148)[1] == 1
+    assert gemm_tc.plan(8, 4096, 4096, 148)[1] > 1 and gemm_tc.plan(8, 102400, 4096, 148)[1] == 1
