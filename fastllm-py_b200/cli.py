@@ -103,3 +103,36 @@ def main(argv=None) -> int:
 
 if __name__ == "__main__":
     sys.exit(main())
+
+
+def make_model_main(argv=None) -> int:
+    """make_model <config.json | model folder> <out folder> [--seed S] [--std X] [--norm-std Y] [--dtype D]
+
+    The random-weights mode from the command line: reads a configuration (the architecture's own
+    config.json keys), writes `out/config.json` and `out/model.safetensors` with seeded random
+    tensors of the names and shapes the architecture's parts expect.  Needs no GPU; meant for
+    small models (tests, replay), since the tensors are made in host memory."""
+    import json
+    from pathlib import Path
+
+    from .config.registry import architecture_of
+    from .weights import write_model_folder
+
+    ap = argparse.ArgumentParser(prog="make_model", description=make_model_main.__doc__,
+                                 formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("config", help="a config.json, or a folder that holds one")
+    ap.add_argument("out", help="folder to write")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--std", type=float, default=0.02, help="standard deviation of matrices and embeddings")
+    ap.add_argument("--norm-std", type=float, default=0.02, help="norm weights are 1 + N(0, this)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])
+    args = ap.parse_args(argv)
+    path = Path(args.config)
+    if path.is_dir():
+        path = path / "config.json"
+    raw = json.loads(path.read_text())
+    arch = architecture_of(raw)
+    config = arch.config_class.from_hf(raw)
+    folder = write_model_folder(config, args.out, args.seed, args.std, args.norm_std, args.dtype)
+    print(f"wrote {folder}/config.json and model.safetensors ({raw.get('architectures', ['?'])[0]}, seed {args.seed})")
+    return 0

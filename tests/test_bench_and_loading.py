@@ -6,6 +6,7 @@ from pathlib import Path
 import torch
 
 sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+sys.path.insert(0, str(Path(__file__).resolve().parent))
 
 
 def test_serving_workload_is_seeded_and_in_range():
@@ -72,3 +73,35 @@ def test_product_plans_without_a_gpu():
             assert (bn >= 512) == (m > 64)
     assert gemm_tc.plan(256, 4096, 4096, 148)[1] > 1 and gemm_tc.plan(2048, 4096, 4096, 148)[1] == 1
     assert gemm_tc.plan(8, 4096, 4096, 148)[1] > 1 and gemm_tc.plan(8, 102400, 4096, 148)[1] == 1
+
+
+def test_make_model_command_writes_a_loadable_folder(tmp_path):
+    """The random-weights mode from the command line: a config.json in, a model folder out whose
+    tensors are exactly what the architecture expects, the same for the same seed."""
+    import json
+    import subprocess
+
+    from safetensors.torch import load_file
+
+    import tiny
+    from fastllm_py_b200.config.registry import load_config
+    from fastllm_py_b200.parts import BuildContext, Decoder
+    from fastllm_py_b200.weights import SafetensorsStore, check_store
+
+    root = Path(__file__).resolve().parent.parent
+    cfg = tiny.CONFIGS["tiny_b"]["config"]
+    src = tmp_path / "config.json"
+    src.write_text(json.dumps(cfg.to_hf()))
+    outs = []
+    for name, seed in (("a", 5), ("b", 5), ("c", 6)):
+        out = tmp_path / name
+        done = subprocess.run([sys.executable, str(root / "bin" / "make_model"), str(src), str(out),
+                               "--seed", str(seed), "--std", "0.03"], capture_output=True, text=True)
+        assert done.returncode == 0, done.stderr
+        outs.append(load_file(str(out / "model.safetensors")))
+    arch, config = load_config(tmp_path / "a")
+    assert config == cfg
+    decoder = Decoder(arch.make_plan(config, None), BuildContext(torch.device("cpu"), torch.bfloat16, 16, 1))
+    check_store(decoder.expected_tensors(), SafetensorsStore(tmp_path / "a"), "a")
+    assert all(torch.equal(outs[0][k], outs[1][k]) for k in outs[0])
+    assert any(not torch.equal(outs[0][k], outs[2][k]) for k in outs[0])
