@@ -102,7 +102,7 @@ class Model:
         if ec.max_tokens is not None:
             num_pages = max(1, -(-ec.max_tokens // ec.page_size))
         else:
-            per_token = CacheManager.bytes_per_token(needs, itemsize)
+            per_token = CacheManager.bytes_per_token(needs, ec.page_size, itemsize)
             free, _ = torch.cuda.mem_get_info(self.decoder.ctx.device)
             reserve = 2 << 30                                   # activations, logits, graphs
             budget = max(0, int(free * ec.memory_fraction) - reserve)

@@ -14,9 +14,15 @@ It replaces fastllm-py's two cache forms: the growable per-sequence buffer
 cannot grow past `max_pages_per_request`, and asking for more pages than are
 free raises OutOfPages and changes nothing.
 
-Device layout of one layer's cache in a group:
-    [num_pages, 2 (keys, values), kv_heads, page_size, head_dim]
-so that the `page_size x head_dim` tile of one head of one page is contiguous.
+Device layout of one layer's cache in a group: [num_pages, *need.page_shape(page_size)];
+what a page holds is the need's business (keys and values, `cache.needs.PagedKV`), not
+the manager's.
+
+Check mode (`poison`): every page that goes back is overwritten on the device with a
+value no computation survives (1e4 by default: keys or values of that size swamp a
+softmax or an output row without turning masked places into NaN), so that a kernel which
+reads a page it no longer owns, or a place of a fresh page that was never written, shows
+in the logits instead of passing by luck.
 """
 from __future__ import annotations
 
@@ -24,13 +30,13 @@ from dataclasses import dataclass, field
 
 import numpy as np
 
-from .needs import FixedState, PagedKV
+from .needs import FixedState, PagedNeed
 from .pages import OutOfPages, PagePool, SlotPool
 
 
 @dataclass
 class PageGroup:
-    need: PagedKV
+    need: PagedNeed
     cache_ids: list
     pool: PagePool
     tensors: dict = field(default_factory=dict)      # cache id -> device tensor
@@ -56,9 +62,11 @@ class RequestCache:
 
 class CacheManager:
     def __init__(self, needs: dict, page_size: int, num_pages: int, max_requests: int,
-                 max_pages_per_request: int):
-        """`needs`: cache id -> PagedKV | FixedState | None, one per run that has a cache."""
+                 max_pages_per_request: int, poison: float | None = None):
+        """`needs`: cache id -> PagedNeed | FixedState | None, one per run that has a cache."""
         self.page_size = page_size
+        self.poison = poison                          # check mode: returned pages are filled with this
+        self.pages_poisoned = 0
         self.max_requests = max_requests
         self.max_pages_per_request = max_pages_per_request
         self.groups: list[PageGroup] = []
@@ -71,7 +79,7 @@ class CacheManager:
                 continue
             if isinstance(need, FixedState):
                 self.state_needs[cid] = need
-            elif isinstance(need, PagedKV):
+            elif isinstance(need, PagedNeed):
                 if need not in by_need:
                     by_need[need] = len(self.groups)
                     self.groups.append(PageGroup(need, [], PagePool(num_pages)))
@@ -90,24 +98,37 @@ class CacheManager:
         import torch
 
         for g in self.groups:
-            n = g.need
+            dt = activation_dtype if g.need.dtype == "activation" else getattr(torch, g.need.dtype)
+            shape = (g.pool.num_pages,) + tuple(g.need.page_shape(self.page_size))
             for cid in g.cache_ids:
-                g.tensors[cid] = torch.zeros(
-                    (g.pool.num_pages, 2, n.kv_heads, self.page_size, n.head_dim),
-                    dtype=activation_dtype, device=device)
+                g.tensors[cid] = torch.zeros(shape, dtype=dt, device=device)
+                if self.poison is not None:
+                    g.tensors[cid].fill_(self.poison)     # never-written places are as bad as stale ones
         for cid, need in self.state_needs.items():
             dt = activation_dtype if need.dtype == "activation" else getattr(torch, need.dtype)
             self.state_tensors[cid] = torch.zeros((self.max_requests,) + tuple(need.shape),
                                                   dtype=dt, device=device)
 
     @staticmethod
-    def bytes_per_token(needs: dict, itemsize: int) -> int:
+    def bytes_per_token(needs: dict, page_size: int, itemsize: int) -> int:
         """Cache bytes one token costs over all paged layers (for sizing the pools)."""
-        total = 0
-        for need in needs.values():
-            if isinstance(need, PagedKV):
-                total += 2 * need.kv_heads * need.head_dim * itemsize
-        return total
+        return sum(need.bytes_per_token(page_size, itemsize) for need in needs.values()
+                   if isinstance(need, PagedNeed))
+
+    def _give_back(self, group: PageGroup, pages: list) -> None:
+        """Pages return to the group's pool; in check mode their contents are destroyed first
+        (on the current stream, so after every kernel launched so far that may still read them)."""
+        if not pages:
+            return
+        if self.poison is not None and group.tensors:
+            import torch
+
+            any_tensor = next(iter(group.tensors.values()))
+            index = torch.tensor(pages, dtype=torch.long, device=any_tensor.device)
+            for tensor in group.tensors.values():
+                tensor.index_fill_(0, index, self.poison)
+            self.pages_poisoned += len(pages)
+        group.pool.give_back(pages)
 
     # ------------------------------------------------------------- requests
     def admit(self, request_id) -> RequestCache:
@@ -175,7 +196,7 @@ class CacheManager:
             row = rc.pages[gi]
             dead_pages = min(max(0, first_needed) // self.page_size, len(row))
             if dead_pages > rc.released[gi]:
-                g.pool.give_back(row[rc.released[gi]:dead_pages])
+                self._give_back(g, row[rc.released[gi]:dead_pages])
                 for i in range(rc.released[gi], dead_pages):
                     row[i] = -1
                 rc.tables[gi][rc.released[gi]:dead_pages] = -1
@@ -186,7 +207,7 @@ class CacheManager:
         """The request ended (or is pushed out): everything it holds goes back."""
         rc = self.live.pop(request_id)
         for gi, g in enumerate(self.groups):
-            g.pool.give_back([p for p in rc.pages[gi] if p >= 0])
+            self._give_back(g, [p for p in rc.pages[gi] if p >= 0])
             rc.pages[gi] = []
         self.slots.give_back(rc.slot)
 

@@ -28,6 +28,9 @@ class EngineConfig:
     max_batched_tokens: int = 2048    # token budget of one step
     max_model_len: int | None = None  # longest sequence (None: the model's max_position_embeddings)
     cuda_graph: bool = True           # capture decode-only steps
+    check_cache: bool = False         # check mode: pages that go back are overwritten with `cache_poison`
+    cache_poison: float = 1.0e4       # ... a value that swamps any softmax or output row it gets into
+    status_every: int = 1             # the scheduler reads the kernels' error word every this many steps (0: never)
     device: str = "cuda:0"
 
     def __post_init__(self):

@@ -422,18 +422,8 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
     }
 }
 
-// ------------------------------------------------------ persistent variant
-// For prompt-sized products (token tiles of 256, no K split) one CTA per SM walks
-// over output tiles tile = blockIdx.x, + gridDim.x, ...  The ring of shared-memory
-// stages runs on across tile boundaries, and the accumulator is double-buffered
-// in tensor memory (2 x 256 columns): while the epilogue warps drain tile i from
-// one buffer, the MMA warp already fills the other with tile i + 1, so the
-// tensor cores do not wait for stores, and a tile count that is no multiple of
-// the SM count costs a partial wave of tiles, not of whole kernels.
-#define TCP_BN 256
-#define TCP_STAGES 4
-
-// The order in which the persistent kernels walk over output tiles.  The CTAs
+// ------------------------------------------------------------ tile order
+// The order in which the persistent (CTA-pair) kernel walks over output tiles.  The CTAs
 // (or CTA pairs) that run at the same time work on consecutive tiles, so these
 // should share operands: token tiles go fastest inside panels of TC_RASTER_M
 // token tiles, i.e. a weight tile is fetched from DRAM once per panel and used by
@@ -450,198 +440,11 @@ __device__ __forceinline__ void tc_raster(int tile, int tiles_n, int tiles_m, in
     tm = panel * TC_RASTER_M + (within - tn * rows);
 }
 
-template <typename OutT>
-__global__ void __launch_bounds__(TC_THREADS) gemm_tc_persistent_kernel(
-    const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-    OutT* __restrict__ C, long ldc, int M, int N, int K, int tiles_n, int num_tiles,
-    int* __restrict__ status) {
-    using L = TcSmem<TCP_BN, TCP_STAGES>;
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full_bar = (uint64_t*)(tiles + L::TILE_BYTES);
-    uint64_t* empty_bar = full_bar + TCP_STAGES;
-    uint64_t* acc_full = empty_bar + TCP_STAGES;            // [2] accumulator ready for the epilogue
-    uint64_t* acc_empty = acc_full + 2;                     // [2] accumulator drained
-    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
-    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_kb = (K + TC_BK - 1) / TC_BK;
-    const int my_tiles = ((int)blockIdx.x < num_tiles) ? (num_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < TCP_STAGES; ++s) {
-            mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], 1);
-        }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], 4);                    // one arrival per epilogue warp
-        }
-        *abort_flag = (*(volatile int*)status != 0) ? 1 : 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    if (warp == 1) {
-        tmem_alloc(tmem_slot, 512);
-        tmem_relinquish();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    pdl_trigger();
-
-    auto tile_coords = [&](int i, int& tn, int& tm) {
-        tc_raster((int)blockIdx.x + i * (int)gridDim.x, tiles_n, num_tiles / tiles_n, tn, tm);
-    };
-
-    if (warp == 0) {
-        if (lane == 0) {
-            // ---- producer (counters are advanced by hand: a division per stage would
-            // cost more than the stage's share of the issue budget)
-            const int total = my_tiles * num_kb;
-            const int ahead = *abort_flag ? 0 : (total < TCP_STAGES ? total : TCP_STAGES);
-            int tn, tm;
-            {
-                int ti = 0, kb = 0;
-                tile_coords(0, tn, tm);
-                for (int it = 0; it < ahead; ++it) {       // weights first: no kernel writes them
-                    mbar_expect_tx(&full_bar[it], L::STAGE_BYTES);
-                    tma_load_2d(tiles + it * L::STAGE_BYTES, &map_w, &full_bar[it], kb * TC_BK, tn * TC_BM);
-                    if (++kb == num_kb) { kb = 0; tile_coords(++ti, tn, tm); }
-                }
-            }
-            pdl_wait();
-            int ti = 0, kb = 0;
-            tile_coords(0, tn, tm);
-            for (int it = 0; it < ahead; ++it) {
-                tma_load_2d(tiles + it * L::STAGE_BYTES + L::A_BYTES, &map_a, &full_bar[it], kb * TC_BK, tm * TCP_BN);
-                if (++kb == num_kb) { kb = 0; tile_coords(++ti, tn, tm); }
-            }
-            int s = ahead % TCP_STAGES;
-            uint32_t ph = (uint32_t)(ahead / TCP_STAGES) & 1u;
-            for (int it = ahead; it < total && !*abort_flag; ++it) {
-                if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
-                    if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_EMPTY_WAIT); }
-                    break;
-                }
-                unsigned char* a_dst = tiles + s * L::STAGE_BYTES;
-                mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
-                tma_load_2d(a_dst, &map_w, &full_bar[s], kb * TC_BK, tn * TC_BM);
-                tma_load_2d(a_dst + L::A_BYTES, &map_a, &full_bar[s], kb * TC_BK, tm * TCP_BN);
-                if (++kb == num_kb) { kb = 0; tile_coords(++ti, tn, tm); }
-                if (++s == TCP_STAGES) { s = 0; ph ^= 1u; }
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0) {
-            // ---- MMA issuer
-            constexpr uint32_t idesc = instr_desc_bf16(TC_BM, TCP_BN);
-            int s = 0;
-            uint32_t ph = 0;
-            bool ok = !*abort_flag;
-            for (int i = 0; i < my_tiles && ok; ++i) {
-                const int buf = i & 1;
-                const uint32_t use = (uint32_t)(i >> 1);
-                if (!mbar_wait(&acc_empty[buf], (use & 1u) ^ 1u, abort_flag)) {
-                    if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_ACC_WAIT); }
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * TCP_BN);
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(&full_bar[s], ph, abort_flag)) {
-                        if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_FULL_WAIT); }
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint32_t a_addr = smem_u32(tiles + s * L::STAGE_BYTES);
-                    const uint64_t adesc = smem_desc_sw128(a_addr);
-                    const uint64_t bdesc = smem_desc_sw128(a_addr + L::A_BYTES);
-#pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k)
-                        umma_bf16(tmem_acc, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                                  (kb > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(&empty_bar[s]);
-                    if (++s == TCP_STAGES) { s = 0; ph ^= 1u; }
-                }
-                if (ok) umma_commit(&acc_full[buf]);
-            }
-        }
-    } else {
-        // ---- epilogue warps 2..5
-        const int quarter = warp & 3;
-        bool ok = !*abort_flag;
-        pdl_wait();
-        for (int i = 0; i < my_tiles && ok; ++i) {
-            const int buf = i & 1;
-            const uint32_t use = (uint32_t)(i >> 1);
-            if (!mbar_wait(&acc_full[buf], use & 1u, abort_flag)) {
-                if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, TC_ERR_ACC_WAIT); }
-                ok = false;
-                break;
-            }
-            tc_fence_after();
-            int tn, tm;
-            tile_coords(i, tn, tm);
-            const int o = tn * TC_BM + quarter * 32 + lane;
-            const int t0 = tm * TCP_BN;
-            const uint32_t t_base = tmem_base + (uint32_t)(buf * TCP_BN) + ((uint32_t)(quarter * 32) << 16);
-#pragma unroll 1
-            for (int c = 0; c < TCP_BN; c += 32) {
-                if (t0 + c >= M) break;
-                uint32_t r[32];
-                tmem_ld16(t_base + (uint32_t)c, r);
-                tmem_ld16(t_base + (uint32_t)c + 16u, r + 16);
-                tmem_ld_wait();
-                if (o < N) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int t = t0 + c + j;
-                        if (t < M) C[(long)t * ldc + o] = from_f32<OutT>(__uint_as_float(r[j]));
-                    }
-                }
-            }
-            // this warp has read all it needs of the buffer: hand it back to the MMA warp
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
-            }
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 1) {
-        tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
-    }
-}
-
-template <typename OutT>
-static int launch_tc_persistent(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C, long ldc, int M,
-                                int N, int K, int num_sms, int* status, cudaStream_t stream) {
-    using L = TcSmem<TCP_BN, TCP_STAGES>;
-    constexpr int SMEM = L::TOTAL + 64;                     // four more barriers than the one-tile kernel
-    static bool configured = false;
-    auto kernel = gemm_tc_persistent_kernel<OutT>;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
-    const int tiles_n = (N + TC_BM - 1) / TC_BM;
-    const int num_tiles = tiles_n * ((M + TCP_BN - 1) / TCP_BN);
-    const int ctas = num_tiles < num_sms ? num_tiles : num_sms;
-    return fl_launch(kernel, dim3(ctas), dim3(TC_THREADS), (size_t)SMEM, stream, map_w, map_a, (OutT*)C, ldc, M, N,
-                     K, tiles_n, num_tiles, status);
-}
-
 // ------------------------------------------------------------- pair variant
-// The persistent kernel again, run by PAIRS of CTAs on neighbouring SMs
+// For everything above 64 tokens: a persistent kernel (a loop over output tiles per
+// CTA, the ring of shared-memory stages running on across tile boundaries, the
+// accumulator double-buffered in tensor memory so that the epilogue of tile i
+// overlaps the MMAs of tile i + 1) run by PAIRS of CTAs on neighbouring SMs
 // (a cluster of two) that issue one MMA together (tcgen05 cta_group::2): a pair
 // computes a 256 x 256 tile, each CTA holding 128 of the weight rows and 128 of
 // the token rows in its shared memory and its own 128 x 256 half of the
@@ -1028,6 +831,22 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, long ld_
     C[(long)t * ldc + o] = from_f32<OutT>(acc);
 }
 
+// C = the sum of `splits` slabs partial[z][M][ld_partial] (what fl_gemm_tc_partial leaves), for a
+// consumer that has no kernel of its own that adds the slabs while it reads them.
+FL_API int fl_splitk_reduce(const float* partial, long ld_partial, int splits, void* C, int c_dtype, long ldc,
+                            int M, int N, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (splits < 1 || M > 65535) return (int)cudaErrorInvalidValue;
+    dim3 grid((N + 255) / 256, M);
+    if (c_dtype == FL_BF16)
+        return fl_launch(splitk_reduce_kernel<bf16>, grid, dim3(256), 0, stream, partial, ld_partial, splits,
+                         (bf16*)C, ldc, M, N);
+    if (c_dtype == FL_F32)
+        return fl_launch(splitk_reduce_kernel<float>, grid, dim3(256), 0, stream, partial, ld_partial, splits,
+                         (float*)C, ldc, M, N);
+    return (int)cudaErrorInvalidValue;
+}
+
 // ----------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -1190,10 +1009,6 @@ static int gemm_tc_impl(const void* A, long lda, const void* W, long ldw, void* 
             rc = dispatch_tc_pair<float>(bnt, map_w, map_a, C, ldc, M, N, K, num_sms, status, stream, splits, kb_per_split, part, ld_partial);
         else
             return (int)cudaErrorInvalidValue;
-    } else if (bn == TCP_BN && splits == 1 && num_sms > 0) {
-        if (c_dtype == FL_BF16) return launch_tc_persistent<bf16>(map_w, map_a, C, ldc, M, N, K, num_sms, status, stream);
-        if (c_dtype == FL_F32) return launch_tc_persistent<float>(map_w, map_a, C, ldc, M, N, K, num_sms, status, stream);
-        return (int)cudaErrorInvalidValue;
     } else if (c_dtype == FL_BF16) {
         rc = dispatch_tc<bf16>(bn, map_w, map_a, C, ldc, workspace, ld_partial, M, N, K, splits, kb_per_split, status, stream);
     } else if (c_dtype == FL_F32) {
@@ -1202,12 +1017,7 @@ static int gemm_tc_impl(const void* A, long lda, const void* W, long ldw, void* 
         return (int)cudaErrorInvalidValue;
     }
     if (rc || splits == 1 || skip_reduce) return rc;
-    dim3 grid((N + 255) / 256, M);
-    if (c_dtype == FL_BF16)
-        return fl_launch(splitk_reduce_kernel<bf16>, grid, dim3(256), 0, stream, (const float*)workspace,
-                         ld_partial, splits, (bf16*)C, ldc, M, N);
-    return fl_launch(splitk_reduce_kernel<float>, grid, dim3(256), 0, stream, (const float*)workspace,
-                     ld_partial, splits, (float*)C, ldc, M, N);
+    return fl_splitk_reduce(workspace, ld_partial, splits, C, c_dtype, ldc, M, N, stream);
 }
 
 FL_API int fl_gemm_tc(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc,
@@ -1306,7 +1116,8 @@ FL_API int fl_gemm_tc_static_scratch(const void* A, long lda, const void* W, lon
         if (e != cudaSuccess) return (int)e;
         tc_static_scratch_addr[device] = p;
     }
-    if (bn == 0 || splits == 0) fl_gemm_tc_plan(M, N, K, num_sms, &bn, &splits);
+    if (bn == 0) fl_gemm_tc_plan(M, N, K, num_sms, &bn, &splits);     // the rule of fl_gemm_tc: only bn == 0 plans
+    if (splits < 1) return (int)cudaErrorInvalidValue;
     const long ld_partial = ((long)N + 3) / 4 * 4;
     const long needed = splits > 1 ? (long)splits * M * ld_partial : 0;
     if (needed > FL_TC_STATIC_SCRATCH_FLOATS) {

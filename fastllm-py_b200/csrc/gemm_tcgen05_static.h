@@ -23,7 +23,9 @@
 //
 // Set-up.  The first call on a device looks up the array's device address (with
 // that device current) and keeps it; make that first call outside any stream
-// capture, once per device, before relying on later calls.
+// capture, once per device, before relying on later calls.  The address is kept
+// in a plain table without a lock: the first call on a device must not run at
+// the same time as another call on that device from a second host thread.
 //
 // Limits.  A problem fits when splits * M * round_up(N, 4) <=
 // FL_TC_STATIC_SCRATCH_FLOATS.  Anything larger is refused: the function
@@ -50,8 +52,9 @@ extern "C" {
 
 // C[M, N] = A[M, K] * W[N, K]^T; A and W bfloat16 (row pitches lda, ldw multiples
 // of 8 elements, bases 16-byte aligned), C bfloat16 (c_dtype 1) or float (0).
-// bn / splits: the token-tile width and the number of K splits, or 0 / 0 to let
-// the library choose (fl_gemm_tc_plan).  status: a device int that receives a
+// bn / splits: the token-tile width and the number of K splits as fl_gemm_tc takes
+// them; bn = 0 lets the library choose both (fl_gemm_tc_plan), and a given bn
+// needs splits >= 1 (anything else returns cudaErrorInvalidValue).  status: a device int that receives a
 // code if a bounded wait inside the kernel gives up.  Returns 0 when launched, a
 // cudaError_t value when a CUDA call failed, or one of the FL_TC_ERR_* codes.
 int fl_gemm_tc_static_scratch(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype,

@@ -22,15 +22,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
-from ..cache.needs import PagedKV
-from ..parts.attention import PagedCacheView
-
-
-@dataclass
-class StateView:
-    """What a mixer with fixed-size state gets for one run."""
-    tensor: torch.Tensor          # [request slots, *shape]
-    writes: bool
+from ..cache.views import PagedCacheView, StateView
 
 
 class StepBuffers:
@@ -116,8 +108,8 @@ class StepContext:
     max_seq_len: int = 0
     rows_identity: bool = False    # the wanted rows are all rows, in order
     n_decode_tokens: int = 0       # tokens of requests that bring exactly one token
-    decode_splits: int = 1         # key splits the decode attention kernel is launched with
-    decode_split_keys: int = 256   # ... and the keys in each
+    for_graph: bool = False        # the step may be captured or replayed as a CUDA graph
+    plans: dict = field(default_factory=dict)   # what mixers decided on the host for this step (plan_step)
     token_feed: object = None      # int32 device tensor: a token id -1 - r stands for token_feed[r]
     _views: dict = field(default_factory=dict)
 

@@ -14,7 +14,8 @@ import torch
 
 from ..cache import CacheManager, OutOfPages
 from ..config.engine import EngineConfig
-from ..parts import BuildContext, Decoder, Workspace
+from ..native import scratch
+from ..parts import BuildContext, Decoder, EngineLimits, Workspace
 from .batch import StepBuffers, StepContext, build_views
 
 
@@ -38,29 +39,46 @@ class Engine:
         self.max_tokens = min(config.max_batched_tokens, 65535)
         bt_stride = -(-max_model_len // self.page_size)
         self.cache = CacheManager(decoder.cache_needs(), self.page_size, num_pages,
-                                  config.max_requests, bt_stride)
+                                  config.max_requests, bt_stride,
+                                  poison=config.cache_poison if config.check_cache else None)
         self.cache.allocate(self.device, self.dtype)
-        # the most key/value heads of any paged cache: how many CTAs a decode token gives the attention kernel
-        self._num_sms = (torch.cuda.get_device_properties(self.device).multi_processor_count
-                         if self.device.type == "cuda" else 148)
-        self._kv_heads = max([getattr(need, "kv_heads", 1) for need in decoder.cache_needs().values()] or [1])
-        self._head_dim = max([getattr(need, "head_dim", 128) for need in decoder.cache_needs().values()] or [128])
         self.workspace = Workspace(self.device, self.max_tokens)
         self.buffers = StepBuffers(self.device, self.max_tokens, config.max_requests,
                                    len(self.cache.groups), bt_stride)
         from ..native.gemm_tc import status_word
         self.status = status_word(self.device)
+        # the error word's last copy on the host: refreshed after every step without waiting for it
+        self.status_host = torch.zeros(1, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        self._status_pinned = self.status_host.is_pinned()
         self.no_rotation = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.vocab = decoder.vocab
         self.steps_run = 0
         # An int32 device tensor (the sampler's output) from which the embedding takes tokens that
         # the host has not read yet: a step may name such a token as -1 - row.  None: not offered.
-        self.token_feed = None
+        # Only an embedding part that says it understands such ids is ever given them.
+        self.accepts_fed_tokens = decoder.takes_fed_tokens
+        self._token_feed = None
         self.use_graph = bool(config.cuda_graph)
         self._graphs: dict = {}          # step shape -> (graph, logits view, kernels in it)
+        self._graphs_generation = None   # the scratch generations the graphs in _graphs were captured under
         self._warmed: dict = {}          # step shape -> times seen before its capture
         self.max_graphs = 64
+        self.graphs_dropped = 0          # graphs thrown away because a buffer they point to was replaced
         self._bt_rows: list = [None] * config.max_requests   # (request uid, table version) last written per row
+        # every part sizes the scratch memory of its kernels now, so that nothing grows under a captured graph
+        self.limits = EngineLimits(self.max_tokens, config.max_requests, max_model_len)
+        decoder.reserve(self.limits, self.workspace)
+
+    @property
+    def token_feed(self):
+        return self._token_feed
+
+    @token_feed.setter
+    def token_feed(self, tensor):
+        if tensor is not None and not self.accepts_fed_tokens:
+            raise RuntimeError("this model's embedding part does not take tokens from the device "
+                               "(it does not declare takes_fed_tokens)")
+        self._token_feed = tensor
 
     # -------------------------------------------------------------- requests
     def begin(self, request_id):
@@ -184,25 +202,10 @@ class Engine:
             max_q_len=max(q_lens), max_seq_len=max(c + q for c, q in zip(ctx_lens, q_lens)),
             n_decode_tokens=n_dec, token_feed=self.token_feed,
             rows_identity=(m == n_tokens and bool((rows[:m] == np.arange(m)).all())))
-        step.decode_split_keys, step.decode_splits = self._decode_splits(step)
+        step.for_graph = self.use_graph and step.max_q_len == 1 and self.decoder.graph_safe
+        self.decoder.plan_step(step)
         step._views = build_views(cache, buf, n_tokens, n)
         return step
-
-    def _decode_splits(self, step: StepContext):
-        """(keys per split, splits) for the decode attention kernel: enough splits
-        for the longest sequence of the step.  Under graph replay both are part of
-        the graph's key: the keys per split change with the length every 256 tokens at
-        most, and the splits cover the length rounded up to 1024 (CTAs of splits beyond
-        a sequence's end leave at once)."""
-        from ..native.attention import DECODE_SPLIT, decode_split_keys, decode_splits
-
-        if step.n_decode_tokens == 0:                       # no launch of that kernel: one answer, one graph key
-            return DECODE_SPLIT, 1
-        longest = step.max_seq_len
-        keys = decode_split_keys(step.n_decode_tokens, self._kv_heads, longest, self._num_sms, self._head_dim)
-        if self.use_graph and step.max_q_len == 1:
-            longest = -(-longest // 1024) * 1024
-        return keys, decode_splits(longest, keys)
 
     def step(self, entries) -> torch.Tensor:
         """Run one step; returns float32 logits [wanted places, vocab] on the
@@ -214,10 +217,29 @@ class Engine:
             logits = self._with_graph(step)
         else:
             logits = self.decoder.forward(step)
+        if self._status_pinned:
+            self.status_host.copy_(self.status, non_blocking=True)     # read by `faulted` once the step is over
         for e in entries:
             self.cache.commit(self.cache.live[e.request_id], len(e.tokens))
         self.steps_run += 1
         return logits
+
+    def _scratch_generation(self):
+        return (scratch.generation(self.device), self.workspace.generation)
+
+    def drop_stale_graphs(self) -> int:
+        """Captured graphs hold the addresses of the buffers they were captured with.  When any
+        such buffer has been replaced since (it grew), those graphs must never run again: all of
+        them are dropped here, before the next replay or capture.  Returns how many went."""
+        now = self._scratch_generation()
+        dropped = 0
+        if self._graphs_generation != now:
+            dropped = len(self._graphs)
+            self._graphs.clear()
+            self._warmed.clear()
+            self._graphs_generation = now
+            self.graphs_dropped += dropped
+        return dropped
 
     def _with_graph(self, step: StepContext) -> torch.Tensor:
         """A step replays a CUDA graph captured for its shape.  The first step of
@@ -225,8 +247,8 @@ class Engine:
         the ones after it are replayed: the step's inputs already sit in fixed
         device buffers, so a replay needs nothing but the upload that `prepare`
         did.  The shape is everything that the launches depend on: the numbers
-        of tokens, requests, single-token requests and wanted rows, the split
-        count of the decode attention, and what the mixers add.  A capture
+        of tokens, requests, single-token requests and wanted rows, and what the
+        mixers add (the attention part: how its decode kernel splits the keys).  A capture
         costs about as much as twenty steps save, so it is made where a shape
         is sure to come again: decode-only steps (hundreds alike; this is the
         captured decode step of fastllm_py/batched.py:230-275 with the LM head
@@ -238,7 +260,8 @@ class Engine:
 
         feed = None if self.token_feed is None else self.token_feed.data_ptr()
         key = (step.n_tokens, step.n_requests, step.n_decode_tokens, step.n_wanted, step.rows_identity,
-               step.decode_splits, step.decode_split_keys, self.decoder.graph_key(step), feed)
+               self.decoder.graph_key(step), feed)
+        self.drop_stale_graphs()
         entry = self._graphs.pop(key, None)
         if entry is not None:
             self._graphs[key] = entry                       # most recently used last
@@ -260,6 +283,8 @@ class Engine:
             before = ops.counter.launches
             with torch.cuda.graph(graph):
                 logits = self.decoder.forward(step)
+            if self._scratch_generation() != self._graphs_generation:
+                raise RuntimeError("a scratch buffer was replaced while a step was being captured")
             entry = self._graphs[key] = (graph, logits, ops.counter.launches - before)
             ops.counter.launches = before
         graph, logits, kernels = entry
@@ -269,8 +294,18 @@ class Engine:
 
     def check_status(self) -> None:
         """Raise if a kernel reported a fault since the last check (synchronises)."""
-        code = int(self.status.item())
+        self._raise_for(int(self.status.item()))
+
+    def faulted(self) -> None:
+        """The same without waiting for the device: looks at the copy of the error word that
+        every step sends to the host behind itself.  Call it after something else has waited
+        for the step (the sampler's token read-back, say); then the copy is the step's own."""
+        self._raise_for(int(self.status_host[0]))
+
+    def _raise_for(self, code: int) -> None:
         if code != 0:
             self.status.zero_()
+            self.status_host.zero_()
             raise RuntimeError(f"a kernel reported error code {code} (a token id outside the "
-                               f"embedding table, or a wait that gave up)")
+                               f"embedding table, or a wait that gave up); the tokens of this "
+                               f"step and of any step after it are not to be trusted")

@@ -34,11 +34,23 @@ left out of step n + 1 beforehand; one that ends by a stop token is found out
 one step late: its row of step n + 1 is computed for nothing and dropped.
 `step()` returns the tokens of the step it collected, which is then the one
 launched a call earlier.  Requests with penalties (which need the tokens on the
-host) and engines or samplers without the device path run without it.
+host), engines whose embedding part does not take tokens from the device, and
+samplers without the device path run without it.
+
+Faults.  Kernels whose bounded waits give up, and the embedding kernel when it
+meets a token outside its table, set an error word on the device; every step
+sends a copy of it to the host behind itself, and the scheduler looks at that
+copy whenever it has read a step's tokens (every `status_every` steps), so that
+generation stops with an error instead of going on with tokens that mean nothing.
+
+Memory of the host.  A request is known to the scheduler while it waits or runs.
+Once its last token has been handed out it moves to `finished`, which keeps the
+most recent ones for inspection and forgets older ones, and its id may be used
+again.
 """
 from __future__ import annotations
 
-from collections import deque
+from collections import OrderedDict, deque
 from dataclasses import dataclass, field
 
 from ..sampling import SamplingParams, SamplingState
@@ -93,14 +105,17 @@ class Scheduler:
         self.token_budget = token_budget or engine.max_tokens
         self.waiting: deque = deque()
         self.running: list = []                    # in order of admission
-        self.requests: dict = {}
+        self.requests: dict = {}                   # waiting or running
+        self.finished: OrderedDict = OrderedDict() # the most recent `keep_finished` that ended
+        self.keep_finished = 1024
+        self.status_every = int(getattr(getattr(engine, "config", None), "status_every", 1) or 0)
         self._next_id = 0
         self.stats = {"steps": 0, "pushed_out": 0, "prefill_tokens": 0, "decode_tokens": 0,
                       "steps_ahead": 0, "rows_dropped": 0}
         self._flight: _InFlight | None = None
         # the device path for tokens: the engine's embedding reads the sampler's output
         feed = getattr(sampler, "out", None)
-        self.run_ahead = bool(run_ahead and feed is not None and hasattr(engine, "token_feed")
+        self.run_ahead = bool(run_ahead and feed is not None and getattr(engine, "accepts_fed_tokens", False)
                               and hasattr(sampler, "launch") and hasattr(sampler, "collect"))
         if self.run_ahead:
             engine.token_feed = feed
@@ -131,8 +146,14 @@ class Scheduler:
                       frozenset(int(s) for s in (stop_ids or ())), arrival_time)
         req.sampling_state = SamplingState(req.sampling)
         self.requests[request_id] = req
+        self.finished.pop(request_id, None)
         self.waiting.append(req)
         return request_id
+
+    def request(self, request_id) -> Request:
+        """A request that waits or runs, or one of the most recently finished."""
+        req = self.requests.get(request_id)
+        return req if req is not None else self.finished[request_id]
 
     def has_work(self) -> bool:
         return bool(self.waiting or self.running or self._flight is not None)
@@ -297,16 +318,30 @@ class Scheduler:
                 req.finished, req.finish_reason = True, done
                 self.engine.end(req.request_id)
                 self.running.remove(req)
+                del self.requests[req.request_id]
+                self.finished[req.request_id] = req
+                while len(self.finished) > self.keep_finished:
+                    self.finished.popitem(last=False)
             outputs.append(StepOutput(req.request_id, tok, bool(done)))
         self.stats["steps"] += 1
+        if self.status_every and self.stats["steps"] % self.status_every == 0:
+            check = getattr(self.engine, "faulted", None)
+            if check is not None:
+                check()                                # the tokens were waited for: the step's error word is here too
         return outputs
 
     def run(self, max_steps: int = 10_000_000, on_token=None) -> dict:
-        """Step until nothing is left; returns request id -> produced tokens."""
+        """Step until nothing is left (or `max_steps`); returns request id -> produced tokens of
+        every request that finished meanwhile and of those still waiting or running at the end."""
+        result = {}
         steps = 0
         while self.has_work() and steps < max_steps:
             for out in self.step():
+                if out.finished:
+                    result[out.request_id] = self.finished[out.request_id].output
                 if on_token is not None:
                     on_token(out)
             steps += 1
-        return {rid: req.output for rid, req in self.requests.items()}
+        for rid, req in self.requests.items():
+            result[rid] = req.output
+        return result

@@ -14,7 +14,7 @@ from ctypes import c_float, c_int, c_long, c_void_p
 
 import torch
 
-from . import ops
+from . import ops, scratch
 from .build import load_library
 
 DECODE_SPLIT = 256          # keys per split of the decode kernel when nothing chooses (any multiple of 64 will do)
@@ -86,17 +86,19 @@ def _prefill_tc_lib(head_dim: int):
     return lib
 
 
+SCRATCH = "decode attention partial results"
+
+
 def _partials(device, floats: int) -> torch.Tensor:
-    """Float scratch for the decode kernel's per-split results; grows on demand,
-    never inside a graph capture."""
-    key = ("partials", str(device))
-    ws = _state.get(key)
-    if ws is None or ws.numel() < floats:
-        if torch.cuda.is_current_stream_capturing():
-            raise RuntimeError("the decode-attention workspace would have to grow during graph capture")
-        ws = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
-        _state[key] = ws
-    return ws
+    """Float scratch for the decode kernel's per-split results (see `scratch`)."""
+    return scratch.get(device, SCRATCH, floats, at_least=1 << 20)
+
+
+def reserve_decode(device, max_tokens: int, heads: int, head_dim: int, max_seq_len: int) -> None:
+    """Size the scratch for `max_tokens` single-token requests of up to `max_seq_len` keys at the
+    shortest split the host ever picks (64 keys)."""
+    splits = decode_splits(-(-max_seq_len // 1024) * 1024, 64)
+    scratch.reserve(device, SCRATCH, max_tokens * heads * splits * (head_dim + 2))
 
 
 def decode_splits(max_seq_len: int, split_keys: int = DECODE_SPLIT) -> int:
@@ -200,15 +202,22 @@ def prefill_attention(q, out, cache_tensor, block_table, req_start, req_ctx, req
     ops._check(rc, "attention_prefill")
 
 
-def paged_attention(q, out, cache, step, heads, kv_heads, head_dim, window, scale):
-    """Attention for every token of a bfloat16 step: the decode kernel for
-    requests with one token, the prefill kernel for the others."""
+def num_sms(device) -> int:
+    key = ("sms", str(device))
+    if key not in _state:
+        _state[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _state[key]
+
+
+def paged_attention(q, out, cache, step, heads, kv_heads, head_dim, window, scale, split_keys, n_splits):
+    """Attention for every token of a bfloat16 step: the decode kernel (its keys cut every
+    `split_keys` into `n_splits`) for requests with one token, the prefill kernel for the others."""
     n_dec = step.n_decode_tokens
     if n_dec:
         tok_list = None if n_dec == step.n_tokens else step.decode_tokens
         decode_attention(q, out, cache.tensor, cache.block_table, step.tok_req, step.positions, tok_list,
                          n_dec, heads, kv_heads, head_dim, window, scale, cache.page_size,
-                         step.decode_splits, 0, step.decode_split_keys)
+                         n_splits, 0, split_keys)
     if n_dec < step.n_tokens:
         prefill_attention(q, out, cache.tensor, cache.block_table, step.req_start, step.req_ctx,
                           step.req_qlen, step.n_requests, step.n_tokens, False, heads, kv_heads,

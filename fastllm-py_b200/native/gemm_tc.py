@@ -6,7 +6,7 @@ from ctypes import c_int, c_long, c_void_p
 
 import torch
 
-from . import ops
+from . import ops, scratch
 from .build import load_library
 
 _state: dict = {}
@@ -28,6 +28,8 @@ def _lib():
         lib.fl_gemm_tc_swiglu.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
                                           c_int, c_int, c_void_p, c_void_p]
         lib.fl_gemm_tc_swiglu.restype = c_int
+        lib.fl_splitk_reduce.argtypes = [c_void_p, c_long, c_int, c_void_p, c_int, c_long, c_int, c_int, c_void_p]
+        lib.fl_splitk_reduce.restype = c_int
         _state["lib"] = lib
     return lib
 
@@ -61,17 +63,28 @@ def plan(m: int, n: int, k: int, num_sms: int):
     return p
 
 
+SCRATCH = "split-K partial sums"
+
+
 def _workspace(device, floats: int) -> torch.Tensor:
-    """Float scratch for split-K partial sums; grows on demand, never inside a graph capture."""
-    key = ("ws", str(device))
-    ws = _state.get(key)
-    if ws is None or ws.numel() < floats:
-        if torch.cuda.is_current_stream_capturing():
-            raise RuntimeError("the split-K workspace would have to grow during graph capture; "
-                               "run the step once before capturing it")
-        ws = torch.empty(max(floats, 4 << 20), dtype=torch.float32, device=device)
-        _state[key] = ws
-    return ws
+    """Float scratch for split-K partial sums (see `scratch`: grows on demand, never inside
+    a graph capture, and a growth invalidates captured graphs)."""
+    return scratch.get(device, SCRATCH, floats, at_least=4 << 20)
+
+
+def workspace_floats(m: int, n: int, k: int, device) -> int:
+    """Floats of scratch that the product [m, k] x [n, k]^T takes (0 when its plan has no K split)."""
+    _, splits = plan(m, n, k, _num_sms(device))
+    return splits * m * (-(-n // 4) * 4) if splits > 1 else 0
+
+
+def reserve(device, n: int, k: int, max_tokens: int) -> None:
+    """Size the scratch for every step of up to `max_tokens` tokens of an [n, k] weight.  The
+    plan's splits depend on the number of token tiles, so within a bracket of 64 tokens the
+    largest need is at the bracket's top: those and every count up to 64 are asked."""
+    counts = list(range(1, min(64, max_tokens) + 1)) + list(range(128, max_tokens + 64, 64))
+    need = max(workspace_floats(min(m, max_tokens), n, k, device) for m in counts)
+    scratch.reserve(device, SCRATCH, need)
 
 
 class Partial:
@@ -84,11 +97,22 @@ class Partial:
         self.data, self.splits, self.rows, self.cols, self.ld = data, splits, rows, cols, ld
         self.split_stride = rows * ld
         self.device = device
-        self.generation = _state.get(("gen", str(device)), 0)
+        self.serial = _state.get(("serial", str(device)), 0)
 
     def check(self):
-        if self.generation != _state.get(("gen", str(self.device)), 0):
+        if self.serial != _state.get(("serial", str(self.device)), 0):
             raise RuntimeError("split-K partial sums were overwritten by a later product before use")
+
+    def reduce_into(self, out: torch.Tensor) -> torch.Tensor:
+        """out[rows, cols] = the slabs added in order: for consumers without a kernel of their
+        own that adds them while reading."""
+        self.check()
+        if tuple(out.shape) != (self.rows, self.cols):
+            raise ops.KernelError(f"reduce: partial sums are {(self.rows, self.cols)}, out is {tuple(out.shape)}")
+        rc = _lib().fl_splitk_reduce(ops._ptr(self.data), self.ld, self.splits, ops._ptr(out),
+                                     ops.dtype_code(out), ops._ld(out), self.rows, self.cols, ops._stream())
+        ops._check(rc, "splitk_reduce")
+        return out
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int = 0, splits: int = 0,
@@ -121,8 +145,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int = 0, split
     deferred = defer and splits > 1
     fn = _lib().fl_gemm_tc_partial if deferred else _lib().fl_gemm_tc
     if splits > 1:
-        gen_key = ("gen", str(a.device))
-        _state[gen_key] = _state.get(gen_key, 0) + 1          # earlier Partials are now stale
+        serial_key = ("serial", str(a.device))
+        _state[serial_key] = _state.get(serial_key, 0) + 1    # earlier Partials are now stale
     rc = fn(ops._ptr(a), lda, ops._ptr(w), ldw, ops._ptr(out), ops.dtype_code(out), ldc,
             m, n, k, bn, splits, ops._ptr(ws), ws_floats, sms,
             ops._ptr(status_word(a.device)), ops._stream())

@@ -13,25 +13,14 @@ One stacked matrix serves q|k|v.  A layer that reads another layer's cache
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
-
 import torch
 
 from ..cache.needs import PagedKV
+from ..cache.views import PagedCacheView
 from ..native import ops
 from .base import Part
 from .linear import Linear
 from .registry import build_part, register_part
-
-
-@dataclass
-class PagedCacheView:
-    """What a paged mixer gets for one run: its layer's pages and this step's tables."""
-    tensor: torch.Tensor          # [pages, 2, kv_heads, page_size, head_dim]
-    block_table: torch.Tensor     # [requests in the step, max pages] int32
-    slots: torch.Tensor           # [tokens in the step] int32: page * page_size + offset
-    page_size: int
-    writes: bool                  # False when the run reads another run's cache
 
 
 @register_part("mixer", "attention")
@@ -70,6 +59,44 @@ class Attention(Part):
         if self.shares_cache:
             return None
         return PagedKV(self.kv_heads, self.head_dim, self.window)
+
+    # ---- what the host decides per step: how the decode kernel splits the keys
+    @property
+    def plan_key(self):
+        """Mixers with equal keys take equal decisions, so one of them is asked per step."""
+        return ("attention", self.heads, self.kv_heads, self.head_dim)
+
+    def _fast(self):
+        from ..native import attention as fast
+        return fast if fast.handles(self.ctx.dtype, self.head_dim) else None
+
+    def reserve(self, limits):
+        for lin in (self.qkv, self.o):
+            if lin is not None:
+                lin.reserve(self.ctx.dtype, limits.max_tokens)
+        fast = self._fast()
+        if fast is not None:
+            fast.reserve_decode(self.ctx.device, min(limits.max_tokens, limits.max_requests), self.heads,
+                                self.head_dim, limits.max_model_len)
+
+    def plan_step(self, step):
+        """(keys per split, splits) of the decode kernel for this step: enough splits for the
+        longest sequence.  In a step that may be replayed from a captured graph the splits cover
+        the length rounded up to 1024 (CTAs of splits beyond a sequence's end leave at once) and
+        the keys per split change every 256 tokens at most, so a graph serves hundreds of steps."""
+        fast = self._fast()
+        if fast is None or step.n_decode_tokens == 0:
+            step.plans[self.plan_key] = (0, 1)             # no launch of that kernel: one answer, one graph key
+            return
+        longest = step.max_seq_len
+        keys = fast.decode_split_keys(step.n_decode_tokens, self.kv_heads, longest, fast.num_sms(self.ctx.device),
+                                      self.head_dim)
+        if step.for_graph:
+            longest = -(-longest // 1024) * 1024
+        step.plans[self.plan_key] = (keys, fast.decode_splits(longest, keys))
+
+    def graph_key(self, step):
+        return step.plans.get(self.plan_key)
 
     def weight_shapes(self):
         q_out, kv_out = self.heads * self.head_dim, self.kv_heads * self.head_dim
@@ -113,10 +140,13 @@ class Attention(Part):
         return self.o.forward(ctx, out, defer=True)
 
     def attend(self, q, ctx, step, cache):
-        from ..native import attention as fast
-        if fast.handles(q.dtype, self.head_dim):
+        fast = self._fast()
+        if fast is not None:
+            if self.plan_key not in step.plans:           # a step built by hand, not by the engine
+                self.plan_step(step)
+            keys, splits = step.plans[self.plan_key]
             fast.paged_attention(q, ctx, cache, step, self.heads, self.kv_heads, self.head_dim,
-                                 self.window, self.scale)
+                                 self.window, self.scale, keys, splits)
         else:
             ops.paged_attention_simt(q, ctx, cache.tensor, cache.block_table, step.tok_req,
                                      step.positions, self.heads, self.kv_heads, self.head_dim,

@@ -12,17 +12,41 @@ engine's StepContext; buffers come from `step.workspace`):
   embedding     forward(step, out)            out: [N, hidden] float32 residual stream
   position      tables(max_positions)         -> (cos, sin) float32 [max_positions, rot_dim/2]
   norm          apply(stream, out, rows=None) adds the stream's pending sum, then norms into `out`
-  mixer         cache_need() -> PagedKV | FixedState | None
+  mixer         cache_need() -> a need of cache.needs (paged, fixed state) | None
                 forward(h, out, step, cache)  h: [N, hidden] -> out: [N, hidden]
   feed_forward  forward(h, out, step)
   block         forward(stream, step, cache)  the arrangement of mixer, feed-forward and norms
   head          forward(h, out)               h: [m, hidden] -> out: [m, vocab] float32
+
+What a part may declare beside its interface (all optional; absent means "no"):
+
+  reserve(limits)          any part: called once when an engine is built, with the most tokens
+                           of a step, the most live requests and the longest sequence, so that
+                           the part can size the scratch memory its kernels take
+  plan_step(step)          mixer: called once per step before anything is launched; decides on
+                           the host what the step's launches need (a split of the keys, say) and
+                           keeps it in `step.plans`; mixers with an equal `plan_key` are asked once
+  graph_key(step)          mixer: what of that plan fixes the launch shapes (part of the key
+                           under which a captured step is replayed)
+  graph_safe = False       any part whose forward decides on the host from the step's host copies
+  takes_partial = True     norm: `apply` accepts split-K partial sums as the stream's pending sum
+                           (otherwise the stream adds them up into a tensor first)
+  takes_fed_tokens = True  embedding: understands a token id -1 - r as "row r of `step.token_feed`"
+                           (without it the scheduler never launches a step ahead of the host)
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
 
 import torch
+
+
+@dataclass(frozen=True)
+class EngineLimits:
+    """The bounds an engine was built with, as parts see them in `reserve`."""
+    max_tokens: int          # tokens of one step
+    max_requests: int        # live requests (and so requests of one step)
+    max_model_len: int       # longest sequence
 
 
 @dataclass
@@ -52,17 +76,33 @@ class Part:
         """Parts nested inside this one (their tensors are loaded too)."""
         return []
 
+    def reserve(self, limits: EngineLimits) -> None:
+        """Size whatever scratch memory this part's kernels take for steps within `limits`."""
+
 
 class ResidualStream:
     """The residual sum, float32 in both precisions, plus a sum not yet added.
 
     A mixer or feed-forward leaves its output as `pending`; the next norm adds
     it while it norms (one pass over the row instead of two), which is the
-    deferred add of fastllm_py/graph_decode.py:810-813."""
+    deferred add of fastllm_py/graph_decode.py:810-813.  The pending sum is a
+    tensor [N, hidden], or the split-K partial sums of the product that made it
+    (an object with `reduce_into(tensor)`): a norm that says `takes_partial`
+    adds the slabs while it reads, any other gets them added up first, into the
+    buffer that `spill()` returns."""
 
-    def __init__(self, x: torch.Tensor):
+    def __init__(self, x: torch.Tensor, spill=None):
         self.x = x
         self.pending = None
+        self.spill = spill
+
+    def norm_into(self, norm, out, rows=None):
+        """`norm.apply(self, out, rows)`, with a pending sum that the norm can take."""
+        pending = self.pending
+        if pending is not None and not isinstance(pending, torch.Tensor):
+            if rows is not None or not getattr(norm, "takes_partial", False):
+                self.pending = pending.reduce_into(self.spill())
+        norm.apply(self, out, rows)
 
 
 class Workspace:
@@ -76,6 +116,7 @@ class Workspace:
         self.device = device
         self.max_tokens = max_tokens
         self._buffers: dict = {}
+        self.generation = 0              # bumped when a buffer is replaced by a larger one
 
     def rows(self, name: str, n: int, cols: int, dtype, initial: int | None = None) -> torch.Tensor:
         """`initial` (for buffers that are wide but usually short, like logits)
@@ -92,6 +133,7 @@ class Workspace:
             cap = self.max_tokens if initial is None else min(self.max_tokens, max(initial, n))
             if buf is not None:
                 cap = min(self.max_tokens, max(n, 2 * buf.shape[0]))
+                self.generation += 1     # captured graphs may hold the old buffer's address
             buf = torch.zeros((cap, pitch), dtype=dtype, device=self.device)
             self._buffers[key] = buf
         return buf[:n, :cols]

@@ -33,9 +33,9 @@ class PreNormBlock(Part):
         delta = step.workspace.rows("delta", n, self.hidden, dt)
         # a mixer or feed-forward returns None when it wrote `delta`, or the
         # split-K partial sums of its last product, which the next norm adds up
-        self.norm_mixer.apply(stream, h)
+        stream.norm_into(self.norm_mixer, h)
         left = self.mixer.forward(h, delta, step, cache)
         stream.pending = delta if left is None else left
-        self.norm_ff.apply(stream, h)
+        stream.norm_into(self.norm_ff, h)
         left = self.feed_forward.forward(h, delta, step)
         stream.pending = delta if left is None else left

@@ -103,22 +103,57 @@ class Decoder:
             safe = self._graph_safe = all(getattr(p, "graph_safe", True) for p in self.all_parts())
         return safe
 
+    def _mixers_with(self, hook: str) -> list:
+        """The mixers that have `hook`, one per `plan_key` (mixers of equal keys decide alike)."""
+        cache = self.__dict__.setdefault("_hooked", {})
+        if hook not in cache:
+            found, seen = [], set()
+            for block in self.blocks:
+                mixer = block.mixer
+                if not hasattr(mixer, hook):
+                    continue
+                key = getattr(mixer, "plan_key", None) or id(mixer)
+                if key not in seen:
+                    seen.add(key)
+                    found.append(mixer)
+            cache[hook] = found
+        return cache[hook]
+
+    def plan_step(self, step) -> None:
+        """Before a step is launched: every mixer that decides something on the host for it
+        (how to split the keys of a decode kernel, say) does so now and keeps it in `step.plans`."""
+        for mixer in self._mixers_with("plan_step"):
+            mixer.plan_step(step)
+
     def graph_key(self, step):
         """What, beside the number of tokens, fixes the launch shapes of a
         decode-only step: each mixer may add its own (a bucket of the longest
         sequence, say).  Steps with equal keys may replay one captured graph."""
-        key = []
-        for block in self.blocks:
-            fn = getattr(block.mixer, "graph_key", None)
-            key.append(fn(step) if fn is not None else None)
-        return tuple(key)
+        return tuple(mixer.graph_key(step) for mixer in self._mixers_with("graph_key"))
+
+    @property
+    def takes_fed_tokens(self) -> bool:
+        """True when the embedding part can take a token from the sampler's output on the device."""
+        return bool(getattr(self.embedding, "takes_fed_tokens", False))
+
+    def reserve(self, limits, workspace) -> None:
+        """Called once when an engine is built: every part sizes its scratch memory, and the
+        buffers whose size follows the requests rather than the tokens get their steady size."""
+        for part in self.all_parts():
+            fn = getattr(part, "reserve", None)
+            if fn is not None:
+                fn(limits)
+        rows = min(limits.max_tokens, limits.max_requests)
+        workspace.rows("logits", rows, self.vocab, torch.float32, initial=rows)
+        workspace.rows("picked", rows, self.hidden, self.ctx.dtype, initial=rows)
 
     # ------------------------------------------------------------------- pass
     def forward(self, step) -> torch.Tensor:
         """Logits [wanted rows, vocab] in float32 for the step's tokens."""
         n = step.n_tokens
         ws = step.workspace
-        stream = ResidualStream(ws.rows("residual", n, self.hidden, torch.float32))
+        stream = ResidualStream(ws.rows("residual", n, self.hidden, torch.float32),
+                                spill=lambda: ws.rows("delta", n, self.hidden, self.ctx.dtype))
         self.embedding.forward(step, stream.x)
         for i, run in enumerate(self.order):
             cache_id = i if run.cache is None else run.cache
@@ -128,10 +163,6 @@ class Decoder:
         if m > 0:
             picked = ws.rows("picked", m, self.hidden, self.ctx.dtype, initial=64)
             rows = None if step.rows_identity else step.logit_rows
-            if rows is not None and stream.pending is not None and \
-                    not isinstance(stream.pending, torch.Tensor):
-                # partial sums cannot be gathered by row: fold them into the stream first
-                self.final_norm.apply(stream, ws.rows("normed", n, self.hidden, self.ctx.dtype))
-            self.final_norm.apply(stream, picked, rows=rows)
+            stream.norm_into(self.final_norm, picked, rows=rows)
             self.head.forward(picked, logits)
         return logits

@@ -16,6 +16,7 @@ from .registry import register_part
 class Embedding(Part):
     """params: vocab_size, hidden_size.  tensors: weight [vocab, hidden]."""
     category = "embedding"
+    takes_fed_tokens = True              # an id -1 - r is taken from row r of step.token_feed
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
@@ -49,6 +50,10 @@ class LinearHead(Part):
 
     def load(self, tensors):
         self.linear = Linear.sharing(tensors["weight"])
+
+    def reserve(self, limits):
+        if self.linear is not None:
+            self.linear.reserve(self.ctx.dtype, min(limits.max_tokens, limits.max_requests))
 
     def forward(self, h, out):
         self.linear.forward(h, out)

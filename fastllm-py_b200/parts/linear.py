@@ -39,20 +39,28 @@ class Linear:
         as split-K partial sums and return them (a `gemm_tc.Partial`) for a
         consumer that adds them as it reads: `out` is then not written."""
         if a.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16:
-            from .. import native
-            if native.tensor_core_gemm_enabled():
-                if self._tc is None:
-                    self._tc = native.gemm_tc.TensorCoreLinear(self.weight)
-                return self._tc.forward(a, out, defer)
+            return self._tensor_core().forward(a, out, defer)
         ops.gemm_simt(a, self.weight, out)
         return None
+
+    def _tensor_core(self):
+        if self._tc is None:
+            from ..native.gemm_tc import TensorCoreLinear
+            self._tc = TensorCoreLinear(self.weight)
+        return self._tc
+
+    def reserve(self, activation_dtype, max_tokens: int) -> None:
+        """Size the scratch memory that products of up to `max_tokens` rows will take, so that
+        nothing has to grow (and no captured graph goes stale) once the engine runs."""
+        if activation_dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16:
+            from ..native import gemm_tc
+            gemm_tc.reserve(self.weight.device, self.out_features, self.in_features, max_tokens)
 
     def forward_gated(self, a: torch.Tensor, out: torch.Tensor) -> bool:
         """For a Linear that stacks a gate and an up matrix: out = silu(a gate^T) * (a up^T)
         in one tensor-core kernel.  False (nothing done) when that kernel does not apply; the
         caller then takes `forward` and the activation kernel."""
         if a.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and self.weight.is_contiguous():
-            from .. import native
-            if native.tensor_core_gemm_enabled():
-                return native.gemm_tc.gemm_swiglu(a, self.weight, out)
+            from ..native.gemm_tc import gemm_swiglu
+            return gemm_swiglu(a, self.weight, out)
         return False

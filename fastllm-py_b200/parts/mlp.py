@@ -33,6 +33,11 @@ class SwiGLU(Part):
         self.gate_up = Linear([tensors["gate"], tensors["up"]])
         self.down = Linear([tensors["down"]])
 
+    def reserve(self, limits):
+        for lin in (self.gate_up, self.down):
+            if lin is not None:
+                lin.reserve(self.ctx.dtype, limits.max_tokens)
+
     def forward(self, h, out, step):
         n = h.shape[0]
         dt = self.ctx.dtype

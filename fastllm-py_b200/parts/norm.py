@@ -14,6 +14,7 @@ from .registry import register_part
 class RMSNorm(Part):
     """params: size, eps.  tensors: weight [size]."""
     category = "norm"
+    takes_partial = True                 # split-K partial sums are added while the row is read
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
@@ -29,7 +30,8 @@ class RMSNorm(Part):
 
     def apply(self, stream, out, rows=None):
         """Norm the residual stream into `out`, adding the pending sum first.
-        With `rows` (int32 indices) only those rows are normed, into out[0..m)."""
+        With `rows` (int32 indices) only those rows are normed, into out[0..m), and the
+        pending sum (a tensor then: `ResidualStream.norm_into` sees to it) stays pending."""
         if stream.pending is not None:
             if not isinstance(stream.pending, torch.Tensor):         # split-K partial sums
                 if rows is not None:

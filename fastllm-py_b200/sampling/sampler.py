@@ -79,7 +79,23 @@ class Sampler:
         # two host buffers: a launch may follow before the one before it was collected
         self.out_host = [torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
         self._launches = 0
-        self._params_uploaded = None                     # event: the staging area may be rewritten after it
+        self._params_uploaded = None                     # event: the staging areas may be rewritten after it
+        # penalties: (row, token, count) triples of the tokens produced so far, staged like the rest
+        self._pen_cap = 0
+        self._pen_host = self._pen_dev = None
+        self._grow_penalties(4096)
+
+    def _grow_penalties(self, triples: int) -> None:
+        """Room for `triples` (row, token, count) entries in pinned and in device memory; an upload
+        still under way from the old staging area is waited for before it is let go."""
+        if triples <= self._pen_cap:
+            return
+        if self._params_uploaded is not None:
+            self._params_uploaded.synchronize()
+        cap = max(triples, 2 * self._pen_cap)
+        self._pen_host = torch.zeros((3, cap), dtype=torch.int32, pin_memory=torch.cuda.is_available())
+        self._pen_dev = torch.zeros((3, cap), dtype=torch.int32, device=self.device)
+        self._pen_cap = cap
 
     def _host(self, name):
         off, dt = self.offsets[name]
@@ -123,15 +139,22 @@ class Sampler:
                 tp[i], mp[i], tk[i] = p.top_p, p.min_p, p.top_k
                 rep[i], fr[i], pr[i] = p.repetition_penalty, p.frequency_penalty, p.presence_penalty
             self.dev.copy_(self.host, non_blocking=True)
+            n_pen = 0
+            if any_penalty:
+                items = [(i, tok, cnt) for i, s in enumerate(states) if s.params.penalized
+                         for tok, cnt in s.counts.items()]
+                n_pen = len(items)
+                self._grow_penalties(n_pen)
+                self._pen_host.numpy()[:, :n_pen] = np.asarray(items, dtype=np.int32).T
+                self._pen_dev[:, :n_pen].copy_(self._pen_host[:, :n_pen], non_blocking=True)
             if self._params_uploaded is None:
                 self._params_uploaded = torch.cuda.Event()
             self._params_uploaded.record()
-        if any_penalty:
-            items = [(i, tok, cnt) for i, s in enumerate(states) if s.params.penalized
-                     for tok, cnt in s.counts.items()]
-            arr = torch.tensor(items, dtype=torch.int32).t().contiguous().to(self.device)
-            ops.apply_penalties(logits, arr[0], arr[1], arr[2], self._dev("repetition", m),
-                                self._dev("frequency", m), self._dev("presence", m))
+            if any_penalty:
+                pen = self._pen_dev
+                ops.apply_penalties(logits, pen[0, :n_pen], pen[1, :n_pen], pen[2, :n_pen],
+                                    self._dev("repetition", m), self._dev("frequency", m),
+                                    self._dev("presence", m))
         out = self.out[:m]
         if any_random:
             ops.sample(logits, out, self._dev("temperature", m), self._dev("top_k", m),

@@ -208,7 +208,7 @@ def test_decodes_run_beside_a_prompt_portion():
     s.step()
     assert eng.steps[2] == [(a, 1, [0]), (b, 5, [4])]
     s.run()
-    assert len(s.requests[a].output) == 4 and len(s.requests[b].output) == 2
+    assert len(s.request(a).output) == 4 and len(s.request(b).output) == 2
 
 
 def test_stop_token_is_emitted_and_ends_the_request():
@@ -216,7 +216,7 @@ def test_stop_token_is_emitted_and_ends_the_request():
     s = Scheduler(eng, ArgmaxSampler())
     rid = s.add_request([7, 7, 7], max_new_tokens=10, stop_ids=[5])
     out = s.run()
-    assert out[rid] == [3, 4, 5] and s.requests[rid].finish_reason == "stop"
+    assert out[rid] == [3, 4, 5] and s.request(rid).finish_reason == "stop"
 
 
 def test_requests_that_can_never_fit_are_refused():
@@ -237,7 +237,7 @@ def test_admission_waits_for_slots_and_pages():
     s.step()
     assert [r.request_id for r in s.running] == ids[:2] and len(s.waiting) == 1   # two slots only
     s.run()
-    assert all(len(s.requests[i].output) == 2 for i in ids)
+    assert all(len(s.request(i).output) == 2 for i in ids)
     assert eng.cache.groups[0].pool.free_pages == 6
 
 
@@ -272,7 +272,7 @@ def test_pages_run_out_last_admitted_is_pushed_out_and_recomputed():
     b = s.add_request([2] * 7, max_new_tokens=8)
     out = s.run()
     assert s.stats["pushed_out"] >= 1
-    assert s.requests[b].times_pushed_out >= 1 and s.requests[a].times_pushed_out == 0
+    assert s.request(b).times_pushed_out >= 1 and s.request(a).times_pushed_out == 0
     # outputs are what an undisturbed run gives: token = tokens held after the step
     assert out[a] == list(range(7, 15)) and out[b] == list(range(7, 15))
     # b's comeback recomputed prompt + produced tokens as one prompt
@@ -296,7 +296,7 @@ def test_no_admission_while_a_request_was_pushed_out():
             seen_push = True
             admitted = {r.request_id for r in s.running} - running_before
             assert not admitted, "a request was admitted in a step that pushed one out"
-    assert seen_push and len(s.requests[c].output) == 1
+    assert seen_push and len(s.request(c).output) == 1
 
 
 @pytest.mark.parametrize("seed", range(4))
@@ -330,6 +330,7 @@ class FeedingEngine(StandInEngine):
     def __init__(self, *a, **k):
         super().__init__(*a, **k)
         self.token_feed = None
+        self.accepts_fed_tokens = True                 # what an engine says whose embedding takes device tokens
         self.fed = {}                                  # request -> running sum of the tokens fed
 
     def step(self, entries):
@@ -391,7 +392,7 @@ def _run_both(add_requests, late=None, **engine_opts):
             if late is not None and steps == late[0]:
                 ids.append(late[1](s))
         assert not eng.cache.live and eng.cache.groups[0].pool.free_pages == engine_opts["pages"]
-        outs.append(([s.requests[i].output for i in ids], dict(s.stats), eng.steps))
+        outs.append(([s.request(i).output for i in ids], dict(s.stats), eng.steps))
     return outs
 
 

@@ -294,7 +294,7 @@ def test_running_ahead_changes_no_token(dtype, model_folders):
             steps += 1
             if steps == 24:                                # a late arrival breaks the steady state
                 ids.append(sched.add_request(prompts[4], lengths[4], params[4]))
-        return [sched.requests[i].output for i in ids], dict(sched.stats)
+        return [sched.request(i).output for i in ids], dict(sched.stats)
 
     free = run(False)[0][3]                                # the sampled request, run to its length
     at = next(k for k in range(8, 22) if free.index(free[k]) == k)
