@@ -48,16 +48,7 @@ def test_greedy_generation_bfloat16(model_folders):
     weights, config = plain.load_folder(model_folders[name])
     model = model_for(name, model_folders[name], "bfloat16")
     for prompt in prompts_of(name, [9, 40]):
-        got = model.generate(prompt, max_new_tokens=12)
-        ids = list(prompt)
-        for tok in got:
-            row = plain.forward(weights, config, ids, store=plain.store_bf16)[-1]
-            best = int(row.argmax())
-            if tok != best:
-                exact = plain.forward(weights, config, ids)[-1]
-                spread = float((row - exact).abs().max())
-                assert float(row[best] - row[tok]) <= 2 * spread + 1e-3
-            ids.append(tok)
+        near_tie_follows(weights, config, prompt, model.generate(prompt, max_new_tokens=12))
 
 
 def test_batch_of_prompts_equals_single_requests(model_folders):
@@ -107,6 +98,148 @@ def test_page_pressure_changes_no_output(model_folders):
     assert [out[i] for i in ids] == want
     tight.engine.cache.check()
     assert not tight.engine.cache.live
+
+
+def near_tie_follows(weights, config, prompt, got):
+    """bfloat16 greedy tokens follow the plain bfloat16-storage model; where the two part ways
+    the plain model's two best logits must be nearly tied (within twice the storage noise)."""
+    ids = list(prompt)
+    for tok in got:
+        row = plain.forward(weights, config, ids, store=plain.store_bf16)[-1]
+        best = int(row.argmax())
+        if tok != best:
+            exact = plain.forward(weights, config, ids)[-1]
+            spread = float((row - exact).abs().max())
+            assert float(row[best] - row[tok]) <= 2 * spread + 1e-3
+        ids.append(tok)
+
+
+# The two schedules that the tiny configurations are specified with, through the scheduler on
+# the GPU, against the plain implementation request by request.
+SCHEDULES = {"tiny_a": dict(lengths=[5, 17, 33], budget=7, new=16),
+             "tiny_b": dict(lengths=[1, 9, 40, 64, 100], budget=13, new=24)}
+
+
+@pytest.mark.parametrize("name", list(SCHEDULES))
+def test_prompts_together_in_portions_beside_decoding_float32(name, model_folders):
+    """All prompts at once under a small token budget (portions of 13, or 7, beside the decode
+    steps of the requests that are already through), greedy and at temperature 0.7 with a seed
+    per request: the ids equal the plain implementation's, which generates one request at a time."""
+    from fastllm_py_b200.sampling import SamplingParams
+
+    sch = SCHEDULES[name]
+    weights, config = plain.load_folder(model_folders[name])
+    model = model_for(name, model_folders[name], "float32")
+    prompts = prompts_of(name, sch["lengths"], seed=21)
+    for temperature in (0.0, 0.7):
+        sched = model.scheduler(token_budget=sch["budget"])
+        ids = [sched.add_request(p, sch["new"], SamplingParams(temperature=temperature, seed=100 + i))
+               for i, p in enumerate(prompts)]
+        out = sched.run()
+        assert sched.stats["prefill_tokens"] == sum(sch["lengths"])
+        assert sched.stats["steps"] > sum(sch["lengths"]) // sch["budget"]
+        for i, (rid, p) in enumerate(zip(ids, prompts)):
+            want = plain.generate(weights, config, p, sch["new"], temperature=temperature, seed=100 + i)
+            assert out[rid] == want, f"{name} T={temperature} request {i}"
+    model.engine.cache.check()
+    assert not model.engine.cache.live
+
+
+def test_prompts_together_in_portions_beside_decoding_bfloat16(model_folders):
+    name = "tiny_b"
+    sch = SCHEDULES[name]
+    weights, config = plain.load_folder(model_folders[name])
+    model = model_for(name, model_folders[name], "bfloat16")
+    prompts = prompts_of(name, sch["lengths"], seed=21)
+    sched = model.scheduler(token_budget=sch["budget"])
+    ids = [sched.add_request(p, sch["new"]) for p in prompts]
+    out = sched.run()
+    for rid, p in zip(ids, prompts):
+        assert len(out[rid]) == sch["new"]
+        near_tie_follows(weights, config, p, out[rid])
+
+
+def test_page_pressure_changes_no_output_bfloat16(model_folders):
+    """Push-out and recompute with everything on that serving has on: bfloat16 kernels, graph
+    replay, decode steps launched ahead of the host.  Recomputing a pushed-out request runs its
+    prompt and its produced tokens as one prompt, through other kernels than decoding them did,
+    so a token may differ where the model's two best are nearly tied; anything else is equal."""
+    name = "tiny_a"
+    weights, config = plain.load_folder(model_folders[name])
+    roomy = model_for(name, model_folders[name], "bfloat16")
+    tight = model_for(name, model_folders[name], "bfloat16", max_tokens=112, max_requests=4)
+    prompts = prompts_of(name, [30, 28, 33, 25], seed=8)
+    want = [roomy.generate(p, max_new_tokens=40) for p in prompts]
+    sched = tight.scheduler()
+    assert sched.run_ahead and tight.engine.use_graph
+    ids = [sched.add_request(p, 40) for p in prompts]
+    out = sched.run()
+    assert sched.stats["pushed_out"] >= 1
+    for rid, p, w in zip(ids, prompts, want):
+        assert len(out[rid]) == 40
+        if out[rid] != w:
+            near_tie_follows(weights, config, p, out[rid])
+    tight.engine.cache.check()
+    assert not tight.engine.cache.live
+
+
+def test_command_line_generates_the_plain_tokens(model_folders):
+    """bin/generate as a user runs it: MODEL PROMPT N DTYPE in fastllm-py's order
+    (scripts/generate.py:16-19), the prompt given as token ids."""
+    import subprocess
+    import sys
+
+    name = "tiny_b"
+    weights, config = plain.load_folder(model_folders[name])
+    prompt = prompts_of(name, [11], seed=33)[0]
+    want = plain.generate(weights, config, prompt, 16)
+    cmd = [sys.executable, str(tiny.ROOT / "bin" / "generate"), str(model_folders[name]), "-", "16", "float32",
+           "--prompt-ids", ",".join(map(str, prompt)), "--page-size", "8", "--max-tokens", "256"]
+    done = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    lines = [ln for ln in done.stdout.splitlines() if ln.strip()]
+    assert lines[0].startswith("[load ") and "3L hidden=96 heads=6/2 dtype=float32" in lines[0]
+    assert [int(t) for t in lines[1].split(",")] == want
+    assert lines[-1].startswith("[16 tokens in ") and lines[-1].endswith("tok/s]")
+    # temperature with a seed, as the plain implementation draws
+    want = plain.generate(weights, config, prompt, 12, temperature=0.7, seed=5)
+    done = subprocess.run(cmd[:4] + ["12", "float32"] + cmd[6:] + ["--temperature", "0.7", "--seed", "5"],
+                          capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    lines = [ln for ln in done.stdout.splitlines() if ln.strip()]
+    assert [int(t) for t in lines[1].split(",")] == want
+
+
+def test_graphs_captured_before_a_scratch_buffer_grew_are_not_replayed(model_folders):
+    """A small engine captures its decode step; then a larger engine of the same process makes
+    the shared scratch buffers grow; the small engine's next steps must not replay graphs that
+    point to the old buffers: it drops them, captures anew, and produces the same tokens as eager."""
+    from fastllm_py_b200 import Model
+    from fastllm_py_b200.native import scratch
+
+    name = "tiny_c"
+    prompts = prompts_of(name, [9, 40, 21], seed=2)
+    page = tiny.CONFIGS[name]["page_size"]
+    small = Model.load(model_folders[name], dtype="bfloat16", page_size=page, max_tokens=1024, max_requests=4,
+                       max_batched_tokens=64, max_model_len=256)
+    eager = small.generate(prompts, max_new_tokens=20, use_graph=False)
+    assert small.generate(prompts, max_new_tokens=20) == eager
+    assert len(small.engine._graphs) >= 1
+    before = scratch.generation(small.engine.device)
+    # ask for more than any engine so far has reserved
+    dev = small.engine.device
+    from fastllm_py_b200.native import attention, gemm_tc
+    scratch.get(dev, gemm_tc.SCRATCH, scratch.size(dev, gemm_tc.SCRATCH) + 1)
+    scratch.get(dev, attention.SCRATCH, scratch.size(dev, attention.SCRATCH) + 1)
+    assert scratch.generation(dev) == before + 2
+    assert small.generate(prompts, max_new_tokens=20) == eager
+    assert small.engine.graphs_dropped >= 1 and len(small.engine._graphs) >= 1
+    # small batch, large batch, small batch through one engine
+    many = prompts_of(name, [5] * 4, seed=3)
+    want_many = small.generate(many, max_new_tokens=8, use_graph=False)
+    assert small.generate(prompts[:1], max_new_tokens=20) == eager[:1]
+    assert small.generate(many, max_new_tokens=8) == want_many
+    assert small.generate(prompts[:1], max_new_tokens=20) == eager[:1]
 
 
 def test_graph_replay_equals_eager_bit_for_bit(model_folders):

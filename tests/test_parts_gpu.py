@@ -539,3 +539,251 @@ def test_toy_position_encoding_and_routed_feed_forward(tmp_path):
         at += n
     eng.end("r")
     eng.cache.check()
+
+
+# ---------- a third toy: a norm that knows nothing of partial sums, a paged mixer with one vector
+# ---------- per token, an embedding that takes no tokens from the device
+
+@dataclass(frozen=True)
+class Toy3Config:
+    hidden_size: int = 64
+    vocab_size: int = 101
+    latent: int = 24
+    intermediate_size: int = 520          # wide enough that the down product's K is split into partial sums
+    num_heads: int = 2
+    head_dim: int = 32
+    eps: float = 1e-5
+
+    @classmethod
+    def from_hf(cls, raw):
+        return cls(**{k: raw[k] for k in cls.__dataclass_fields__})
+
+    def to_hf(self):
+        return dict(architectures=["Toy3ForCausalLM"], **self.__dict__)
+
+
+def register_toy3():
+    from fastllm_py_b200.cache import PagedNeed
+    from fastllm_py_b200.config import register_architecture
+    from fastllm_py_b200.parts import LayerRun, LayerSpec, ModelPlan, Part, PartSpec, register_part
+    from fastllm_py_b200.parts.linear import Linear
+
+    @dataclass(frozen=True)
+    class PagedVector(PagedNeed):
+        """One vector of `dim` values per token: a page is [page_size, dim]."""
+        dim: int
+        window: int | None = None
+
+        def page_shape(self, page_size):
+            return (page_size, self.dim)
+
+    @register_part("norm", "toy_centered_plus_one")
+    class CenteredPlusOne(Part):
+        """(x - mean) / sqrt(var + eps) * (1 + w): centred, and the weight is an offset from one.
+        It does not declare `takes_partial`, so the pending sum always reaches it as a tensor."""
+        category = "norm"
+
+        def __init__(self, spec, ctx):
+            super().__init__(spec, ctx)
+            self.size, self.eps = int(spec.params["size"]), float(spec.params["eps"])
+
+        def weight_shapes(self):
+            return {"weight": (self.size,)}
+
+        def load(self, tensors):
+            self.weight = tensors["weight"].float()
+
+        def apply(self, stream, out, rows=None):
+            assert stream.pending is None or isinstance(stream.pending, torch.Tensor)
+            x = stream.x
+            if stream.pending is not None and rows is None:
+                x += stream.pending.float()
+                stream.pending = None
+            elif stream.pending is not None:
+                x = x[rows.long()] + stream.pending[rows.long()].float()
+            elif rows is not None:
+                x = x[rows.long()]
+            c = x - x.mean(dim=1, keepdim=True)
+            y = c * torch.rsqrt(c.pow(2).mean(dim=1, keepdim=True) + self.eps) * (1.0 + self.weight)
+            out.copy_(y.to(out.dtype))
+
+    @register_part("mixer", "toy_latent_mean")
+    class LatentMean(Part):
+        """c_t = Wc h_t is kept per token in pages of [page_size, latent]; out_t = Wo mean(c_0 .. c_t)."""
+        category = "mixer"
+        graph_safe = False
+
+        def __init__(self, spec, ctx):
+            super().__init__(spec, ctx)
+            self.hidden, self.latent = spec.params["hidden_size"], spec.params["latent"]
+
+        def cache_need(self):
+            return PagedVector(self.latent)
+
+        def weight_shapes(self):
+            return {"c": (self.latent, self.hidden), "o": (self.hidden, self.latent)}
+
+        def load(self, tensors):
+            self.wc, self.wo = Linear([tensors["c"]]), Linear([tensors["o"]])
+
+        def forward(self, h, out, step, cache):
+            n, ps = h.shape[0], cache.page_size
+            assert tuple(cache.tensor.shape[1:]) == (ps, self.latent)
+            c = torch.empty(n, self.latent, dtype=h.dtype, device=h.device)
+            self.wc.forward(h, c)
+            flat = cache.tensor.view(-1, self.latent)
+            flat[cache.slots.long()] = c
+            means = torch.empty_like(c)
+            at = 0
+            for r, (q, ctx_len) in enumerate(zip(step.q_lens, step.ctx_lens)):
+                pos = torch.arange(ctx_len + q, device=h.device)
+                pages = cache.block_table[r, pos // ps].long()
+                seen = flat[pages * ps + pos % ps].float()
+                mean = torch.cumsum(seen, 0)[ctx_len:] / torch.arange(ctx_len + 1, ctx_len + q + 1, device=h.device)[:, None]
+                means[at:at + q] = mean.to(h.dtype)
+                at += q
+            self.wo.forward(means, out)
+
+    @register_part("embedding", "toy_scaled_table")
+    class ScaledTable(Part):
+        """x = table[id] * sqrt(hidden); takes host-known ids only (no `takes_fed_tokens`)."""
+        category = "embedding"
+
+        def __init__(self, spec, ctx):
+            super().__init__(spec, ctx)
+            self.hidden = int(spec.params["hidden_size"])
+
+        def weight_shapes(self):
+            return {"weight": (int(self.spec.params["vocab_size"]), self.hidden)}
+
+        def load(self, tensors):
+            self.table = tensors["weight"]
+
+        def forward(self, step, out):
+            assert int(step.token_ids.min()) >= 0, "a token id that stands for a device token reached this part"
+            out.copy_(self.table[step.token_ids.long()].float() * self.hidden ** 0.5)
+
+    def make_plan(cfg, names=None):
+        def norm(n):
+            return PartSpec("toy_centered_plus_one", dict(size=cfg.hidden_size, eps=cfg.eps), {"weight": n})
+
+        def ffn(i):
+            return PartSpec("swiglu", dict(hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size),
+                            {s: f"l{i}.ffn.{s}" for s in ("gate", "up", "down")})
+
+        mixers = [PartSpec("toy_latent_mean", dict(hidden_size=cfg.hidden_size, latent=cfg.latent),
+                           {"c": "l0.c", "o": "l0.o"}),
+                  PartSpec("attention", dict(hidden_size=cfg.hidden_size, num_heads=cfg.num_heads,
+                                             num_kv_heads=cfg.num_heads, head_dim=cfg.head_dim, window=None,
+                                             position=PartSpec("rotary", dict(rot_dim=cfg.head_dim, theta=10000.0,
+                                                                              scaling=None))),
+                           {s: f"l1.{s}" for s in ("q", "k", "v", "o")})]
+        layers = [LayerSpec("prenorm", m, ffn(i), {"mixer": norm(f"l{i}.n1"), "feed_forward": norm(f"l{i}.n2")})
+                  for i, m in enumerate(mixers)]
+        io = dict(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size)
+        return ModelPlan(cfg.hidden_size, cfg.vocab_size, 256, PartSpec("toy_scaled_table", io, {"weight": "emb"}),
+                         layers, [LayerRun(0), LayerRun(1)], norm("final"), PartSpec("linear", io, {"weight": "head"}))
+
+    register_architecture("Toy3ForCausalLM", Toy3Config, make_plan)
+    return PagedVector
+
+
+def toy3_plain(w, cfg, ids, store):
+    T, H, D = len(ids), cfg.num_heads, cfg.head_dim
+
+    def norm(x, weight):
+        c = x - x.mean(dim=1, keepdim=True)
+        return c * torch.rsqrt(c.pow(2).mean(dim=1, keepdim=True) + cfg.eps) * (1.0 + weight)
+
+    x = plain.embedding(w["emb"], torch.as_tensor(ids)) * cfg.hidden_size ** 0.5
+    cos, sin = plain.rope_tables(torch.arange(T), D, 10000.0)
+    for i in range(2):
+        p = f"l{i}."
+        h = store(norm(x, w[p + "n1"]))
+        if i == 0:
+            c = store(plain.linear(h, w[p + "c"]))
+            mean = store(torch.cumsum(c, 0) / torch.arange(1, T + 1)[:, None])
+            delta = store(plain.linear(mean, w[p + "o"]))
+        else:
+            q = store(plain.apply_rope(store(plain.linear(h, w[p + "q"])).reshape(T, H, D), cos, sin))
+            k = store(plain.apply_rope(store(plain.linear(h, w[p + "k"])).reshape(T, H, D), cos, sin))
+            v = store(plain.linear(h, w[p + "v"])).reshape(T, H, D)
+            delta = store(plain.linear(store(plain.attention(q, k, v)), w[p + "o"]))
+        x = x + delta
+        h = store(norm(x, w[p + "n2"]))
+        a = store(plain.swiglu(store(plain.linear(h, w[p + "ffn.gate"])), store(plain.linear(h, w[p + "ffn.up"]))))
+        x = x + store(plain.linear(a, w[p + "ffn.down"]))
+    return plain.linear(store(norm(x, w["final"])), w["head"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_norm_paged_vector_mixer_and_plain_embedding(dtype, tmp_path):
+    """Registered from here without touching the package: a norm of another kind that has never
+    heard of split-K partial sums (the stream hands it tensors), a mixer whose pages hold one
+    vector per token (the need states the page shape, the manager allocates and recycles it),
+    and an embedding that cannot take tokens from the device (the scheduler then never runs
+    ahead of the host); stepped in portions beside single tokens with pages used again, with
+    the cache's check mode on, and generated from through the scheduler."""
+    from safetensors.torch import load_file
+
+    from fastllm_py_b200 import Model, StepEntry
+    from fastllm_py_b200.native import gemm_tc
+    from fastllm_py_b200.weights import write_model_folder
+
+    PagedVector = register_toy3()
+    cfg = Toy3Config()
+    folder = write_model_folder(cfg, tmp_path / "toy3", seed=13, std=0.08, norm_std=0.1)
+    model = Model.load(folder, dtype=dtype, page_size=4, max_tokens=96, max_requests=3, max_batched_tokens=64,
+                       max_model_len=96, check_cache=True)
+    eng = model.engine
+    assert [type(g.need).__name__ for g in eng.cache.groups] == ["PagedVector", "PagedKV"]
+    assert tuple(eng.cache.groups[0].tensors[0].shape) == (24, 4, cfg.latent)
+    assert not eng.accepts_fed_tokens and not model.scheduler().run_ahead
+    if dtype == "bfloat16":                                  # the down product does leave partial sums here
+        assert gemm_tc.plan(5, cfg.hidden_size, cfg.intermediate_size, 148)[1] > 1
+    weights = {k: v.float() for k, v in load_file(str(folder / "model.safetensors")).items()}
+    store = plain.store_bf16 if dtype == "bfloat16" else plain.identity
+    rng = np.random.default_rng(6)
+    seqs = {r: rng.integers(0, cfg.vocab_size, n).tolist() for r, n in (("a", 41), ("b", 30), ("c", 37))}
+    want = {r: toy3_plain(weights, cfg, ids, store) for r, ids in seqs.items()}
+    exact = {r: toy3_plain(weights, cfg, ids, plain.identity) for r, ids in seqs.items()}
+    tol = 1e-4 * max(1.0, max(float(v.abs().max()) for v in exact.values())) if dtype == "float32" else \
+        2 * max(float((want[r] - exact[r]).abs().max()) for r in seqs) + 1e-3
+    fed = {r: 0 for r in seqs}
+
+    def run(batch, want_last_only=False):
+        entries = [StepEntry(r, seqs[r][fed[r]:fed[r] + n], [n - 1] if want_last_only else list(range(n)))
+                   for r, n in batch]
+        logits = eng.step(entries).cpu()
+        row = 0
+        for r, n in batch:
+            places = [n - 1] if want_last_only else list(range(n))
+            for k in places:
+                diff = float((logits[row] - want[r][fed[r] + k]).abs().max())
+                assert diff <= tol, f"{r} token {fed[r] + k}: {diff:.3e} > {tol:.3e}"
+                row += 1
+            fed[r] += n
+
+    eng.begin("a")
+    eng.begin("b")
+    run([("a", 9)])
+    run([("b", 2), ("a", 1)])
+    run([("a", 17), ("b", 1)], want_last_only=True)          # gathered rows after partial sums
+    run([("b", 27), ("a", 1)])
+    eng.end("b")                                             # b's pages (both groups) go back, poisoned ...
+    eng.begin("c")
+    run([("c", 30), ("a", 1)])                               # ... and c takes them
+    run([("a", 12), ("c", 7)])
+    eng.end("a")
+    eng.end("c")
+    eng.check_status()
+    eng.cache.check()
+    assert eng.cache.pages_poisoned > 0
+    # generation through the scheduler (no run-ahead with this embedding): greedy follows the plain logits
+    prompt = seqs["a"][:7]
+    out = model.generate(prompt, max_new_tokens=5)
+    ids = list(prompt)
+    for tok in out:
+        row = toy3_plain(weights, cfg, ids, store)[-1]
+        assert tok == int(row.argmax()) or float(row.max() - row[tok]) <= tol
+        ids.append(tok)

@@ -63,9 +63,16 @@ def test_two_calls_match_the_ordinary_entry_point():
 
     fn = entry_point()
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    # (m, n, k, bn, splits, out dtype): the second problem is smaller than the first
+    # (m, n, k, bn, splits, out dtype): the second problem is smaller than the first; the third lets
+    # the library plan (bn = 0; a few tokens of a narrow product: it splits K); the fourth is the
+    # CTA-pair kernel (code 512: tiles of 256 tokens) with K split, which still fits the array
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert gemm_tc.plan(8, 256, 2048, sms)[1] > 1
+    assert 3 * 300 * 512 <= SCRATCH_FLOATS
     for seed, (m, n, k, bn, splits, dt) in enumerate([(48, 640, 1024, 64, 4, torch.float32),
-                                                       (5, 200, 520, 16, 3, torch.bfloat16)]):
+                                                       (5, 200, 520, 16, 3, torch.bfloat16),
+                                                       (8, 256, 2048, 0, 0, torch.bfloat16),
+                                                       (300, 512, 1600, 512, 3, torch.float32)]):
         a, w = problem(m, n, k, seed)
         got = torch.full((m, n), float("nan"), dtype=dt, device=DEV)
         rc, text = call(fn, a, w, got, bn, splits, status)
@@ -92,3 +99,7 @@ def test_a_problem_beyond_the_array_is_refused():
     assert rc == ERR_TOO_SMALL
     assert str(splits * m * n) in text and str(SCRATCH_FLOATS) in text
     assert bool(torch.all(out == 7.0)), "a refused call must not launch anything"
+    # a tile width without a split count is the caller's mistake, as it is for fl_gemm_tc
+    rc, _ = call(fn, a, w, out, 64, 0, status)
+    assert rc == 1                                       # cudaErrorInvalidValue
+    assert bool(torch.all(out == 7.0))
