@@ -17,8 +17,11 @@ prints ONE line of JSON:
              reads the token ids back (the scheduler launches a decode step
              before it has read the tokens of the one before; K steps by wall
              clock, the median of three such passes);
-  prefill    one 2048-token prompt in one step: tokens/s, ms and the fraction
-             of the bfloat16 tensor-core peak that its FLOPs / time reach;
+  prefill    one 2048-token prompt in one step, 20 runs: tokens/s, ms (median;
+             `ms_mean` beside it) and the fraction of the bfloat16 tensor-core
+             peak that its FLOPs / time reach, timed after the decode runs (the
+             GPU at its power cap, as a serving GPU is) and, as `*_before_decode`,
+             before them;
   roofline   the decode step against HBM: bytes it has to read (every weight
              once, the cache of the live requests) / time / peak bandwidth;
   points     decode tokens/s at batch 1 and 64.
@@ -60,6 +63,7 @@ MODEL_7B = dict(num_layers=30, hidden_size=4096, num_heads=32, num_kv_heads=32, 
                 max_position_embeddings=4096)
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
+PREFILL_REPEATS = 20
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -88,11 +92,24 @@ class ClockSampler:
     def __init__(self):
         self.samples = []
         self.proc = None
+        self.gpu = self._this_gpu()
+
+    @staticmethod
+    def _this_gpu() -> str:
+        """The id nvidia-smi knows the timed device by: its UUID (under CUDA_VISIBLE_DEVICES cuda:0
+        is usually not the machine's GPU 0, and the clocks of another user's GPU say nothing)."""
+        try:
+            import torch
+
+            uuid = str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
+            return uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        except Exception:                                    # noqa: BLE001  (no device: nothing to sample)
+            return "0"
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                ["nvidia-smi", "-i", self.gpu, f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                  "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -122,7 +139,7 @@ class ClockSampler:
         reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
         return {"sm_mhz": int(statistics.median(int(s[0]) for s in self.samples)),
                 "sm_max_mhz": int(self.samples[0][1]), "reasons": reasons,
-                "samples": len(self.samples)}
+                "samples": len(self.samples), "gpu": self.gpu}
 
 
 def decode_bytes(cfg, batch, mean_context):
@@ -227,10 +244,11 @@ def time_e2e(model, batch, steps, warmup, context):
     h2d = (buf.uploaded_bytes - bytes_before) // steps
     for r in list(sched.running):
         model.engine.end(r.request_id)
-    return produced / dt, h2d, 4 * batch
+    return produced / dt, h2d, 4 * batch + 4          # the token ids and the kernels' error word
 
 
 def time_prefill(model, tokens, repeats, warmup):
+    """(median, mean) milliseconds of one prompt step of `tokens` tokens over `repeats` runs."""
     import torch
 
     from fastllm_py_b200 import StepEntry
@@ -251,7 +269,7 @@ def time_prefill(model, tokens, repeats, warmup):
         if i >= warmup:
             times.append(start.elapsed_time(stop))
         engine.end(rid)
-    return statistics.median(times)
+    return statistics.median(times), statistics.fmean(times)
 
 
 MODEL_1B3 = dict(num_layers=24, hidden_size=2048, num_heads=16, num_kv_heads=16, head_dim=128,
@@ -386,7 +404,7 @@ def run_67b(args, warmup):
         nbytes = decode_bytes(cfg, b, context + warmup + (steps + 1) / 2)
         points[f"decode_b{b}"] = {"value": round(v, 2), "ms_per_step": round(ms, 3),
                                   "frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
-    pms = time_prefill(model, PREFILL_TOKENS, 3, 2)
+    pms, _ = time_prefill(model, PREFILL_TOKENS, 5, 2)
     flops = prefill_flops(cfg, PREFILL_TOKENS)
     line = {
         "metric": "decode tok/s @ batch 8, 4000-token context, deepseek-llm-67b size bf16",
@@ -456,6 +474,11 @@ def main():
     torch.cuda.synchronize()
     load_s = time.time() - t_load
 
+    flops = prefill_flops(cfg, PREFILL_TOKENS)
+    prefill_first = None
+    if not args.no_points:
+        # the prompt step once before the decode runs (the GPU has not yet reached its power cap) ...
+        prefill_first = time_prefill(model, PREFILL_TOKENS, PREFILL_REPEATS, 3)
     value, ms, launches, clocks = time_decode(model, args.batch, args.steps, warmup, CONTEXT, True)
     mean_ctx = CONTEXT + warmup + (args.steps + 1) / 2
     nbytes = decode_bytes(cfg, args.batch, mean_ctx)
@@ -485,11 +508,15 @@ def main():
                      "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
     }
     if not args.no_points:
-        pms = time_prefill(model, PREFILL_TOKENS, 5, 3)
-        flops = prefill_flops(cfg, PREFILL_TOKENS)
+        # ... and again after them, where a serving GPU sits: this is the figure reported as `ms`
+        pms, pmean = time_prefill(model, PREFILL_TOKENS, PREFILL_REPEATS, 3)
+        frac = lambda t: round(flops / (t * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
         line["prefill"] = {"value": round(PREFILL_TOKENS * 1000.0 / pms, 1), "tokens": PREFILL_TOKENS,
-                           "ms": round(pms, 3),
-                           "frac": round(flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+                           "ms": round(pms, 3), "frac": frac(pms), "ms_mean": round(pmean, 3),
+                           "repeats": PREFILL_REPEATS, "ms_before_decode": round(prefill_first[0], 3),
+                           "ms_mean_before_decode": round(prefill_first[1], 3),
+                           "frac_before_decode": frac(prefill_first[0]),
+                           "frac_of_sustained": round(flops / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)}
         points = {}
         for b in (1, 64):
             v, _, _, _ = time_decode(model, b, max(8, args.steps // 2), warmup, CONTEXT)

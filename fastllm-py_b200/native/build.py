@@ -136,6 +136,13 @@ def compile_library(name: str, defines: dict | None = None, verbose_ptxas: bool 
             pass
         raise NativeBuildError(f"nvcc failed for {source.name} ({' '.join(cmd)}):\n{log}")
     os.replace(tmp, out)           # atomic: a concurrent builder sees a whole file or none
+    tag = "".join(f"_{k}{v}" for k, v in sorted(defines.items()))
+    for old in out.parent.glob(f"{name}{tag}-*.so"):        # builds of earlier versions of this source
+        if old != out and len(old.name) == len(out.name):
+            try:
+                old.unlink()
+            except OSError:
+                pass
     if verbose_ptxas:
         _say(log)
     _say(f"built {out.name} in {time.time() - t0:.1f} s")

@@ -30,8 +30,9 @@ def harness(needs, dtype, page_size=8, max_tokens=256):
     from fastllm_py_b200.parts import BuildContext
 
     ctx = BuildContext(torch.device(DEV), dtype, page_size, 256)
-    decoder = types.SimpleNamespace(ctx=ctx, vocab=100, cache_needs=lambda: needs,
-                                    graph_key=lambda step: ())
+    decoder = types.SimpleNamespace(ctx=ctx, vocab=100, cache_needs=lambda: needs, graph_safe=True,
+                                    takes_fed_tokens=False, reserve=lambda limits, workspace: None,
+                                    plan_step=lambda step: None, graph_key=lambda step: ())
     cfg = EngineConfig(dtype="float32" if dtype == torch.float32 else "bfloat16", page_size=page_size,
                        max_tokens=max_tokens, max_requests=4, max_batched_tokens=128, cuda_graph=False)
     return Engine(decoder, cfg, 256, max_tokens // page_size), ctx
