@@ -425,6 +425,131 @@ def run_67b(args, warmup):
     return 0
 
 
+def reference_cpu_path(ref_root, layers=1, context=256, decode_tokens=8):
+    """fastllm-py's own NumPy model code (its CPU device, float32) timed at DeepSeek-LLM-7B layer
+    sizes: `layers` of the 30 layers, one sequence (that path has no batch), a `context`-token
+    prompt through Model.forward and `decode_tokens` greedy tokens one by one.  The package imports
+    CuPy inside its functions; a stand-in module that maps the few names it uses onto NumPy lets
+    the CPU path run where CuPy is absent (its GPU path cannot)."""
+    import tempfile
+    import types
+
+    import numpy as np
+
+    from fastllm_py_b200 import LlamaConfig
+    from fastllm_py_b200.weights import write_model_folder
+
+    if "cupy" not in sys.modules:
+        cp = types.ModuleType("cupy")
+        cp.ndarray = type("ndarray", (), {})
+        cp.asnumpy = lambda x: np.asarray(x)
+        cp.asarray = lambda x: np.asarray(x)
+        cp.float32, cp.float16 = np.float32, np.float16
+        sys.modules["cupy"] = cp
+    sys.path.insert(0, str(ref_root))
+    from fastllm_py import DeviceMap, Model
+
+    cfg = LlamaConfig(architecture="LlamaForCausalLM", rope_scaling=None, tie_word_embeddings=False,
+                      **dict(MODEL_7B, num_layers=layers))
+    with tempfile.TemporaryDirectory() as tmp:
+        folder = write_model_folder(cfg, Path(tmp) / "model", seed=0, std=0.02, norm_std=0.02)
+        model = Model.load(str(folder), DeviceMap({"cpu": 1}), dtype="float32")
+        ids = np.random.default_rng(7).integers(0, cfg.vocab_size, size=context).astype(np.int64)
+        t0 = time.perf_counter()
+        logits, kvs = model.forward(ids)
+        prefill_s = time.perf_counter() - t0
+        nxt = int(np.asarray(logits[-1]).argmax())
+        times = []
+        for _ in range(decode_tokens):
+            t0 = time.perf_counter()
+            logits, kvs = model.forward(np.asarray([nxt]), kvs)
+            nxt = int(np.asarray(logits[-1]).argmax())
+            times.append(time.perf_counter() - t0)
+    return {"device": "cpu (NumPy path of the reference, float32)", "layers": layers,
+            "layers_of_config": MODEL_7B["num_layers"], "batch": 1, "context": context,
+            "prefill_tok_s": round(context / prefill_s, 1),
+            "decode_tok_s": round(1.0 / statistics.median(times), 2)}
+
+
+def run_reference(args):
+    """The reference arm: codemk8/fastllm-py as installed under baseline/_ref, through its own API.
+    Its GPU path is CuPy (RawKernel, cuBLAS through cupy): it is tried whenever `import cupy` works;
+    where it does not, the line says so (and, with --reference-cpu, carries the timing of the
+    reference's CPU path at one layer of the same sizes, for scale: no ratio is meant by it)."""
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "fastllm_py").is_dir():
+        print(json.dumps({"impl": "reference", "unavailable": "fastllm-py is not installed under baseline/_ref "
+                          "(pip install --no-index --no-deps --target baseline/_ref of a copy of the reference)"}))
+        return 0
+    try:
+        import cupy  # noqa: F401
+        have_cupy = True
+    except Exception as e:                                   # noqa: BLE001
+        have_cupy, why = False, f"{type(e).__name__}: {e}"
+    if not have_cupy:
+        line = {"impl": "reference", "unavailable":
+                "fastllm-py's GPU path needs CuPy (cupy-cuda12x), which cannot be imported here "
+                f"({why}) and is not in the offline wheelhouse; the package itself installs with --no-deps"}
+        if args.reference_cpu:
+            try:
+                line["cpu_path"] = reference_cpu_path(ref_root)
+            except Exception as e:                           # noqa: BLE001
+                line["cpu_path"] = {"failed": f"{type(e).__name__}: {e}"}
+        print(json.dumps(line))
+        return 0
+    return run_reference_gpu(args, ref_root)
+
+
+def run_reference_gpu(args, ref_root):
+    """With CuPy at hand: the reference's own batched decoder (fastllm_py/batched.py:96-275) at the
+    headline shape in float16 (it has no bfloat16), random weights written to a model folder."""
+    import tempfile
+
+    import numpy as np
+
+    from fastllm_py_b200 import LlamaConfig
+    from fastllm_py_b200.weights import write_model_folder
+
+    sys.path.insert(0, str(ref_root))
+    try:
+        import cupy as cp
+        from fastllm_py import DeviceMap, Model
+        from fastllm_py.batched import BatchedDecoder
+
+        layers = args.layers or MODEL_7B["num_layers"]
+        cfg = LlamaConfig(architecture="LlamaForCausalLM", rope_scaling=None, tie_word_embeddings=False,
+                          **dict(MODEL_7B, num_layers=layers))
+        warmup = max(3, args.warmup)
+        with tempfile.TemporaryDirectory() as tmp:
+            folder = write_model_folder(cfg, Path(tmp) / "model", seed=0, std=0.02, norm_std=0.02)
+            model = Model.load(str(folder), DeviceMap({"cuda:0": 1}), dtype="float16")
+        rng = np.random.default_rng(8)
+        prompts = [rng.integers(0, cfg.vocab_size, size=CONTEXT).astype(np.int64) for _ in range(args.batch)]
+        dec = BatchedDecoder(model, args.batch, max_len=CONTEXT + warmup + args.steps + 8)
+        dec.prime(prompts)
+        tokens = np.zeros(args.batch, dtype=np.int64)
+        for _ in range(warmup):
+            dec.step(tokens)
+        cp.cuda.Device().synchronize()
+        start, stop = cp.cuda.Event(), cp.cuda.Event()
+        start.record()
+        for _ in range(args.steps):
+            dec.step(tokens)
+        stop.record()
+        stop.synchronize()
+        ms = cp.cuda.get_elapsed_time(start, stop) / args.steps
+        print(json.dumps({"impl": "reference", "metric": "decode tok/s @ batch 8, 2048-token context, DeepSeek-LLM-7B",
+                          "value": round(args.batch * 1000.0 / ms, 2), "unit": "tokens/s", "n_gpus": 1,
+                          "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms, 4),
+                          "higher_is_better": True, "dtype": "fp16", "data": "synthetic",
+                          "config": {"model": "DeepSeek-LLM-7B size, random weights", "global_batch": args.batch,
+                                     "seq_len": CONTEXT, "layers": layers,
+                                     "layers_of_config": MODEL_7B["num_layers"]}}))
+    except Exception as e:                                   # noqa: BLE001
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference's GPU path failed: {type(e).__name__}: {e}"}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -441,13 +566,12 @@ def main():
                          "deepseek-coder-1.3b size; 67b: prompt and decode steps at deepseek-llm-67b size")
     ap.add_argument("--requests", type=int, default=128, help="serve: how many requests")
     ap.add_argument("--rate", type=float, default=16.0, help="serve: mean arrivals a second")
+    ap.add_argument("--reference-cpu", action="store_true",
+                    help="--impl reference without CuPy: also time the reference's NumPy path (one layer, one sequence)")
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "fastllm-py's GPU path needs CuPy (cupy-cuda12x), which is not installed and "
-                          "not in the offline wheelhouse; the package itself installs with --no-deps"}))
-        return 0
+        return run_reference(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
