@@ -38,6 +38,8 @@ Two more workloads, each printing one line of its own:
              token budget of 2048 and a cache pool that holds a quarter of what all requests
              together would need; generated and prompt tokens a second, time to the first
              token, time between tokens, how often a request was pushed out;
+  --workload tables  the headline model at other sizes: prompt steps of 128 to 8192 tokens, a 4096-token
+             prompt in portions of 512, decode steps over a grid of batch sizes and context lengths;
   --workload 67b     deepseek-llm-67b size (95 layers, hidden 8192, 64 heads over 8 key/value
              heads; 135 GB of weights on the one GPU): a 2048-token prompt step and decode
              steps at batch 1, 8 and 16 with 4000-token contexts, with their roofline fractions.
@@ -84,15 +86,18 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs.  nvidia-smi takes
+    a few tenths of a second to come up, so the sampler is started ahead of the region (`start`),
+    the region is marked (`with sampler:`), and only the samples taken inside it count."""
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
     def __init__(self):
-        self.samples = []
+        self.samples = []                                    # (wall-clock second, fields)
         self.proc = None
         self.gpu = self._this_gpu()
+        self.begin = self.end = None
 
     @staticmethod
     def _this_gpu() -> str:
@@ -106,26 +111,34 @@ class ClockSampler:
         except Exception:                                    # noqa: BLE001  (no device: nothing to sample)
             return "0"
 
-    def __enter__(self):
+    def start(self):
+        if self.proc is not None:
+            return self
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", self.gpu, f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
         return self
 
+    def __enter__(self):
+        self.start()
+        self.begin = time.time()
+        return self
+
     def _read(self):
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) == 6 and parts[0].isdigit():
-                self.samples.append(parts)
+            if len(parts) == 7 and parts[1].isdigit():
+                self.samples.append((time.time(), parts[1:]))
 
     def __exit__(self, *exc):
+        self.end = time.time()
         if self.proc is not None:
-            time.sleep(0.15)
+            time.sleep(0.12)                                 # a last sample that was taken inside the region may still be on its way
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
@@ -133,13 +146,15 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        # a sample is printed a moment after it was taken: allow for that at the region's end
+        inside = [f for t, f in self.samples if self.begin <= t <= self.end + 0.06] if self.begin else []
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"], "gpu": self.gpu}
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
-        return {"sm_mhz": int(statistics.median(int(s[0]) for s in self.samples)),
-                "sm_max_mhz": int(self.samples[0][1]), "reasons": reasons,
-                "samples": len(self.samples), "gpu": self.gpu}
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in inside)]
+        return {"sm_mhz": int(statistics.median(int(s[0]) for s in inside)),
+                "sm_max_mhz": int(inside[0][1]), "reasons": reasons,
+                "samples": len(inside), "gpu": self.gpu}
 
 
 def decode_bytes(cfg, batch, mean_context):
@@ -188,6 +203,7 @@ def time_decode(model, batch, steps, warmup, context, sample_clocks=False):
     vocab = engine.vocab
     gen = torch.Generator().manual_seed(batch)
     rids = [f"b{batch}_{i}" for i in range(batch)]
+    sampler = ClockSampler().start() if sample_clocks else None      # up and sampling by the time the contexts are in
     fill_context(engine, rids, context, vocab, gen)
     tokens = torch.randint(0, vocab, (warmup + steps, batch), generator=gen).tolist()
     out = torch.zeros(batch, dtype=torch.int32, device=engine.device)
@@ -200,7 +216,6 @@ def time_decode(model, batch, steps, warmup, context, sample_clocks=False):
         one(i)
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler() if sample_clocks else None
     if sampler:
         sampler.__enter__()
     before = ops.counter.launches
@@ -425,6 +440,68 @@ def run_67b(args, warmup):
     return 0
 
 
+def run_tables(args, warmup):
+    """The other sizes of the headline model, one JSON line: a prompt step of 128 to 8192 tokens
+    (whole, and a 4096-token prompt in portions of 512) with its fraction of the tensor peak, and
+    decode steps over a grid of batch sizes and context lengths with their fractions of the HBM
+    roofline.  Every figure that the design notes quote from these tables is in this line."""
+    import torch
+
+    from fastllm_py_b200 import LlamaConfig, Model, StepEntry
+
+    layers = args.layers or MODEL_7B["num_layers"]
+    cfg = LlamaConfig(architecture="LlamaForCausalLM", rope_scaling=None, tie_word_embeddings=False,
+                      **dict(MODEL_7B, num_layers=layers, max_position_embeddings=16384))
+    pk = peaks()
+    grid = [(1, 512), (1, 4096), (1, 8192), (8, 512), (8, 4096), (8, 8192), (16, 8192), (32, 2048), (64, 512),
+            (64, 2048), (128, 2048)]
+    steps = max(8, min(args.steps, 32))
+    pool = max(b * (c + warmup + steps + 64) for b, c in grid)
+    model = Model.from_config(cfg, seed=0, dtype="bfloat16", page_size=16, max_tokens=pool, max_requests=128,
+                              max_batched_tokens=8192, max_model_len=16384, cuda_graph=not args.no_graph)
+    sampler = ClockSampler().start()
+    sampler.__enter__()
+    prompt = {}
+    for t in (128, 256, 512, 1024, 2048, 4096, 8192):
+        ms, mean = time_prefill(model, t, 10, 3)
+        prompt[str(t)] = {"ms": round(ms, 3), "ms_mean": round(mean, 3),
+                          "frac": round(prefill_flops(cfg, t) / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    # a 4096-token prompt in eight portions of 512
+    engine = model.engine
+    toks = torch.randint(0, cfg.vocab_size, (4096,), generator=torch.Generator().manual_seed(3)).tolist()
+    times = []
+    for i in range(3 + 5):
+        engine.begin("chunked")
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for at in range(0, 4096, 512):
+            engine.step([StepEntry("chunked", toks[at:at + 512], [511] if at + 512 == 4096 else [])])
+        stop.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(start.elapsed_time(stop))
+        engine.end("chunked")
+    chunked_ms = statistics.median(times)
+    decode = {}
+    for b, c in grid:
+        v, ms, _, _ = time_decode(model, b, steps, warmup, c)
+        nbytes = decode_bytes(cfg, b, c + warmup + (steps + 1) / 2)
+        decode[f"{b}x{c}"] = {"ms_per_step": round(ms, 3), "value": round(v, 1),
+                              "frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+    sampler.__exit__()
+    print(json.dumps({
+        "metric": "prompt steps and decode steps at other sizes, DeepSeek-LLM-7B size bf16", "n_gpus": 1,
+        "dtype": "bf16", "data": "synthetic", "impl": "ours", "steps": steps, "warmup": warmup,
+        "config": {"model": "DeepSeek-LLM-7B size, random weights", "layers": layers,
+                   "layers_of_config": MODEL_7B["num_layers"], "page_size": 16, "peaks": pk["source"],
+                   "hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "cuda_graph": not args.no_graph},
+        "prompt_step": prompt,
+        "prompt_4096_in_portions_of_512": {"ms": round(chunked_ms, 3), "value": round(4096 * 1000.0 / chunked_ms, 1)},
+        "decode": decode, "clocks": sampler.summary()}))
+    return 0
+
+
 def reference_cpu_path(ref_root, layers=1, context=256, decode_tokens=8):
     """fastllm-py's own NumPy model code (its CPU device, float32) timed at DeepSeek-LLM-7B layer
     sizes: `layers` of the 30 layers, one sequence (that path has no batch), a `context`-token
@@ -561,7 +638,7 @@ def main():
                     help="run fewer layers of the same sizes (the line names both numbers)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "67b"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "67b", "tables"],
                     help="decode: the headline line (DeepSeek-LLM-7B size); serve: continuous batching at "
                          "deepseek-coder-1.3b size; 67b: prompt and decode steps at deepseek-llm-67b size")
     ap.add_argument("--requests", type=int, default=128, help="serve: how many requests")
@@ -580,6 +657,8 @@ def main():
         return run_serving(args)
     if args.workload == "67b":
         return run_67b(args, warmup)
+    if args.workload == "tables":
+        return run_tables(args, warmup)
     args.layers = args.layers or MODEL_7B["num_layers"]
 
     import torch

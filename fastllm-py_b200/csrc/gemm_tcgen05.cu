@@ -886,6 +886,17 @@ static int launch_tc(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C
                      float* partial, long ld_partial, int M, int N, int K, int splits,
                      int kb_per_split, int* status, cudaStream_t stream, int gate_rows = 0, int feat = 64) {
     using L = TcSmem<BN, STAGES>;
+    // This kernel is launched with programmatic overlap, so CTAs of it and of its neighbours in the stream share
+    // SMs; as many of them as fit an SM by shared memory must find their tensor-memory columns free at once, or an
+    // allocation would wait for a CTA that waits for its predecessor (see fl_launch).  Every kernel launched that
+    // way which takes tensor memory is an instance of this one, and the instance with the least shared memory
+    // decides how many fit.
+    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr int SMALLEST_TOTAL = 96 * 1024;                  // no instance has less shared memory than this ...
+    constexpr int MOST_COLS = 256;                             // ... and none takes more columns than this
+    static_assert(L::TOTAL >= SMALLEST_TOTAL && TMEM_COLS <= MOST_COLS, "a new instance: revise the two bounds");
+    static_assert(TMEM_COLS + (232448 - L::TOTAL) / SMALLEST_TOTAL * MOST_COLS <= 512,
+                  "CTAs that fit an SM together could ask for more than its 512 tensor-memory columns");
     static bool configured = false;
     auto kernel = gemm_tc_kernel<BN, STAGES, OutT, GATED>;
     if (!configured) {
