@@ -514,17 +514,106 @@ __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {    // arrive
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & TC2_PEER_MASK) : "memory");
 }
 
+// ROPE: the q|k|v product of an attention layer with heads of 128, followed in the same kernel by what
+// would otherwise be a kernel of its own (rope_kv.cu): a CTA's 128 features are exactly one head, so the
+// epilogue, which has 32 tokens x 128 features of it in shared memory anyway, rotates a query head and
+// writes it to C, rotates a key head straight into the tokens' slots of the paged cache, and copies a value
+// head there.  The k and v columns never go to memory as activations (a third of what the rotary kernel
+// read and wrote).  Values are rounded to bfloat16 before the rotation, as the separate kernel finds them,
+// and rotated by the same expressions.
+struct TcRope {
+    const int* positions;       // [tokens] absolute position
+    const int* slots;           // [tokens] page * page_size + offset, < 0: no cache write for the token
+    const float* cos_table;     // [positions, 64]
+    const float* sin_table;
+    bf16* k_cache;              // the layer's keys: [page][kv head][page_size][128], pages page_stride elements apart
+    bf16* v_cache;
+    long page_stride;
+    int page_size, n_heads, n_kv_heads;
+};
+// How the 128 epilogue threads share a round of 32 tokens x 128 features: four threads a token row, thread
+// q of a row owning the pairs (j, j + 64) for j in [16 q, 16 q + 16).  What a thread needs from global memory for
+// a round (its token's position and slot, then 16 cosines and sines) is asked for well before it is used: the
+// position and slot a round ahead, the table values before the round's accumulator is read from tensor memory.
+#define TC_ROPE_PITCH 136                                   // staging row pitch in elements: rows 272 bytes apart spread over the banks
+struct TcRopeRow {
+    int pos, slot;
+    float4 c[4], s[4];
+};
+__device__ __forceinline__ void tc_rope_ask_row(const TcRope& rp, TcRopeRow& w, int t, bool real) {
+    w.pos = real ? rp.positions[t] : 0;
+    w.slot = real ? rp.slots[t] : -1;
+}
+__device__ __forceinline__ void tc_rope_ask_table(const TcRope& rp, TcRopeRow& w, int q, bool rotates) {
+    if (!rotates) return;
+    const float4* cs = reinterpret_cast<const float4*>(rp.cos_table + (long)w.pos * 64 + 16 * q);
+    const float4* sn = reinterpret_cast<const float4*>(rp.sin_table + (long)w.pos * 64 + 16 * q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        w.c[i] = cs[i];
+        w.s[i] = sn[i];
+    }
+}
+// one token row of one head from the staging area `x` (128 values): a query head is rotated and goes to C, a
+// key head is rotated into the token's cache slot, a value head is copied there
+__device__ __forceinline__ void tc_rope_row(const TcRope& rp, const TcRopeRow& w, bf16* __restrict__ C, long ldc,
+                                            const bf16* __restrict__ x, int t, int o0, int q) {
+    constexpr int HD = 128, HALF = 64;
+    const int head = o0 / HD;
+    const bool is_query = head < rp.n_heads, is_key = head < rp.n_heads + rp.n_kv_heads;
+    bf16* dst;
+    if (is_query) {
+        dst = C + (long)t * ldc + o0;
+    } else {
+        if (w.slot < 0) return;
+        const long page = w.slot / rp.page_size;
+        const int off = w.slot - (int)page * rp.page_size;
+        const int kvh = head - rp.n_heads - (is_key ? 0 : rp.n_kv_heads);
+        dst = (is_key ? rp.k_cache : rp.v_cache) + page * rp.page_stride + (long)kvh * rp.page_size * HD + (long)off * HD;
+        if (!is_key) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                *reinterpret_cast<uint4*>(dst + 32 * q + 8 * i) = *reinterpret_cast<const uint4*>(x + 32 * q + 8 * i);
+            return;
+        }
+    }
+    const int j = 16 * q;
+#pragma unroll
+    for (int v = 0; v < 2; ++v) {                           // two vectors of eight pairs
+        const uint4 a = *reinterpret_cast<const uint4*>(x + j + 8 * v);
+        const uint4 b = *reinterpret_cast<const uint4*>(x + j + 8 * v + HALF);
+        const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b);
+        const float c[8] = {w.c[2 * v].x, w.c[2 * v].y, w.c[2 * v].z, w.c[2 * v].w,
+                            w.c[2 * v + 1].x, w.c[2 * v + 1].y, w.c[2 * v + 1].z, w.c[2 * v + 1].w};
+        const float sv[8] = {w.s[2 * v].x, w.s[2 * v].y, w.s[2 * v].z, w.s[2 * v].w,
+                             w.s[2 * v + 1].x, w.s[2 * v + 1].y, w.s[2 * v + 1].z, w.s[2 * v + 1].w};
+        uint4 lo, hi;
+        __nv_bfloat162* lp = reinterpret_cast<__nv_bfloat162*>(&lo);
+        __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 x1 = __bfloat1622float2(ap[i]), x2 = __bfloat1622float2(bp[i]);
+            lp[i] = __floats2bfloat162_rn(x1.x * c[2 * i] - x2.x * sv[2 * i], x1.y * c[2 * i + 1] - x2.y * sv[2 * i + 1]);
+            hp[i] = __floats2bfloat162_rn(x2.x * c[2 * i] + x1.x * sv[2 * i], x2.y * c[2 * i + 1] + x1.y * sv[2 * i + 1]);
+        }
+        *reinterpret_cast<uint4*>(dst + j + 8 * v) = lo;
+        *reinterpret_cast<uint4*>(dst + j + 8 * v + HALF) = hi;
+    }
+}
+
 // GATED as in gemm_tc_kernel: each CTA's 128 weight rows are 64 gate rows and the 64 up rows of the
 // same features, a pair's tile is 128 features wide, and the epilogue writes silu(gate) * up
 // (whole K only: `splits` is 1 then).
-template <int BNT, typename OutT, bool GATED>
+template <int BNT, typename OutT, bool GATED, bool ROPE>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
     OutT* __restrict__ C, long ldc, int M, int N, int K, int tiles_n, int num_tiles,
     int* __restrict__ status, int gate_rows, int splits, int kb_per_split, float* __restrict__ partial,
-    long ld_partial) {
+    long ld_partial, const TcRope rope) {
     using L = Tc2<BNT>;
     static_assert(!GATED || BNT == 256, "the gated epilogue is written for 256-token tiles");
+    static_assert(!ROPE || (!GATED && sizeof(OutT) == 2), "the rotary epilogue writes bfloat16 and is not gated");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full_bar = (uint64_t*)(tiles + L::TILE_BYTES);
@@ -724,6 +813,32 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
                 float* slab = splits > 1 ? partial + (long)split * M * ld_partial : nullptr;
                 const bool vec_ok = slab ? ((((uintptr_t)slab | (uintptr_t)(ld_partial * 4)) & 15) == 0)
                                          : ((((uintptr_t)C | (uintptr_t)(ldc * (long)sizeof(OutT))) & 15) == 0);
+                if constexpr (ROPE) {
+                    // (ROPE: whole K, bfloat16, one head a CTA; see TcRope)
+                    const int row = e >> 2, q4 = e & 3;         // this thread's token row of a round and its quarter of the pairs
+                    const bool rotates = o0 / 128 < rope.n_heads + rope.n_kv_heads;
+                    TcRopeRow cur, nxt;
+                    tc_rope_ask_row(rope, cur, t0 + row, t0 + row < M);
+#pragma unroll 1
+                    for (int c = 0; c < BNT; c += 32) {
+                        if (t0 + c >= M) break;                 // uniform over the four warps
+                        const int t = t0 + c + row;
+                        tc_rope_ask_table(rope, cur, q4, rotates && t < M);
+                        tc_rope_ask_row(rope, nxt, t + 32, c + 32 < BNT && t + 32 < M);
+                        uint32_t r[32];
+                        tmem_ld16(t_base + (uint32_t)c, r);
+                        tmem_ld16(t_base + (uint32_t)c + 16u, r + 16);
+                        tmem_ld_wait();
+                        bf16* st = reinterpret_cast<bf16*>(staged + (rounds_out++ & 1u) * (TC2_OUT_BYTES / 2));
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) st[j * TC_ROPE_PITCH + e] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                        epilogue_sync();
+                        if (cols > 0 && t < M)
+                            tc_rope_row(rope, cur, reinterpret_cast<bf16*>(C), ldc, st + row * TC_ROPE_PITCH, t, o0, q4);
+                        cur.pos = nxt.pos;
+                        cur.slot = nxt.slot;
+                    }
+                } else {
 #pragma unroll 1
                 for (int c = 0; c < BNT; c += 32) {
                     if (t0 + c >= M) break;                     // uniform over the four warps
@@ -752,6 +867,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
                     }
                 }
             }
+                }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_leader(&acc_empty[buf]);
@@ -770,12 +886,15 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
     cluster_sync_all();
 }
 
-template <int BNT, typename OutT, bool GATED = false>
+template <int BNT, typename OutT, bool GATED = false, bool ROPE = false>
 static int launch_tc_pair(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C, long ldc, int M, int N,
                           int K, int num_sms, int* status, cudaStream_t stream, int gate_rows = 0, int splits = 1,
-                          int kb_per_split = 0, float* partial = nullptr, long ld_partial = 0) {
+                          int kb_per_split = 0, float* partial = nullptr, long ld_partial = 0,
+                          const TcRope* rope_args = nullptr) {
     static bool configured = false;
-    auto kernel = gemm_tc_pair_kernel<BNT, OutT, GATED>;
+    auto kernel = gemm_tc_pair_kernel<BNT, OutT, GATED, ROPE>;
+    TcRope rope = {};
+    if (rope_args) rope = *rope_args;
     constexpr int smem = Tc2<BNT>::SMEM + (GATED ? TC2_XCH_BYTES + TC2_GATED_OUT_BYTES : TC2_OUT_BYTES);
     static_assert(smem <= 232448, "more shared memory than a CTA can have");
     if (!configured) {
@@ -802,7 +921,7 @@ static int launch_tc_pair(const CUtensorMap& map_w, const CUtensorMap& map_a, vo
     // Launched in plain stream order (no programmatic overlap with its neighbours): see the note in the kernel.
     cfg.numAttrs = 1;
     return (int)cudaLaunchKernelEx(&cfg, kernel, map_w, map_a, (OutT*)C, ldc, M, N, K, tiles_n, num_tiles, status,
-                                   gate_rows, splits, kb_per_split, partial, ld_partial);
+                                   gate_rows, splits, kb_per_split, partial, ld_partial, rope);
 }
 
 template <typename OutT>
@@ -1084,6 +1203,41 @@ FL_API int fl_gemm_tc_swiglu(const void* A, long lda, const void* W, long ldw, v
         case 32: return launch_tc<32, 5, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I, feat);
         case 64: return launch_tc<64, 4, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I, feat);
         case 128: return launch_tc<128, 3, bf16, true>(map_w, map_a, C, ldc, nullptr, 0, M, I, K, 1, kb, status, stream, I, feat);
+    }
+    return -1;
+}
+
+// The q|k|v product of an attention layer with its rotary encoding and cache write in the epilogue (see TcRope):
+// W is [(n_heads + 2 n_kv_heads) * 128, K], q|k|v head-major; the rotated queries go to C[M, n_heads * 128]
+// (row pitch ldc), rotated keys and the values into the cache slots of the tokens.  Returns 0 when launched and
+// -1 when this problem is not taken (heads not of 128 rotated in full, 64 tokens or fewer, a plan that splits K,
+// an output that is not 16-byte aligned): the caller then runs the product and the rotary kernel apart.
+FL_API int fl_gemm_tc_qkv_rope(const void* A, long lda, const void* W, long ldw, void* C, long ldc, int M, int K,
+                               int n_heads, int n_kv_heads, int head_dim, int rot_dim, const int* positions,
+                               const int* slots, const float* cos_table, const float* sin_table, void* k_cache,
+                               void* v_cache, long page_stride, int page_size, int num_sms, int* status,
+                               cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (K <= 0 || n_heads <= 0 || n_kv_heads <= 0) return (int)cudaErrorInvalidValue;
+    if (head_dim != 128 || rot_dim != 128 || M <= 64 || num_sms < 2 || k_cache == nullptr || v_cache == nullptr) return -1;
+    if ((ldc % 8) || ((uintptr_t)C & 15) || (page_stride % 8) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
+        return -1;
+    const int N = (n_heads + 2 * n_kv_heads) * 128;
+    int bn = 0, splits = 0;
+    fl_gemm_tc_plan(M, N, K, num_sms, &bn, &splits);
+    if (splits != 1 || bn < 512) return -1;
+    const int bnt = bn == 512 ? 256 : bn - 512;
+    CUtensorMap map_w, map_a;
+    int rc = make_map(&map_w, W, N, K, ldw, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&map_a, A, M, K, lda, bnt / 2);
+    if (rc) return rc;
+    TcRope rope = {positions, slots, cos_table, sin_table, (bf16*)k_cache, (bf16*)v_cache, page_stride, page_size,
+                   n_heads, n_kv_heads};
+    switch (bnt) {
+        case 64: return launch_tc_pair<64, bf16, false, true>(map_w, map_a, C, ldc, M, N, K, num_sms, status, stream, 0, 1, 0, nullptr, 0, &rope);
+        case 128: return launch_tc_pair<128, bf16, false, true>(map_w, map_a, C, ldc, M, N, K, num_sms, status, stream, 0, 1, 0, nullptr, 0, &rope);
+        case 256: return launch_tc_pair<256, bf16, false, true>(map_w, map_a, C, ldc, M, N, K, num_sms, status, stream, 0, 1, 0, nullptr, 0, &rope);
     }
     return -1;
 }

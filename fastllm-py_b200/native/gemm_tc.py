@@ -28,6 +28,10 @@ def _lib():
         lib.fl_gemm_tc_swiglu.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
                                           c_int, c_int, c_void_p, c_void_p]
         lib.fl_gemm_tc_swiglu.restype = c_int
+        lib.fl_gemm_tc_qkv_rope.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
+                                            c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                            c_void_p, c_long, c_int, c_int, c_void_p, c_void_p]
+        lib.fl_gemm_tc_qkv_rope.restype = c_int
         lib.fl_splitk_reduce.argtypes = [c_void_p, c_long, c_int, c_void_p, c_int, c_long, c_int, c_int, c_void_p]
         lib.fl_splitk_reduce.restype = c_int
         _state["lib"] = lib
@@ -176,6 +180,39 @@ def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     if rc == -1:
         return False
     ops._check(rc, "gemm_tcgen05 (gated)")
+    return True
+
+
+def gemm_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, n_heads: int, n_kv_heads: int,
+                  head_dim: int, rot_dim: int, cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor,
+                  slots: torch.Tensor, cache: torch.Tensor, page_size: int) -> bool:
+    """The q|k|v product of an attention layer with the rotary encoding and the cache write in its
+    epilogue: q_out[M, n_heads * head_dim] gets the rotated queries, `cache`
+    ([pages, 2, kv_heads, page_size, head_dim]) the rotated keys and the values at the tokens' `slots`;
+    w = [q; k; v] stacked as [(n_heads + 2 n_kv_heads) * head_dim, K], all bfloat16.  Returns False,
+    having done nothing, when the kernel does not take the problem (heads not of 128 rotated in full,
+    64 tokens or fewer, a plan that splits K)."""
+    m, k = a.shape
+    if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or q_out.dtype != torch.bfloat16
+            or cache.dtype != torch.bfloat16 or w.shape != ((n_heads + 2 * n_kv_heads) * head_dim, k)
+            or tuple(q_out.shape) != (m, n_heads * head_dim) or cos.dtype != torch.float32):
+        raise ops.KernelError(f"gemm_qkv_rope: {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(q_out.shape)}, "
+                              f"{a.dtype}/{w.dtype}/{q_out.dtype}/{cache.dtype}")
+    if m == 0:
+        return True
+    lda, ldw = ops._ld(a), ops._ld(w)
+    if lda % 8 or ldw % 8 or a.data_ptr() % 16 or w.data_ptr() % 16 or not cache.is_contiguous() \
+            or cos.shape[1] * 2 != rot_dim or not cos.is_contiguous() or not sin.is_contiguous():
+        return False
+    k_ptr = c_void_p(cache.data_ptr())
+    v_ptr = c_void_p(cache.data_ptr() + cache.stride(1) * cache.element_size())
+    rc = _lib().fl_gemm_tc_qkv_rope(ops._ptr(a), lda, ops._ptr(w), ldw, ops._ptr(q_out), ops._ld(q_out), m, k,
+                                    n_heads, n_kv_heads, head_dim, rot_dim, ops._ptr(positions), ops._ptr(slots),
+                                    ops._ptr(cos), ops._ptr(sin), k_ptr, v_ptr, cache.stride(0), page_size,
+                                    _num_sms(a.device), ops._ptr(status_word(a.device)), ops._stream())
+    if rc == -1:
+        return False
+    ops._check(rc, "gemm_tcgen05 (q|k|v with rotary)")
     return True
 
 

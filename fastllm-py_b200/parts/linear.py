@@ -56,6 +56,19 @@ class Linear:
             from ..native import gemm_tc
             gemm_tc.reserve(self.weight.device, self.out_features, self.in_features, max_tokens)
 
+    def forward_qkv_rope(self, a: torch.Tensor, q_out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                         rot_dim: int, cos, sin, positions, slots, cache, page_size: int) -> bool:
+        """For a Linear that stacks q, k and v matrices: the product with the rotary encoding and the
+        cache write in its epilogue (rotated queries into `q_out`, rotated keys and values into the
+        tokens' cache slots), in one tensor-core kernel.  False (nothing done) when that kernel does
+        not apply; the caller then takes `forward` and the rotary kernel."""
+        if a.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and self.weight.is_contiguous() \
+                and self.in_features % 8 == 0:
+            from ..native.gemm_tc import gemm_qkv_rope
+            return gemm_qkv_rope(a, self.weight, q_out, n_heads, n_kv_heads, head_dim, rot_dim, cos, sin, positions,
+                                 slots, cache, page_size)
+        return False
+
     def forward_gated(self, a: torch.Tensor, out: torch.Tensor) -> bool:
         """For a Linear that stacks a gate and an up matrix: out = silu(a gate^T) * (a up^T)
         in one tensor-core kernel.  False (nothing done) when that kernel does not apply; the

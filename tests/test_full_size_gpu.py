@@ -122,6 +122,49 @@ def test_products_of_prompt_portions(m, n, k):
     assert float((out.float() - ref).abs().max()) <= 2 ** -8 * float(ref.abs().max()) + 1e-3
 
 
+@pytest.mark.parametrize("m", [128, 300, 2304])
+def test_qkv_product_with_rotary_and_cache_write_in_its_epilogue(m):
+    """The q|k|v product at 4096 -> 12288 with heads of 128: the fused kernel (rotation and cache write in
+    the product's epilogue) against the product followed by the rotary kernel, on the same inputs: the
+    rotated queries and what lands in the cache pages are the same bit for bit, and pages of no token
+    stay untouched."""
+    from fastllm_py_b200.native import gemm_tc, ops
+
+    heads = kv_heads = 32
+    k, hd, page = 4096, 128, 16
+    a, w = _randn((m, k), m + 7, 0.5), _randn(((heads + 2 * kv_heads) * hd, k), 11, 0.05)
+    g = torch.Generator().manual_seed(m)
+    n_pages = -(-m // page) + 9
+    perm = torch.randperm(n_pages, generator=g)[:-(-m // page)]
+    positions = torch.arange(100, 100 + m, dtype=torch.int32)
+    slots = (perm[torch.arange(m) // page] * page + torch.arange(m) % page).to(torch.int32)
+    slots[5] = -1                                            # a token without a cache slot writes nothing
+    ang = torch.arange(100 + m + 1, dtype=torch.float32)[:, None] * (10000.0 ** (-torch.arange(0, hd, 2) / hd))[None, :]
+    cos, sin = torch.cos(ang).to(DEV).contiguous(), torch.sin(ang).to(DEV).contiguous()
+    positions, slots = positions.to(DEV), slots.to(DEV)
+
+    def run(fused):
+        cache = torch.full((n_pages, 2, kv_heads, page, hd), 3.0, dtype=torch.bfloat16, device=DEV)
+        qkv = torch.full((m, (heads + 2 * kv_heads) * hd), -5.0, dtype=torch.bfloat16, device=DEV)
+        if fused:
+            assert gemm_tc.gemm_qkv_rope(a, w, qkv[:, :heads * hd], heads, kv_heads, hd, hd, cos, sin, positions,
+                                         slots, cache, page)
+        else:
+            gemm_tc.gemm(a, w, qkv)
+            ops.rope_kv_write(qkv, heads, kv_heads, hd, hd, cos, sin, positions, slots, cache, page)
+        torch.cuda.synchronize()
+        assert _status() == 0
+        return qkv[:, :heads * hd].clone(), cache
+
+    q_ref, cache_ref = run(False)
+    q_got, cache_got = run(True)
+    assert torch.equal(q_got, q_ref)
+    assert torch.equal(cache_got, cache_ref)
+    untouched = torch.ones(n_pages, dtype=torch.bool)
+    untouched[perm] = False
+    assert bool((cache_got[untouched.to(DEV)] == 3.0).all())
+
+
 # ------------------------------------------------------------------------ attention
 
 class PagedCase:
