@@ -32,6 +32,8 @@ def _lib():
                                             c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_long, c_int, c_int, c_void_p, c_void_p]
         lib.fl_gemm_tc_qkv_rope.restype = c_int
+        lib.fl_pack_weight.argtypes = [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p]
+        lib.fl_pack_weight.restype = c_int
         lib.fl_splitk_reduce.argtypes = [c_void_p, c_long, c_int, c_void_p, c_int, c_long, c_int, c_int, c_void_p]
         lib.fl_splitk_reduce.restype = c_int
         _state["lib"] = lib
@@ -91,6 +93,41 @@ def reserve(device, n: int, k: int, max_tokens: int) -> None:
     scratch.reserve(device, SCRATCH, need)
 
 
+class PackedWeight:
+    """A weight matrix [n, k] packed by k-block for the tensor-core kernels: [ceil(k / 64)][n][64], so
+    that the 128 rows x 64 columns of a stage's tile are 16 KB in one piece (from the row-major
+    matrix DRAM serves them 128 bytes at a time from 128 pages: streaming products are 4 to 7 %
+    slower).  Made once, when a model is loaded; the kernels take either layout."""
+
+    def __init__(self, weight: torch.Tensor):
+        if weight.dtype != torch.bfloat16 or weight.dim() != 2 or (weight.shape[1] > 1 and weight.stride(1) != 1):
+            raise ops.KernelError("only a bfloat16 matrix with a dense last axis can be packed")
+        self.n, self.k = weight.shape
+        self.shape = (self.n, self.k)
+        self.dtype, self.device = weight.dtype, weight.device
+        self.data = torch.empty((-(-self.k // 64), self.n, 64), dtype=torch.bfloat16, device=weight.device)
+        rc = _lib().fl_pack_weight(ops._ptr(weight), ops._ld(weight), ops._ptr(self.data), self.n, self.k, ops._stream())
+        ops._check(rc, "pack_weight")
+
+    def data_ptr(self) -> int:
+        return self.data.data_ptr()
+
+    def unpacked(self) -> torch.Tensor:
+        """The row-major matrix again (tests)."""
+        return self.data.permute(1, 0, 2).reshape(self.n, -1)[:, :self.k].contiguous()
+
+
+def _weight_args(w):
+    """(pointer, leading dimension) of a weight for the kernels: a leading dimension of 0 says packed."""
+    if isinstance(w, PackedWeight):
+        return c_void_p(w.data_ptr()), 0
+    ldw = ops._ld(w)
+    if ldw % 8 or w.data_ptr() % 16:
+        raise ops.KernelError("tensor-core gemm: operands must be 16-byte aligned with a row pitch "
+                              "that is a multiple of 8 elements")
+    return ops._ptr(w), ldw
+
+
 class Partial:
     """A product left as split-K partial sums: `splits` float slabs [rows, ld] in
     the shared workspace, to be added (in slab order) by the kernel that reads
@@ -119,10 +156,10 @@ class Partial:
         return out
 
 
-def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int = 0, splits: int = 0,
+def gemm(a: torch.Tensor, w, out: torch.Tensor, bn: int = 0, splits: int = 0,
          defer: bool = False):
     """out[M, N] = a[M, K] @ w[N, K]^T; a and w bfloat16 (row pitch a multiple of 8
-    elements, base 16-byte aligned), out bfloat16 or float32.
+    elements, base 16-byte aligned; w may be a PackedWeight), out bfloat16 or float32.
 
     With `defer`, a product whose K is split returns a Partial instead of
     writing `out`: its consumer adds the slabs while it reads them."""
@@ -134,10 +171,11 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int = 0, split
         raise ops.KernelError(f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
     if m == 0:
         return
-    lda, ldw, ldc = ops._ld(a), ops._ld(w), ops._ld(out)
-    if lda % 8 or ldw % 8 or a.data_ptr() % 16 or w.data_ptr() % 16:
+    lda, ldc = ops._ld(a), ops._ld(out)
+    if lda % 8 or a.data_ptr() % 16:
         raise ops.KernelError("tensor-core gemm: operands must be 16-byte aligned with a row pitch "
                               "that is a multiple of 8 elements")
+    w_ptr, ldw = _weight_args(w)
     sms = _num_sms(a.device)
     if bn == 0:
         bn, splits = plan(m, n, k, sms)
@@ -151,7 +189,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int = 0, split
     if splits > 1:
         serial_key = ("serial", str(a.device))
         _state[serial_key] = _state.get(serial_key, 0) + 1    # earlier Partials are now stale
-    rc = fn(ops._ptr(a), lda, ops._ptr(w), ldw, ops._ptr(out), ops.dtype_code(out), ldc,
+    rc = fn(ops._ptr(a), lda, w_ptr, ldw, ops._ptr(out), ops.dtype_code(out), ldc,
             m, n, k, bn, splits, ops._ptr(ws), ws_floats, sms,
             ops._ptr(status_word(a.device)), ops._stream())
     ops._check(rc, "gemm_tcgen05", 2 if (splits > 1 and not deferred) else 1)
@@ -160,7 +198,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int = 0, split
     return None
 
 
-def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+def gemm_swiglu(a: torch.Tensor, w, out: torch.Tensor) -> bool:
     """out[M, I] = silu(a @ gate^T) * (a @ up^T) for w = [gate; up] stacked as [2 I, K], all
     bfloat16, in one kernel (the activation in the product's epilogue).  Returns False, having
     done nothing, when the kernel does not take the problem (its plan splits K)."""
@@ -172,10 +210,14 @@ def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
                               f"{a.dtype}/{w.dtype}/{out.dtype}")
     if m == 0:
         return True
-    lda, ldw = ops._ld(a), ops._ld(w)
-    if lda % 8 or ldw % 8 or a.data_ptr() % 16 or w.data_ptr() % 16:
+    lda = ops._ld(a)
+    if lda % 8 or a.data_ptr() % 16:
         return False
-    rc = _lib().fl_gemm_tc_swiglu(ops._ptr(a), lda, ops._ptr(w), ldw, ops._ptr(out), ops._ld(out), m, inter, k,
+    try:
+        w_ptr, ldw = _weight_args(w)
+    except ops.KernelError:
+        return False
+    rc = _lib().fl_gemm_tc_swiglu(ops._ptr(a), lda, w_ptr, ldw, ops._ptr(out), ops._ld(out), m, inter, k,
                                   _num_sms(a.device), ops._ptr(status_word(a.device)), ops._stream())
     if rc == -1:
         return False
@@ -183,7 +225,7 @@ def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     return True
 
 
-def gemm_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, n_heads: int, n_kv_heads: int,
+def gemm_qkv_rope(a: torch.Tensor, w, q_out: torch.Tensor, n_heads: int, n_kv_heads: int,
                   head_dim: int, rot_dim: int, cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor,
                   slots: torch.Tensor, cache: torch.Tensor, page_size: int) -> bool:
     """The q|k|v product of an attention layer with the rotary encoding and the cache write in its
@@ -194,19 +236,23 @@ def gemm_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, n_heads
     64 tokens or fewer, a plan that splits K)."""
     m, k = a.shape
     if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or q_out.dtype != torch.bfloat16
-            or cache.dtype != torch.bfloat16 or w.shape != ((n_heads + 2 * n_kv_heads) * head_dim, k)
+            or cache.dtype != torch.bfloat16 or tuple(w.shape) != ((n_heads + 2 * n_kv_heads) * head_dim, k)
             or tuple(q_out.shape) != (m, n_heads * head_dim) or cos.dtype != torch.float32):
         raise ops.KernelError(f"gemm_qkv_rope: {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(q_out.shape)}, "
                               f"{a.dtype}/{w.dtype}/{q_out.dtype}/{cache.dtype}")
     if m == 0:
         return True
-    lda, ldw = ops._ld(a), ops._ld(w)
-    if lda % 8 or ldw % 8 or a.data_ptr() % 16 or w.data_ptr() % 16 or not cache.is_contiguous() \
+    lda = ops._ld(a)
+    if lda % 8 or a.data_ptr() % 16 or not cache.is_contiguous() \
             or cos.shape[1] * 2 != rot_dim or not cos.is_contiguous() or not sin.is_contiguous():
+        return False
+    try:
+        w_ptr, ldw = _weight_args(w)
+    except ops.KernelError:
         return False
     k_ptr = c_void_p(cache.data_ptr())
     v_ptr = c_void_p(cache.data_ptr() + cache.stride(1) * cache.element_size())
-    rc = _lib().fl_gemm_tc_qkv_rope(ops._ptr(a), lda, ops._ptr(w), ldw, ops._ptr(q_out), ops._ld(q_out), m, k,
+    rc = _lib().fl_gemm_tc_qkv_rope(ops._ptr(a), lda, w_ptr, ldw, ops._ptr(q_out), ops._ld(q_out), m, k,
                                     n_heads, n_kv_heads, head_dim, rot_dim, ops._ptr(positions), ops._ptr(slots),
                                     ops._ptr(cos), ops._ptr(sin), k_ptr, v_ptr, cache.stride(0), page_size,
                                     _num_sms(a.device), ops._ptr(status_word(a.device)), ops._stream())
@@ -217,10 +263,14 @@ def gemm_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, n_heads
 
 
 class TensorCoreLinear:
-    """A weight made ready for the tensor-core kernel: a row pitch that is not a
-    multiple of 16 bytes (K not a multiple of 8) is padded once, at load."""
+    """A weight made ready for the tensor-core kernels: packed by k-block (see PackedWeight), or, with
+    `pack=False` (a matrix that something else reads row-major as well: a tied embedding table),
+    left as it is, padded once if its row pitch is not a multiple of 16 bytes."""
 
-    def __init__(self, weight: torch.Tensor):
+    def __init__(self, weight: torch.Tensor, pack: bool = True):
+        if pack:
+            self.weight = PackedWeight(weight)
+            return
         n, k = weight.shape
         if k % 8 or weight.data_ptr() % 16 or not weight.is_contiguous():
             pitch = -(-k // 8) * 8

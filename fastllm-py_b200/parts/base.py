@@ -69,8 +69,11 @@ class Part:
         """slot -> expected shape of the checkpoint tensor."""
         return {}
 
+    shared_slots: frozenset = frozenset()    # set by the decoder before `load`: slots whose tensor another part holds too
+
     def load(self, tensors: dict) -> None:
-        """Receives slot -> device tensor in its stored dtype."""
+        """Receives slot -> device tensor in its stored dtype.  A tensor of a slot in
+        `shared_slots` belongs to another part as well and must be left as it is."""
 
     def children(self) -> list:
         """Parts nested inside this one (their tensors are loaded too)."""

@@ -77,11 +77,21 @@ class Decoder:
         return table
 
     def load(self, tensors_by_name: dict) -> None:
+        """Hands every part its tensors.  A part is told beforehand (`shared_slots`) which of its
+        slots hold a tensor that another part holds too (a tied embedding table): it must leave
+        such a tensor as it is."""
+        users: dict = {}
+        for part in self.all_parts():
+            tensors = getattr(part.spec, "tensors", None)
+            if tensors is not None:
+                for slot in part.weight_shapes():
+                    users[tensors[slot]] = users.get(tensors[slot], 0) + 1
         for part in self.all_parts():
             tensors = getattr(part.spec, "tensors", None)
             if tensors is None:
                 continue
             shapes = part.weight_shapes()
+            part.shared_slots = frozenset(slot for slot in shapes if users[tensors[slot]] > 1)
             part.load({slot: tensors_by_name[tensors[slot]] for slot in shapes})
 
     def cache_needs(self) -> dict:

@@ -49,7 +49,9 @@ class LinearHead(Part):
         return {"weight": (self.vocab, self.hidden)}
 
     def load(self, tensors):
-        self.linear = Linear.sharing(tensors["weight"])
+        # a table that the embedding part reads too stays row-major; a matrix of its own may be packed
+        w = tensors["weight"]
+        self.linear = Linear.sharing(w) if "weight" in self.shared_slots else Linear([w])
 
     def reserve(self, limits):
         if self.linear is not None:

@@ -143,12 +143,14 @@ def test_qkv_product_with_rotary_and_cache_write_in_its_epilogue(m):
     cos, sin = torch.cos(ang).to(DEV).contiguous(), torch.sin(ang).to(DEV).contiguous()
     positions, slots = positions.to(DEV), slots.to(DEV)
 
+    packed = gemm_tc.PackedWeight(w)
+
     def run(fused):
         cache = torch.full((n_pages, 2, kv_heads, page, hd), 3.0, dtype=torch.bfloat16, device=DEV)
         qkv = torch.full((m, (heads + 2 * kv_heads) * hd), -5.0, dtype=torch.bfloat16, device=DEV)
         if fused:
-            assert gemm_tc.gemm_qkv_rope(a, w, qkv[:, :heads * hd], heads, kv_heads, hd, hd, cos, sin, positions,
-                                         slots, cache, page)
+            assert gemm_tc.gemm_qkv_rope(a, packed if fused == "packed" else w, qkv[:, :heads * hd], heads, kv_heads,
+                                         hd, hd, cos, sin, positions, slots, cache, page)
         else:
             gemm_tc.gemm(a, w, qkv)
             ops.rope_kv_write(qkv, heads, kv_heads, hd, hd, cos, sin, positions, slots, cache, page)
@@ -157,9 +159,10 @@ def test_qkv_product_with_rotary_and_cache_write_in_its_epilogue(m):
         return qkv[:, :heads * hd].clone(), cache
 
     q_ref, cache_ref = run(False)
-    q_got, cache_got = run(True)
-    assert torch.equal(q_got, q_ref)
-    assert torch.equal(cache_got, cache_ref)
+    for fused in (True, "packed"):                           # the weights row-major, and packed by k-block
+        q_got, cache_got = run(fused)
+        assert torch.equal(q_got, q_ref)
+        assert torch.equal(cache_got, cache_ref)
     untouched = torch.ones(n_pages, dtype=torch.bool)
     untouched[perm] = False
     assert bool((cache_got[untouched.to(DEV)] == 3.0).all())

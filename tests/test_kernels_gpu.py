@@ -94,6 +94,44 @@ def test_tensor_core_gemm_in_cta_pairs_every_tile_and_split(bn, splits, m, out_d
         assert float((slabs.sum(0).cpu() - ref).abs().max()) <= 1e-3 * math.sqrt(k)
 
 
+@pytest.mark.parametrize("m, n, k", [(3, 300, 728), (40, 130, 72), (70, 515, 200), (300, 700, 1000), (600, 257, 520)])
+def test_packed_weights_give_the_row_major_result(m, n, k):
+    """A weight packed by k-block ([ceil(K / 64)][N][64], what a model's matrices become at load) and
+    the same weight row-major go through the same kernels and give the same result bit for bit: the
+    plain product (one tile a CTA and CTA pairs, K whole and split, feature and K counts that end
+    inside a tile) and the product with the SwiGLU epilogue."""
+    from fastllm_py_b200.native import gemm_tc
+
+    g = torch.Generator(device="cpu").manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = torch.randn(n, k, generator=g).to(torch.bfloat16)
+    pitch = -(-k // 8) * 8
+    a_dev = torch.zeros(m, pitch, dtype=torch.bfloat16, device=DEV)[:, :k]
+    a_dev.copy_(a)
+    w_dev = torch.zeros(n, pitch, dtype=torch.bfloat16, device=DEV)[:, :k]
+    w_dev.copy_(w)
+    packed = gemm_tc.PackedWeight(w_dev)
+    assert torch.equal(packed.unpacked().cpu(), w)
+    outs = []
+    for weight in (w_dev, packed):
+        out = torch.full((m, n), -5.0, dtype=torch.float32, device=DEV)
+        gemm_tc.gemm(a_dev, weight, out)
+        outs.append(out.clone())
+    torch.cuda.synchronize()
+    assert int(gemm_tc.status_word(torch.device(DEV)).item()) == 0
+    assert torch.equal(outs[0], outs[1])
+    assert float((outs[1].cpu() - a.float() @ w.float().t()).abs().max()) <= 1e-3 * math.sqrt(k)
+    if n % 2 == 0:
+        acts = []
+        for weight in (w_dev, packed):
+            act = torch.full((m, n // 2), -5.0, dtype=torch.bfloat16, device=DEV)
+            if not gemm_tc.gemm_swiglu(a_dev, weight, act):
+                break
+            acts.append(act.clone())
+        if len(acts) == 2:
+            assert torch.equal(acts[0], acts[1])
+
+
 def test_tensor_core_gemm_plan_is_launchable():
     """What the plan answers for many problem sizes is a kernel the launcher has, with no empty split."""
     from fastllm_py_b200.native import gemm_tc
