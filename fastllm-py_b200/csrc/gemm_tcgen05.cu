@@ -468,9 +468,11 @@ __device__ __forceinline__ void tc_raster(int tile, int tiles_n, int tiles_m, in
 //     leader's accumulator-empty barrier.
 // No load is multicast.  The two CTAs meet at a cluster barrier after set-up and
 // before they leave, so neither touches the other's barriers outside its life.
-// The token side of a pair's tile is BNT = 256, 128 or 64 wide (each CTA holds half of it), so that
-// steps of a few hundred tokens do not compute on padding; a narrower tile leaves room for a deeper
-// ring.  K may be split: a pair's units of work are (tile, K range) pairs, and with more than one
+// The token side of a pair's tile has room for BNT = 256, 128 or 64 tokens (each CTA holds half of it); a
+// narrower tile leaves room for a deeper ring.  The tiles of a launch are `wt` <= BNT tokens wide, a
+// multiple of 32 chosen by the launcher so that the token tiles are equally wide and a step of, say,
+// 520 tokens is three tiles of 192 and not three of 256 (the box of the token rows' tensor map, the
+// bytes a stage expects and the MMA's N all follow wt).  K may be split: a pair's units of work are (tile, K range) pairs, and with more than one
 // split every unit writes its float partial sums to partial[split][token][feature] for the consumer
 // (or the reduce kernel) to add, exactly as the one-tile kernel does.
 template <int BNT>
@@ -619,7 +621,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
     OutT* __restrict__ C, long ldc, int M, int N, int K, int tiles_n, int num_tiles,
     int* __restrict__ status, int gate_rows, int splits, int kb_per_split, float* __restrict__ partial,
-    long ld_partial, const TcRope rope, int wp) {
+    long ld_partial, const TcRope rope, int wp, int wt) {
     using L = Tc2<BNT>;
     static_assert(!GATED || BNT == 256, "the gated epilogue is written for 256-token tiles");
     static_assert(!ROPE || (!GATED && sizeof(OutT) == 2), "the rotary epilogue writes bfloat16 and is not gated");
@@ -708,18 +710,18 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
                         break;
                     }
                     unsigned char* dst = tiles + s * L::STAGE_BYTES;
-                    if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * L::STAGE_BYTES);
+                    if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * (L::W_BYTES + (wt / 2) * TC_BK * 2));
                     load_weights(dst, &full_bar[s], kb, tn);
                     tma_load_2d_pair(dst + L::W_BYTES, &map_a, &full_bar[s], kb * TC_BK,
-                                     tm * BNT + (int)rank * (BNT / 2));
+                                     tm * wt + (int)rank * (wt / 2));
                     if (++s == L::STAGES) { s = 0; ph ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
-            // ---- MMA issuer (leader only): one 256 x BNT x 16 MMA per 16 columns of K, for both CTAs
-            constexpr uint32_t idesc = instr_desc_bf16(256, BNT);
+            // ---- MMA issuer (leader only): one 256 x wt x 16 MMA per 16 columns of K, for both CTAs
+            const uint32_t idesc = instr_desc_bf16(256, wt);
             int s = 0;
             uint32_t ph = 0;
             bool ok = !*abort_flag;
@@ -775,7 +777,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
             tc_fence_after();
             int tn, tm, split, kb0, kb1;
             unit(i, tn, tm, split, kb0, kb1);
-            const int t0 = tm * BNT;
+            const int t0 = tm * wt;
             const uint32_t t_base = tmem_base + (uint32_t)(buf * 256) + ((uint32_t)(quarter * 32) << 16);
             if (GATED) {
                 // accumulator lanes 0..63: gate features, 64..127: the same features' up values; the
@@ -786,7 +788,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
                 const int f0 = tn * 128 + (int)rank * 64;   // first of this CTA's 64 features
                 const bool vec_ok = (((uintptr_t)C | (uintptr_t)(ldc * (long)sizeof(OutT))) & 15) == 0;
 #pragma unroll 1
-                for (int c = 0; c < BNT; c += 32) {
+                for (int c = 0; c < wt; c += 32) {
                     if (t0 + c >= M) break;                 // uniform over the four warps
                     uint32_t r[32];
                     tmem_ld16(t_base + (uint32_t)c, r);
@@ -830,11 +832,11 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
                     TcRopeRow cur, nxt;
                     tc_rope_ask_row(rope, cur, t0 + row, t0 + row < M);
 #pragma unroll 1
-                    for (int c = 0; c < BNT; c += 32) {
+                    for (int c = 0; c < wt; c += 32) {
                         if (t0 + c >= M) break;                 // uniform over the four warps
                         const int t = t0 + c + row;
                         tc_rope_ask_table(rope, cur, q4, rotates && t < M);
-                        tc_rope_ask_row(rope, nxt, t + 32, c + 32 < BNT && t + 32 < M);
+                        tc_rope_ask_row(rope, nxt, t + 32, c + 32 < wt && t + 32 < M);
                         uint32_t r[32];
                         tmem_ld16(t_base + (uint32_t)c, r);
                         tmem_ld16(t_base + (uint32_t)c + 16u, r + 16);
@@ -850,7 +852,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
                     }
                 } else {
 #pragma unroll 1
-                for (int c = 0; c < BNT; c += 32) {
+                for (int c = 0; c < wt; c += 32) {
                     if (t0 + c >= M) break;                     // uniform over the four warps
                     uint32_t r[32];
                     tmem_ld16(t_base + (uint32_t)c, r);
@@ -896,6 +898,14 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_pair_kernel(
     cluster_sync_all();
 }
 
+// Width in tokens of the pair kernel's tiles for M tokens and room for `bnt`: as many tiles as whole ones
+// would take, equally wide, a multiple of 32 (the epilogue's round).  Each CTA's box of token rows is half of it.
+static int tc_pair_tile_tokens(int M, int bnt) {
+    const int tiles = (M + bnt - 1) / bnt;
+    const int wt = ((M + tiles - 1) / tiles + 31) / 32 * 32;
+    return wt < bnt ? wt : bnt;
+}
+
 template <int BNT, typename OutT, bool GATED = false, bool ROPE = false>
 static int launch_tc_pair(const CUtensorMap& map_w, const CUtensorMap& map_a, void* C, long ldc, int M, int N,
                           int K, int num_sms, int* status, cudaStream_t stream, int gate_rows = 0, int splits = 1,
@@ -913,7 +923,8 @@ static int launch_tc_pair(const CUtensorMap& map_w, const CUtensorMap& map_a, vo
         configured = true;
     }
     const int tiles_n = GATED ? (N + 127) / 128 : (N + 255) / 256;
-    const int num_tiles = tiles_n * ((M + BNT - 1) / BNT);
+    const int wt = tc_pair_tile_tokens(M, BNT);
+    const int num_tiles = tiles_n * ((M + wt - 1) / wt);
     const long num_units = (long)num_tiles * splits;
     const int pairs = num_units < num_sms / 2 ? (int)num_units : num_sms / 2;
     if (splits == 1) kb_per_split = (K + TC_BK - 1) / TC_BK;
@@ -931,7 +942,7 @@ static int launch_tc_pair(const CUtensorMap& map_w, const CUtensorMap& map_a, vo
     // Launched in plain stream order (no programmatic overlap with its neighbours): see the note in the kernel.
     cfg.numAttrs = 1;
     return (int)cudaLaunchKernelEx(&cfg, kernel, map_w, map_a, (OutT*)C, ldc, M, N, K, tiles_n, num_tiles, status,
-                                   gate_rows, splits, kb_per_split, partial, ld_partial, rope, wp);
+                                   gate_rows, splits, kb_per_split, partial, ld_partial, rope, wp, wt);
 }
 
 template <typename OutT>
@@ -1180,7 +1191,7 @@ static int gemm_tc_impl(const void* A, long lda, const void* W, long ldw, void* 
     const bool paired = bn >= 512;                           // 512, 640, 576: pair kernel, 256 / 128 / 64 tokens wide
     const int bnt = bn == 512 ? 256 : bn - 512;
     if (paired && (num_sms < 2 || (bnt != 64 && bnt != 128 && bnt != 256))) return (int)cudaErrorInvalidValue;
-    rc = make_map(&map_a, A, M, K, lda, paired ? bnt / 2 : bn);
+    rc = make_map(&map_a, A, M, K, lda, paired ? tc_pair_tile_tokens(M, bnt) / 2 : bn);
     if (rc) return rc;
     if (paired) {                                            // each CTA of a pair loads half of the token rows
         float* part = splits > 1 ? workspace : nullptr;
@@ -1246,7 +1257,7 @@ FL_API int fl_gemm_tc_swiglu(const void* A, long lda, const void* W, long ldw, v
     int rc = make_w_map(&map_w, W, 2L * I, K, ldw, feat);           // boxes of `feat` weight rows
     if (rc) return rc;
     const int wp = ldw == 0 ? 2 * I : 0;
-    rc = make_map(&map_a, A, M, K, lda, bn > 256 ? TC_BM : bn);
+    rc = make_map(&map_a, A, M, K, lda, bn > 256 ? tc_pair_tile_tokens(M, 256) / 2 : bn);
     if (rc) return rc;
     if (bn == 512)
         return launch_tc_pair<256, bf16, true>(map_w, map_a, C, ldc, M, I, K, num_sms, status, stream, I, 1, 0, nullptr, 0, nullptr, wp);
@@ -1284,7 +1295,7 @@ FL_API int fl_gemm_tc_qkv_rope(const void* A, long lda, const void* W, long ldw,
     int rc = make_w_map(&map_w, W, N, K, ldw, TC_BM);
     if (rc) return rc;
     const int wp = ldw == 0 ? N : 0;
-    rc = make_map(&map_a, A, M, K, lda, bnt / 2);
+    rc = make_map(&map_a, A, M, K, lda, tc_pair_tile_tokens(M, bnt) / 2);
     if (rc) return rc;
     TcRope rope = {positions, slots, cos_table, sin_table, (bf16*)k_cache, (bf16*)v_cache, page_stride, page_size,
                    n_heads, n_kv_heads};

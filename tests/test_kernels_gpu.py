@@ -563,7 +563,9 @@ def test_gate_up_product_with_swiglu_epilogue_declines_split_problems():
     assert torch.all(out == -5.0)
 
 
-@pytest.mark.parametrize("m, n, k", [(256, 256, 64), (300, 515, 200), (1024, 768, 1032), (257, 130, 72), (2048, 1024, 512)])
+# (the later shapes: token counts whose equally wide tiles are 96, 192, 160, 192 and 224 tokens wide)
+@pytest.mark.parametrize("m, n, k", [(256, 256, 64), (300, 515, 200), (1024, 768, 1032), (257, 130, 72), (2048, 1024, 512),
+                                     (97, 130, 72), (161, 515, 200), (385, 515, 200), (520, 300, 136), (673, 257, 72)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_tensor_core_gemm_cta_pairs(m, n, k, out_dtype):
     """The kernel in which two CTAs issue one 256 x 256 MMA together (cta_group::2), forced."""
