@@ -1130,38 +1130,84 @@ static void plan_one_tile(int M, int N, int K, int num_sms, int* bn_out, int* sp
     *splits_out = splits;
 }
 
-// The plan for a product: up to 64 tokens the one-tile kernel (it overlaps with its
-// neighbours in the stream, which counts most for the short kernels of a decode step);
-// above that the CTA-pair kernel, reported as 512 + its token-tile width (640: 128
-// tokens wide) or plain 512 for 256 tokens.  Its K splits come from a small cost model
-// in microseconds, fitted to measurements on B200: a pair spends 0.28 us on a 64-deep
-// K step of either tile width and about 1 us between units; partial sums cost their
-// bytes once out and once back in at about 3 TB/s.
-FL_API void fl_gemm_tc_plan(int M, int N, int K, int num_sms, int* bn_out, int* splits_out) {
+// Modelled microseconds of a product [M, K] x [N, K]^T run as (bn, splits): bn 64, 128, 256: the one-tile
+// kernel with that token tile; 512, 640: the CTA-pair kernel, 256 or 128 tokens wide.  `deferred`: the
+// partial sums of a split K are left to the consumer kernel, which adds them as it reads them; else a reduce
+// kernel follows.  The constants were fitted (least squares on the logarithm) to event-timed runs of every
+// candidate on B200 for 12 weight shapes of 2048 to 102400 features and 2048 to 22016 inputs at 80 to 768
+// tokens: 8 % root-mean-square error, and the candidate the model picks is within 1.6 % of the best one on
+// average (15 % at worst).  One-tile CTAs cost a fixed start plus a time per 64-deep K step that is a fifth
+// shorter when a CTA has its SM to itself; a pair costs a fixed 7.3 us a launch and 0.28 to 0.31 us a K step;
+// no product is faster than its operands stream from memory; partial sums cost their bytes.
+static double tc_cost(int M, int N, int K, int num_sms, int bn, int splits, int deferred) {
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const int per = (num_kb + splits - 1) / splits;
+    double t;
+    if (bn >= 512) {
+        const int bnt = bn == 512 ? 256 : bn - 512;
+        const long units = (long)((N + 255) / 256) * ((M + bnt - 1) / bnt) * splits;
+        const long pairs = num_sms / 2;
+        const long rounds = (units + pairs - 1) / pairs;
+        t = 7.29 + (double)rounds * per * (bnt == 256 ? 0.312 : 0.283);
+    } else {
+        const long ctas = (long)((N + TC_BM - 1) / TC_BM) * ((M + bn - 1) / bn) * splits;
+        const long slots = (bn <= 128 ? 2L : 1L) * num_sms;
+        const long rounds = (ctas + slots - 1) / slots;
+        const double start = bn == 64 ? 2.11 : (bn == 128 ? 1.95 : 4.11);
+        const double step = bn == 64 ? 0.374 : (bn == 128 ? 0.481 : 0.398);
+        double load = 1.0;
+        if (bn <= 128) {
+            const double per_sm = (double)ctas / rounds / num_sms;    // CTAs on an SM in a round
+            if (per_sm <= 1.0) load = 0.80 + 0.20 * per_sm;
+        }
+        t = (double)rounds * (start + per * step * load);
+    }
+    const double stream = ((double)N * K + (double)M * K) * 2.0 / 6.01e6 + 3.0;
+    if (t < stream) t = stream;
+    if (splits > 1) {
+        const double slab_mb = (double)splits * M * N * 4.0 / 1.0e6;
+        t += deferred ? slab_mb / 3.88 : 1.31 + slab_mb / 1.70;
+    }
+    return t;
+}
+
+// The plan for a product: up to 64 tokens the one-tile kernel (it overlaps with its neighbours in the
+// stream, which counts most for the short kernels of a decode step), with the smallest tile that holds
+// the tokens and K split until every SM has a CTA or two; above 64 tokens the cheapest candidate by
+// tc_cost: the one-tile kernel with 64-, 128- or 256-token tiles (up to 1024 tokens; it has four times
+// the CTAs of the pair kernel, which small weight matrices need) or the CTA-pair kernel (reported as 512:
+// 256 tokens wide, or 640: 128 wide, for at most 128 tokens), each with 1 to 16 K splits of at least four
+// k-blocks.  Of equally cheap candidates the one with fewer splits wins.
+FL_API void fl_gemm_tc_plan_for(int M, int N, int K, int num_sms, int deferred, int* bn_out, int* splits_out) {
     if (M <= 64 || num_sms < 2) {
         plan_one_tile(M, N, K, num_sms, bn_out, splits_out);
         return;
     }
-    const int bnt = M <= 128 ? 128 : 256;
     const int num_kb = (K + TC_BK - 1) / TC_BK;
-    const long tiles = (long)((N + 255) / 256) * ((M + bnt - 1) / bnt);
-    const int pairs = num_sms / 2;
-    int best = 1;
-    double best_cost = 0.0;
-    for (int sp = 1; sp <= 16; ++sp) {
-        const int per = (num_kb + sp - 1) / sp;
-        if ((num_kb + per - 1) / per != sp) continue;           // no empty split
-        if (sp > 1 && per < 4) break;
-        const long rounds = (tiles * sp + pairs - 1) / pairs;
-        double cost = (double)rounds * (0.28 * per + 1.0);
-        if (sp > 1) cost += (double)sp * M * N * 4.0 / 3.0e6;
-        if (sp == 1 || cost < best_cost * 0.95) {               // a split has to pay for the trouble
-            best = sp;
-            best_cost = cost;
+    const int widths[4] = {M <= 128 ? 640 : 512, 64, 128, 256};
+    int best_bn = widths[0], best_sp = 1;
+    double best_cost = -1.0;
+    for (int w = 0; w < 4; ++w) {
+        const int bn = widths[w];
+        if (bn < 512 && (M > 1024 || (bn == 64 && M > 256))) continue;
+        for (int sp = 1; sp <= 16; ++sp) {
+            const int per = (num_kb + sp - 1) / sp;
+            if ((num_kb + per - 1) / per != sp) continue;           // no empty split
+            if (sp > 1 && per < 4) break;
+            const double cost = tc_cost(M, N, K, num_sms, bn, sp, deferred);
+            if (best_cost < 0.0 || cost < best_cost * 0.99) {
+                best_cost = cost;
+                best_bn = bn;
+                best_sp = sp;
+            }
         }
     }
-    *bn_out = bnt == 256 ? 512 : 512 + bnt;
-    *splits_out = best;
+    *bn_out = best_bn;
+    *splits_out = best_sp;
+}
+
+FL_API void fl_gemm_tc_plan(int M, int N, int K, int num_sms, int* bn_out, int* splits_out) {
+    fl_gemm_tc_plan_for(M, N, K, num_sms, 0, bn_out, splits_out);
 }
 
 // A: [M, K] bfloat16 with lda elements between rows; W: [N, K] bfloat16 with ldw, or packed by k-block
@@ -1175,7 +1221,7 @@ static int gemm_tc_impl(const void* A, long lda, const void* W, long ldw, void* 
                         int num_sms, int* status, cudaStream_t stream, int skip_reduce) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return (int)cudaErrorInvalidValue;
-    if (bn == 0) fl_gemm_tc_plan(M, N, K, num_sms, &bn, &splits);
+    if (bn == 0) fl_gemm_tc_plan_for(M, N, K, num_sms, skip_reduce, &bn, &splits);
     const int num_kb = (K + TC_BK - 1) / TC_BK;
     if (splits < 1 || splits > num_kb) return (int)cudaErrorInvalidValue;
     const int kb_per_split = (num_kb + splits - 1) / splits;
@@ -1287,10 +1333,12 @@ FL_API int fl_gemm_tc_qkv_rope(const void* A, long lda, const void* W, long ldw,
     if ((ldc % 8) || ((uintptr_t)C & 15) || (page_stride % 8) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
         return -1;
     const int N = (n_heads + 2 * n_kv_heads) * 128;
+    // taken when the pair kernel over whole K costs no more than the cheapest product whose partial sums the
+    // rotary kernel would add up, plus that kernel (about 3 us)
+    const int bnt = M <= 128 ? 128 : 256;
     int bn = 0, splits = 0;
-    fl_gemm_tc_plan(M, N, K, num_sms, &bn, &splits);
-    if (splits != 1 || bn < 512) return -1;
-    const int bnt = bn == 512 ? 256 : bn - 512;
+    fl_gemm_tc_plan_for(M, N, K, num_sms, 1, &bn, &splits);
+    if (tc_cost(M, N, K, num_sms, bnt == 256 ? 512 : 640, 1, 1) > tc_cost(M, N, K, num_sms, bn, splits, 1) + 3.0) return -1;
     CUtensorMap map_w, map_a;
     int rc = make_w_map(&map_w, W, N, K, ldw, TC_BM);
     if (rc) return rc;

@@ -25,6 +25,9 @@ def _lib():
         lib.fl_gemm_tc_plan.argtypes = [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int),
                                         ctypes.POINTER(c_int)]
         lib.fl_gemm_tc_plan.restype = None
+        lib.fl_gemm_tc_plan_for.argtypes = [c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(c_int),
+                                            ctypes.POINTER(c_int)]
+        lib.fl_gemm_tc_plan_for.restype = None
         lib.fl_gemm_tc_swiglu.argtypes = [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int,
                                           c_int, c_int, c_void_p, c_void_p]
         lib.fl_gemm_tc_swiglu.restype = c_int
@@ -58,13 +61,14 @@ def _num_sms(device) -> int:
 _plans: dict = {}
 
 
-def plan(m: int, n: int, k: int, num_sms: int):
-    """(token-tile width, K splits) the kernel will use for this problem."""
-    key = (m, n, k, num_sms)
+def plan(m: int, n: int, k: int, num_sms: int, deferred: bool = False):
+    """(token-tile width, K splits) the kernel will use for this problem; `deferred`: for a caller
+    that leaves the partial sums of a split K to the consumer kernel (a split is cheaper then)."""
+    key = (m, n, k, num_sms, bool(deferred))
     p = _plans.get(key)
     if p is None:
         bn, splits = c_int(0), c_int(0)
-        _lib().fl_gemm_tc_plan(m, n, k, num_sms, ctypes.byref(bn), ctypes.byref(splits))
+        _lib().fl_gemm_tc_plan_for(m, n, k, num_sms, int(bool(deferred)), ctypes.byref(bn), ctypes.byref(splits))
         p = _plans[key] = (bn.value, splits.value)
     return p
 
@@ -80,15 +84,20 @@ def _workspace(device, floats: int) -> torch.Tensor:
 
 def workspace_floats(m: int, n: int, k: int, device) -> int:
     """Floats of scratch that the product [m, k] x [n, k]^T takes (0 when its plan has no K split)."""
-    _, splits = plan(m, n, k, _num_sms(device))
-    return splits * m * (-(-n // 4) * 4) if splits > 1 else 0
+    need = 0
+    for deferred in (False, True):
+        _, splits = plan(m, n, k, _num_sms(device), deferred)
+        if splits > 1:
+            need = max(need, splits * m * (-(-n // 4) * 4))
+    return need
 
 
 def reserve(device, n: int, k: int, max_tokens: int) -> None:
-    """Size the scratch for every step of up to `max_tokens` tokens of an [n, k] weight.  The
-    plan's splits depend on the number of token tiles, so within a bracket of 64 tokens the
-    largest need is at the bracket's top: those and every count up to 64 are asked."""
-    counts = list(range(1, min(64, max_tokens) + 1)) + list(range(128, max_tokens + 64, 64))
+    """Size the scratch for every step of up to `max_tokens` tokens of an [n, k] weight.  Up to
+    1024 tokens the plan weighs candidates by a cost model, so every count is asked; above that
+    the splits depend on the number of token tiles only, and within a bracket of 64 tokens the
+    largest need is at the bracket's top."""
+    counts = list(range(1, min(1024, max_tokens) + 1)) + list(range(1088, max_tokens + 64, 64))
     need = max(workspace_floats(min(m, max_tokens), n, k, device) for m in counts)
     scratch.reserve(device, SCRATCH, need)
 
@@ -178,7 +187,7 @@ def gemm(a: torch.Tensor, w, out: torch.Tensor, bn: int = 0, splits: int = 0,
     w_ptr, ldw = _weight_args(w)
     sms = _num_sms(a.device)
     if bn == 0:
-        bn, splits = plan(m, n, k, sms)
+        bn, splits = plan(m, n, k, sms, defer)
     ws, ws_floats = None, 0
     if splits > 1:
         ws_floats = splits * m * (-(-n // 4) * 4)

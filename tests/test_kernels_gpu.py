@@ -143,8 +143,13 @@ def test_tensor_core_gemm_plan_is_launchable():
             kb = -(-k // 64)
             per = -(-kb // splits)
             assert 1 <= splits <= 16 and (splits - 1) * per < kb
-            if m > 64:
-                assert bn == (640 if m <= 128 else 512)
+            assert (bn <= 64) if m <= 64 else (bn >= 64)
+            if m > 1024:
+                assert bn == 512
+            for deferred in (False, True):
+                bn, splits = gemm_tc.plan(m, n, k, 148, deferred)
+                assert bn in (16, 32, 64, 128, 256, 512, 640) and 1 <= splits <= 16
+                assert (splits - 1) * -(-kb // splits) < kb
 
 
 @pytest.mark.parametrize("a_dt, w_dt, c_dt", [(torch.float32, torch.float32, torch.float32),
