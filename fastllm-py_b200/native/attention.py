@@ -203,7 +203,7 @@ def prefill_attention(q, out, cache_tensor, block_table, req_start, req_ctx, req
 
 
 def num_sms(device) -> int:
-    key = ("sms", str(device))
+    key = ("sms", device)
     if key not in _state:
         _state[key] = torch.cuda.get_device_properties(device).multi_processor_count
     return _state[key]

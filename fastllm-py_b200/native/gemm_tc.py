@@ -45,14 +45,21 @@ def _lib():
 
 def status_word(device) -> torch.Tensor:
     """The int32 word in which kernels of this process record a fault (0 = none)."""
-    key = ("status", str(device))
-    if key not in _state:
-        _state[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _state[key]
+    key = ("status", device)
+    word = _state.get(key)
+    if word is None:
+        device = torch.device(device)
+        if device.type == "cuda" and device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        word = _state.get(("status", device))
+        if word is None:
+            word = _state[("status", device)] = torch.zeros(1, dtype=torch.int32, device=device)
+        _state[key] = word                                # the same word under every spelling of the device
+    return word
 
 
 def _num_sms(device) -> int:
-    key = ("sms", str(device))
+    key = ("sms", device)
     if key not in _state:
         _state[key] = torch.cuda.get_device_properties(device).multi_processor_count
     return _state[key]
@@ -147,10 +154,10 @@ class Partial:
         self.data, self.splits, self.rows, self.cols, self.ld = data, splits, rows, cols, ld
         self.split_stride = rows * ld
         self.device = device
-        self.serial = _state.get(("serial", str(device)), 0)
+        self.serial = _state.get(("serial", device), 0)
 
     def check(self):
-        if self.serial != _state.get(("serial", str(self.device)), 0):
+        if self.serial != _state.get(("serial", self.device), 0):
             raise RuntimeError("split-K partial sums were overwritten by a later product before use")
 
     def reduce_into(self, out: torch.Tensor) -> torch.Tensor:
@@ -196,7 +203,7 @@ def gemm(a: torch.Tensor, w, out: torch.Tensor, bn: int = 0, splits: int = 0,
     deferred = defer and splits > 1
     fn = _lib().fl_gemm_tc_partial if deferred else _lib().fl_gemm_tc
     if splits > 1:
-        serial_key = ("serial", str(a.device))
+        serial_key = ("serial", a.device)
         _state[serial_key] = _state.get(serial_key, 0) + 1    # earlier Partials are now stale
     rc = fn(ops._ptr(a), lda, w_ptr, ldw, ops._ptr(out), ops.dtype_code(out), ldc,
             m, n, k, bn, splits, ops._ptr(ws), ws_floats, sms,

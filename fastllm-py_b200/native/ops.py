@@ -81,17 +81,25 @@ def _require_cuda(*tensors):
             raise KernelError("the engine's kernels run on a CUDA device only; got a CPU tensor")
 
 
-_sigs_done: set = set()
+_fns: dict = {}
 
 
 def _fn(lib_name: str, fn_name: str, argtypes, defines=None):
-    lib = load_library(lib_name, defines)
-    fn = getattr(lib, fn_name)
+    """The launcher `fn_name` of a library with its signature set, looked up once (a step calls
+    these wrappers a few hundred times and is short of host time when its kernels are small)."""
+    if defines is None:
+        fn = _fns.get(fn_name)
+        if fn is not None:
+            return fn
     key = (lib_name, tuple(sorted((defines or {}).items())), fn_name)
-    if key not in _sigs_done:
+    fn = _fns.get(key)
+    if fn is None:
+        fn = getattr(load_library(lib_name, defines), fn_name)
         fn.argtypes = argtypes
         fn.restype = c_int
-        _sigs_done.add(key)
+        _fns[key] = fn
+        if defines is None:
+            _fns[fn_name] = fn
     return fn
 
 

@@ -77,6 +77,36 @@ def test_product_plans_without_a_gpu():
     assert gemm_tc.plan(8, 4096, 4096, 148)[1] > 1 and gemm_tc.plan(8, 102400, 4096, 148)[1] == 1
 
 
+def test_product_plan_against_timed_candidates():
+    """tests/data/gemm_candidates_b200.jsonl holds event-timed runs of every candidate (kernel, token tile,
+    K splits; reduce kernel or partial sums left to the consumer) for 149 problems of 80 to 1024 tokens on a
+    B200 (tests/data/measure_gemm_candidates.py made it).  The plan's pick must be close to the fastest
+    measured candidate: within 3 % on average, never more than 40 % off."""
+    import json
+    import shutil
+    from pathlib import Path
+
+    import pytest
+
+    if shutil.which("nvcc") is None:
+        pytest.skip("no CUDA compiler here")
+    from fastllm_py_b200.native import gemm_tc
+
+    records = [json.loads(line) for line in open(Path(__file__).parent / "data" / "gemm_candidates_b200.jsonl")]
+    assert len(records) > 100
+    for deferred in (False, True):
+        col = 3 if deferred else 2
+        ratios = []
+        for r in records:
+            bn, splits = gemm_tc.plan(r["m"], r["n"], r["k"], 148, deferred)
+            timed = [c[col] for c in r["cands"] if c[0] == bn and c[1] == splits]
+            if timed:                                   # (5 and 7 splits were not among the timed ones)
+                ratios.append(timed[0] / min(c[col] for c in r["cands"]))
+        assert len(ratios) > 0.9 * len(records)
+        assert sum(ratios) / len(ratios) <= 1.03, (deferred, sum(ratios) / len(ratios))
+        assert max(ratios) <= 1.40, (deferred, max(ratios))
+
+
 def test_make_model_command_writes_a_loadable_folder(tmp_path):
     """The random-weights mode from the command line: a config.json in, a model folder out whose
     tensors are exactly what the architecture expects, the same for the same seed."""
