@@ -100,6 +100,47 @@ def test_page_pressure_changes_no_output(model_folders):
     assert not tight.engine.cache.live
 
 
+@pytest.mark.parametrize("name, seed", [("tiny_a", 1), ("tiny_b", 2), ("tiny_c", 3)])
+def test_random_arrivals_under_random_settings(name, seed, model_folders):
+    """Requests of random lengths that arrive while others run, under settings drawn at random: the page
+    size, a pool of little more than the longest request (so that running requests are pushed out and
+    recomputed), the number of live requests, the token budget, graphs and running ahead on or off.
+    Greedy, float32: every output is the plain implementation's."""
+    from fastllm_py_b200 import Model
+
+    cfg = tiny.CONFIGS[name]["config"]
+    weights, config = plain.load_folder(model_folders[name])
+    rng = np.random.default_rng(seed)
+    max_len = min(cfg.max_position_embeddings, 160)
+    page = int(rng.choice([8, 16, 32]))
+    requests = []
+    for _ in range(int(rng.integers(8, 14))):
+        new = int(rng.integers(1, 60))
+        requests.append((rng.integers(0, cfg.vocab_size, size=int(rng.integers(1, max_len - new))).tolist(), new))
+    pages_one = -(-max(len(p) + n for p, n in requests) // page)
+    pool_pages = pages_one + int(rng.integers(0, max(2, pages_one)))
+    budget = int(rng.choice([13, 32, 64]))
+    model = Model.load(model_folders[name], dtype="float32", page_size=page, max_tokens=pool_pages * page,
+                       max_requests=int(rng.integers(2, 7)), max_batched_tokens=max(budget, 16),
+                       max_model_len=max_len, cuda_graph=bool(rng.random() < 0.6), check_cache=True)
+    sched = model.scheduler(token_budget=budget, run_ahead=bool(rng.random() < 0.7))
+    waiting, ids, outs, steps = list(enumerate(requests)), {}, {}, 0
+    while waiting or sched.has_work():
+        while waiting and (rng.random() < 0.4 or not sched.has_work()):
+            i, (prompt, new) = waiting.pop(0)
+            ids[sched.add_request(prompt, new)] = i
+        for o in sched.step():
+            if o.finished:
+                outs[ids[o.request_id]] = list(sched.finished[o.request_id].output)
+        steps += 1
+        assert steps < 5000, "the scheduler makes no progress"
+    model.engine.check_status()
+    model.engine.cache.check()
+    assert not model.engine.cache.live
+    for i, (prompt, new) in enumerate(requests):
+        assert outs[i] == plain.generate(weights, config, prompt, new), f"request {i} of {name}"
+
+
 def near_tie_follows(weights, config, prompt, got):
     """bfloat16 greedy tokens follow the plain bfloat16-storage model; where the two part ways
     the plain model's two best logits must be nearly tied (within twice the storage noise)."""
@@ -225,10 +266,13 @@ def test_graphs_captured_before_a_scratch_buffer_grew_are_not_replayed(model_fol
     eager = small.generate(prompts, max_new_tokens=20, use_graph=False)
     assert small.generate(prompts, max_new_tokens=20) == eager
     assert len(small.engine._graphs) >= 1
-    before = scratch.generation(small.engine.device)
-    # ask for more than any engine so far has reserved
+    # ask for more than any engine so far has reserved (a buffer that nobody has needed yet is made first:
+    # making one is no growth)
     dev = small.engine.device
     from fastllm_py_b200.native import attention, gemm_tc
+    for buf in (gemm_tc.SCRATCH, attention.SCRATCH):
+        scratch.get(dev, buf, 1)
+    before = scratch.generation(dev)
     scratch.get(dev, gemm_tc.SCRATCH, scratch.size(dev, gemm_tc.SCRATCH) + 1)
     scratch.get(dev, attention.SCRATCH, scratch.size(dev, attention.SCRATCH) + 1)
     assert scratch.generation(dev) == before + 2
