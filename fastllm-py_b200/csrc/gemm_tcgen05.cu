@@ -353,6 +353,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
             const uint32_t t_base = tmem_acc + ((uint32_t)(quarter * 32) << 16);
             const int t0 = tile_m * BN;
             float* xch = reinterpret_cast<float*>(tiles);            // [2][16 tokens][128 rows]
+            const bool vec_ok = (((uintptr_t)C | (uintptr_t)(ldc * (long)sizeof(OutT))) & 15) == 0;
             if (ok) {
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
@@ -368,11 +369,25 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(
                     }
                     epilogue_sync();
                     const int rows = min(16, M - (t0 + c));
-                    for (int i = row; i < rows * feat; i += 128) {
-                        const int t = i / feat, f = i - t * feat;
-                        if (f0 + f < N)
-                            C[(long)(t0 + c + t) * ldc + f0 + f] =
-                                from_f32<OutT>(gated_act(x[t * TC_BM + f], x[t * TC_BM + feat + f]));
+                    // a thread finishes eight neighbouring features of one token and stores them as 16 bytes
+                    // (feat is a multiple of 8, so 16 tokens x feat / 8 such pieces are at most one a thread)
+                    const int pieces = feat >> 3;
+                    const int t = row / pieces, f = (row - t * pieces) << 3;
+                    if (t < rows && f0 + f < N) {
+                        const float* xg = x + t * TC_BM + f;
+                        OutT* dst = C + (long)(t0 + c + t) * ldc + f0 + f;
+                        if (sizeof(OutT) == 2 && vec_ok && f0 + f + 8 <= N) {
+                            const float4 g0 = *reinterpret_cast<const float4*>(xg), g1 = *reinterpret_cast<const float4*>(xg + 4);
+                            const float4 u0 = *reinterpret_cast<const float4*>(xg + feat), u1 = *reinterpret_cast<const float4*>(xg + feat + 4);
+                            const OutT v[8] = {from_f32<OutT>(gated_act(g0.x, u0.x)), from_f32<OutT>(gated_act(g0.y, u0.y)),
+                                               from_f32<OutT>(gated_act(g0.z, u0.z)), from_f32<OutT>(gated_act(g0.w, u0.w)),
+                                               from_f32<OutT>(gated_act(g1.x, u1.x)), from_f32<OutT>(gated_act(g1.y, u1.y)),
+                                               from_f32<OutT>(gated_act(g1.z, u1.z)), from_f32<OutT>(gated_act(g1.w, u1.w))};
+                            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(v);
+                        } else {
+                            for (int j = 0; j < 8 && f0 + f + j < N; ++j)
+                                dst[j] = from_f32<OutT>(gated_act(xg[j], xg[feat + j]));
+                        }
                     }
                 }
             }
