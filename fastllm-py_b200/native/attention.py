@@ -43,6 +43,9 @@ def tc_prefill_takes(head_dim: int, page_size: int) -> bool:
         and 128 % page_size == 0
 
 
+_launches: dict = {}        # operands' places and sizes -> (launcher, converted arguments): see prefill_attention
+
+
 def _decode_lib(head_dim: int):
     key = ("decode", head_dim)
     lib = _libs.get(key)
@@ -177,19 +180,31 @@ def prefill_attention(q, out, cache_tensor, block_table, req_start, req_ctx, req
                       variant=0):
     """Tensor-core attention for the requests of the step that bring several tokens.
     variant 0 chooses: the tcgen05 kernel where it applies (2), else mma.sync (1)."""
+    # (the same operands in the same places: launched from what the first such call converted; see gemm_tc.gemm)
+    key = (q.data_ptr(), q.shape, q.stride(0), q.dtype, out.data_ptr(), out.stride(0), cache_tensor.data_ptr(),
+           cache_tensor.shape, cache_tensor.stride(0), block_table.data_ptr(), block_table.stride(0),
+           req_start.data_ptr(), req_ctx.data_ptr(), req_qlen.data_ptr(), n_requests, n_tokens, include_single,
+           heads, kv_heads, head_dim, window, scale, page_size, variant)
+    known = _launches.get(key)
+    if known is not None:
+        ops._check(known[0](*known[1], ops._stream()), "attention_prefill_tc")
+        return
     if variant == 0:
         variant = 2 if tc_prefill_takes(head_dim, page_size) and cache_tensor.is_contiguous() else 1
     if variant == 2:
         from .gemm_tc import status_word
 
-        lib = _prefill_tc_lib(head_dim)
-        rc = lib.fl_attention_prefill_tc(ops._ptr(q), ops._ld(q), ops._ptr(out), ops._ld(out),
-                                         ops._ptr(cache_tensor), cache_tensor.shape[0], page_size,
-                                         ops._ptr(block_table), block_table.stride(0), ops._ptr(req_start),
-                                         ops._ptr(req_ctx), ops._ptr(req_qlen), n_requests, n_tokens,
-                                         1 if include_single else 0, heads, kv_heads, int(window or 0),
-                                         float(scale), ops._ptr(status_word(q.device)), ops._stream())
-        ops._check(rc, "attention_prefill_tc")
+        fn = _prefill_tc_lib(head_dim).fl_attention_prefill_tc
+        args = (ops._ptr(q), ops._ld(q), ops._ptr(out), ops._ld(out),
+                ops._ptr(cache_tensor), cache_tensor.shape[0], page_size,
+                ops._ptr(block_table), block_table.stride(0), ops._ptr(req_start),
+                ops._ptr(req_ctx), ops._ptr(req_qlen), n_requests, n_tokens,
+                1 if include_single else 0, heads, kv_heads, int(window or 0),
+                float(scale), ops._ptr(status_word(q.device)))
+        ops._check(fn(*args, ops._stream()), "attention_prefill_tc")
+        if len(_launches) > 8192:
+            _launches.clear()
+        _launches[key] = (fn, args)
         return
     lib = _prefill_lib(head_dim)
     k_ptr = c_void_p(cache_tensor.data_ptr())

@@ -172,6 +172,27 @@ class Partial:
         return out
 
 
+_launches: dict = {}        # operands' places and sizes -> (launcher, converted arguments, ...): see gemm
+_scratch_seen: dict = {}    # device -> the scratch generation the remembered launches belong to
+
+
+def _forget_if_scratch_moved(device) -> None:
+    """Remembered launches hold the scratch buffer's address (and the Partial handed out for it):
+    none of them survives a buffer that was replaced."""
+    gen = scratch.generation(device)
+    if _scratch_seen.get(device) != gen:
+        _launches.clear()
+        _scratch_seen[device] = gen
+
+
+def _remember(key, launch) -> None:
+    """Only addresses and sizes are kept, no tensor (but the scratch buffer inside a Partial): memory
+    that is freed and handed out again under a remembered address gets the same launch, rightly."""
+    if len(_launches) > 8192:           # (a few hundred in practice: layers x products x step sizes met)
+        _launches.clear()
+    _launches[key] = launch
+
+
 def gemm(a: torch.Tensor, w, out: torch.Tensor, bn: int = 0, splits: int = 0,
          defer: bool = False):
     """out[M, N] = a[M, K] @ w[N, K]^T; a and w bfloat16 (row pitch a multiple of 8
@@ -179,6 +200,23 @@ def gemm(a: torch.Tensor, w, out: torch.Tensor, bn: int = 0, splits: int = 0,
 
     With `defer`, a product whose K is split returns a Partial instead of
     writing `out`: its consumer adds the slabs while it reads them."""
+    # A product asked for again with the same operands in the same places (a layer's buffers do not move
+    # from step to step) is launched from what the first call worked out: the checks, the plan and the
+    # argument conversions below cost more host time than the driver's launch.
+    _forget_if_scratch_moved(a.device)
+    key = (a.data_ptr(), a.shape, a.stride(0), a.dtype, w.data_ptr(), w.shape, out.data_ptr(), out.shape,
+           out.stride(0), out.dtype, bn, splits, defer)
+    known = _launches.get(key)
+    if known is not None:
+        fn, args, kernels, partial = known
+        if partial is not None:
+            serial_key = ("serial", a.device)
+            partial.serial = _state[serial_key] = _state.get(serial_key, 0) + 1
+        elif kernels == 2:
+            serial_key = ("serial", a.device)
+            _state[serial_key] = _state.get(serial_key, 0) + 1
+        ops._check(fn(*args, ops._stream()), "gemm_tcgen05", kernels)
+        return partial
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise ops.KernelError("tensor-core gemm takes bfloat16 operands")
     m, k = a.shape
@@ -205,19 +243,27 @@ def gemm(a: torch.Tensor, w, out: torch.Tensor, bn: int = 0, splits: int = 0,
     if splits > 1:
         serial_key = ("serial", a.device)
         _state[serial_key] = _state.get(serial_key, 0) + 1    # earlier Partials are now stale
-    rc = fn(ops._ptr(a), lda, w_ptr, ldw, ops._ptr(out), ops.dtype_code(out), ldc,
-            m, n, k, bn, splits, ops._ptr(ws), ws_floats, sms,
-            ops._ptr(status_word(a.device)), ops._stream())
-    ops._check(rc, "gemm_tcgen05", 2 if (splits > 1 and not deferred) else 1)
-    if deferred:
-        return Partial(ws, splits, m, n, -(-n // 4) * 4, a.device)
-    return None
+    args = (ops._ptr(a), lda, w_ptr, ldw, ops._ptr(out), ops.dtype_code(out), ldc,
+            m, n, k, bn, splits, ops._ptr(ws), ws_floats, sms, ops._ptr(status_word(a.device)))
+    kernels = 2 if (splits > 1 and not deferred) else 1
+    ops._check(fn(*args, ops._stream()), "gemm_tcgen05", kernels)
+    partial = Partial(ws, splits, m, n, -(-n // 4) * 4, a.device) if deferred else None
+    _remember(key, (fn, args, kernels, partial))
+    return partial
 
 
 def gemm_swiglu(a: torch.Tensor, w, out: torch.Tensor) -> bool:
     """out[M, I] = silu(a @ gate^T) * (a @ up^T) for w = [gate; up] stacked as [2 I, K], all
     bfloat16, in one kernel (the activation in the product's epilogue).  Returns False, having
     done nothing, when the kernel does not take the problem (its plan splits K)."""
+    key = ("swiglu", a.data_ptr(), a.shape, a.stride(0), a.dtype, w.data_ptr(), w.shape, out.data_ptr(), out.shape,
+           out.stride(0), out.dtype)
+    known = _launches.get(key)                              # (see gemm)
+    if known is not None:
+        if known is False:
+            return False
+        ops._check(known[0](*known[1], ops._stream()), "gemm_tcgen05 (gated)")
+        return True
     m, k = a.shape
     inter = w.shape[0] // 2
     if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16
@@ -233,11 +279,15 @@ def gemm_swiglu(a: torch.Tensor, w, out: torch.Tensor) -> bool:
         w_ptr, ldw = _weight_args(w)
     except ops.KernelError:
         return False
-    rc = _lib().fl_gemm_tc_swiglu(ops._ptr(a), lda, w_ptr, ldw, ops._ptr(out), ops._ld(out), m, inter, k,
-                                  _num_sms(a.device), ops._ptr(status_word(a.device)), ops._stream())
+    fn = _lib().fl_gemm_tc_swiglu
+    args = (ops._ptr(a), lda, w_ptr, ldw, ops._ptr(out), ops._ld(out), m, inter, k,
+            _num_sms(a.device), ops._ptr(status_word(a.device)))
+    rc = fn(*args, ops._stream())
     if rc == -1:
+        _remember(key, False)
         return False
     ops._check(rc, "gemm_tcgen05 (gated)")
+    _remember(key, (fn, args))
     return True
 
 
@@ -250,6 +300,15 @@ def gemm_qkv_rope(a: torch.Tensor, w, q_out: torch.Tensor, n_heads: int, n_kv_he
     w = [q; k; v] stacked as [(n_heads + 2 n_kv_heads) * head_dim, K], all bfloat16.  Returns False,
     having done nothing, when the kernel does not take the problem (heads not of 128 rotated in full,
     64 tokens or fewer, a plan that splits K)."""
+    key = ("qkv", a.data_ptr(), a.shape, a.stride(0), a.dtype, w.data_ptr(), w.shape, q_out.data_ptr(), q_out.shape,
+           q_out.stride(0), q_out.dtype, n_heads, n_kv_heads, head_dim, rot_dim, cos.data_ptr(), sin.data_ptr(),
+           cos.shape, positions.data_ptr(), slots.data_ptr(), cache.data_ptr(), cache.shape, cache.dtype, page_size)
+    known = _launches.get(key)                              # (see gemm)
+    if known is not None:
+        if known is False:
+            return False
+        ops._check(known[0](*known[1], ops._stream()), "gemm_tcgen05 (q|k|v with rotary)")
+        return True
     m, k = a.shape
     if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or q_out.dtype != torch.bfloat16
             or cache.dtype != torch.bfloat16 or tuple(w.shape) != ((n_heads + 2 * n_kv_heads) * head_dim, k)
@@ -268,13 +327,17 @@ def gemm_qkv_rope(a: torch.Tensor, w, q_out: torch.Tensor, n_heads: int, n_kv_he
         return False
     k_ptr = c_void_p(cache.data_ptr())
     v_ptr = c_void_p(cache.data_ptr() + cache.stride(1) * cache.element_size())
-    rc = _lib().fl_gemm_tc_qkv_rope(ops._ptr(a), lda, w_ptr, ldw, ops._ptr(q_out), ops._ld(q_out), m, k,
-                                    n_heads, n_kv_heads, head_dim, rot_dim, ops._ptr(positions), ops._ptr(slots),
-                                    ops._ptr(cos), ops._ptr(sin), k_ptr, v_ptr, cache.stride(0), page_size,
-                                    _num_sms(a.device), ops._ptr(status_word(a.device)), ops._stream())
+    fn = _lib().fl_gemm_tc_qkv_rope
+    args = (ops._ptr(a), lda, w_ptr, ldw, ops._ptr(q_out), ops._ld(q_out), m, k,
+            n_heads, n_kv_heads, head_dim, rot_dim, ops._ptr(positions), ops._ptr(slots),
+            ops._ptr(cos), ops._ptr(sin), k_ptr, v_ptr, cache.stride(0), page_size,
+            _num_sms(a.device), ops._ptr(status_word(a.device)))
+    rc = fn(*args, ops._stream())
     if rc == -1:
+        _remember(key, False)
         return False
     ops._check(rc, "gemm_tcgen05 (q|k|v with rotary)")
+    _remember(key, (fn, args))
     return True
 
 

@@ -82,6 +82,7 @@ def _require_cuda(*tensors):
 
 
 _fns: dict = {}
+_launches: dict = {}        # operands' places and sizes -> (launcher, converted arguments) of wrappers that remember
 
 
 def _fn(lib_name: str, fn_name: str, argtypes, defines=None):
@@ -143,14 +144,27 @@ def add_rmsnorm(resid, delta, weight, out, eps, rows=None):
 
 def add_rmsnorm_partial(resid, partial, weight, out, eps):
     """resid += (split-K partial sums, added in slab order); out = rmsnorm(resid) * weight."""
-    _require_cuda(resid, weight, out)
     partial.check()
+    # (the same operands in the same places, as in every layer of every step of a size: launched from
+    # what the first such call converted; see gemm_tc.gemm)
+    key = ("add_rmsnorm_partial", resid.data_ptr(), resid.shape, resid.stride(0), partial.data.data_ptr(),
+           partial.splits, partial.split_stride, partial.ld, weight.data_ptr(), weight.dtype, out.data_ptr(),
+           out.shape, out.stride(0), out.dtype, eps)
+    known = _launches.get(key)
+    if known is not None:
+        _check(known[0](*known[1], _stream()), "add_rmsnorm_partial")
+        return
+    _require_cuda(resid, weight, out)
     fn = _fn("elementwise", "fl_add_rmsnorm_partial", [c_void_p, c_long, c_void_p, c_int, c_long, c_long,
                                                        c_void_p, c_int, c_void_p, c_int, c_long, c_int,
                                                        c_int, c_float, c_void_p])
-    _check(fn(_ptr(resid), _ld(resid), _ptr(partial.data), partial.splits, partial.split_stride,
-              partial.ld, _ptr(weight), dtype_code(weight), _ptr(out), dtype_code(out), _ld(out),
-              out.shape[0], resid.shape[1], float(eps), _stream()), "add_rmsnorm_partial")
+    args = (_ptr(resid), _ld(resid), _ptr(partial.data), partial.splits, partial.split_stride,
+            partial.ld, _ptr(weight), dtype_code(weight), _ptr(out), dtype_code(out), _ld(out),
+            out.shape[0], resid.shape[1], float(eps))
+    _check(fn(*args, _stream()), "add_rmsnorm_partial")
+    if len(_launches) > 8192:
+        _launches.clear()
+    _launches[key] = (fn, args)
 
 
 def swiglu_partial(partial, out):

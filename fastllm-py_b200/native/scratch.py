@@ -27,8 +27,14 @@ _buffers: dict = {}          # (device, name) -> float32 tensor
 _generation: dict = {}       # device -> int
 
 
+_keys: dict = {}             # any spelling of a device -> its key below (str() of a device is slow)
+
+
 def _key(device) -> str:
-    return str(torch.device(device))
+    key = _keys.get(device)
+    if key is None:
+        key = _keys[device] = str(torch.device(device))
+    return key
 
 
 def generation(device) -> int:

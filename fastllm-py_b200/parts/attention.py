@@ -121,6 +121,7 @@ class Attention(Part):
         if cache.writes == self.shares_cache:
             raise RuntimeError("attention: the run's cache and the layer's shares_cache disagree")
         qkv = step.workspace.rows("qkv", n, cols, dt)
+        queries = qkv if cols == q_cols else step.workspace.rows("qkv", n, cols, dt, first=q_cols)
         if self.position is not None:
             cos, sin = self.position.tables()
             rot = self.position.rot_dim
@@ -129,7 +130,7 @@ class Attention(Part):
         kv_cache = cache.tensor if cache.writes else None
         # prompt-sized steps of a layer with heads of 128: product, rotation and cache write in one kernel
         fused = kv_cache is not None and rot == self.head_dim and self.qkv.forward_qkv_rope(
-            h, qkv[:, :q_cols], self.heads, self.kv_heads, self.head_dim, rot, cos, sin, step.positions,
+            h, queries, self.heads, self.kv_heads, self.head_dim, rot, cos, sin, step.positions,
             cache.slots, kv_cache, cache.page_size)
         if not fused:
             partial = self.qkv.forward(h, qkv, defer=True)
@@ -137,11 +138,11 @@ class Attention(Part):
                 ops.rope_kv_write(qkv, self.heads, self.kv_heads, self.head_dim, rot, cos, sin,
                                   step.positions, cache.slots, kv_cache, cache.page_size)
             else:
-                ops.rope_kv_write_partial(partial, qkv[:, :q_cols], self.heads, self.kv_heads, self.head_dim,
+                ops.rope_kv_write_partial(partial, queries, self.heads, self.kv_heads, self.head_dim,
                                           rot, cos, sin, step.positions, cache.slots, kv_cache,
                                           cache.page_size)
         ctx = step.workspace.rows("attn_ctx", n, q_cols, dt)
-        self.attend(qkv[:, :q_cols], ctx, step, cache)
+        self.attend(queries, ctx, step, cache)
         return self.o.forward(ctx, out, defer=True)
 
     def attend(self, q, ctx, step, cache):

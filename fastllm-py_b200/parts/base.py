@@ -119,11 +119,24 @@ class Workspace:
         self.device = device
         self.max_tokens = max_tokens
         self._buffers: dict = {}
+        self._views: dict = {}           # (name, cols, dtype, n) -> the view handed out for it before
         self.generation = 0              # bumped when a buffer is replaced by a larger one
 
-    def rows(self, name: str, n: int, cols: int, dtype, initial: int | None = None) -> torch.Tensor:
+    def rows(self, name: str, n: int, cols: int, dtype, initial: int | None = None,
+             first: int | None = None) -> torch.Tensor:
         """`initial` (for buffers that are wide but usually short, like logits)
-        starts the buffer at that many rows and lets it grow to max_tokens on demand."""
+        starts the buffer at that many rows and lets it grow to max_tokens on demand.
+        `first`: only the first so many of the `cols` columns (the same memory as the
+        whole rows: the queries of a q|k|v buffer, say)."""
+        if first is not None:
+            view = self._views.get((name, cols, dtype, n, first))
+            if view is None:
+                whole = self.rows(name, n, cols, dtype, initial)
+                view = self._views[(name, cols, dtype, n, first)] = whole[:, :first]
+            return view
+        view = self._views.get((name, cols, dtype, n))
+        if view is not None:             # (making a view costs a few microseconds: a step asks a hundred times)
+            return view
         key = (name, cols, dtype)
         buf = self._buffers.get(key)
         if n > self.max_tokens:
@@ -139,4 +152,9 @@ class Workspace:
                 self.generation += 1     # captured graphs may hold the old buffer's address
             buf = torch.zeros((cap, pitch), dtype=dtype, device=self.device)
             self._buffers[key] = buf
-        return buf[:n, :cols]
+            for k in [k for k in self._views if k[:3] == key]:
+                del self._views[k]
+        if len(self._views) > 4096:
+            self._views.clear()
+        view = self._views[(name, cols, dtype, n)] = buf[:n, :cols]
+        return view

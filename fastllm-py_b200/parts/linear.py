@@ -21,6 +21,18 @@ import torch
 from ..native import ops
 
 
+_gemm_tc_module = None
+
+
+def _gemm_tc():
+    """native/gemm_tc.py, imported when a bfloat16 product first needs it (it compiles its library)."""
+    global _gemm_tc_module
+    if _gemm_tc_module is None:
+        from ..native import gemm_tc
+        _gemm_tc_module = gemm_tc
+    return _gemm_tc_module
+
+
 class Linear:
     def __init__(self, weights: list):
         """`weights`: matrices [out_i, in] of one dtype, stacked along out."""
@@ -81,8 +93,7 @@ class Linear:
         tokens' cache slots), in one tensor-core kernel.  False (nothing done) when that kernel does
         not apply; the caller then takes `forward` and the rotary kernel."""
         if a.dtype == torch.bfloat16 and self.dtype == torch.bfloat16:
-            from ..native.gemm_tc import gemm_qkv_rope
-            return gemm_qkv_rope(a, self._tensor_core().weight, q_out, n_heads, n_kv_heads, head_dim, rot_dim,
+            return _gemm_tc().gemm_qkv_rope(a, self._tensor_core().weight, q_out, n_heads, n_kv_heads, head_dim, rot_dim,
                                  cos, sin, positions, slots, cache, page_size)
         return False
 
@@ -91,6 +102,5 @@ class Linear:
         in one tensor-core kernel.  False (nothing done) when that kernel does not apply; the
         caller then takes `forward` and the activation kernel."""
         if a.dtype == torch.bfloat16 and self.dtype == torch.bfloat16:
-            from ..native.gemm_tc import gemm_swiglu
-            return gemm_swiglu(a, self._tensor_core().weight, out)
+            return _gemm_tc().gemm_swiglu(a, self._tensor_core().weight, out)
         return False
