@@ -5,6 +5,7 @@ sums left to the consumer], ...]}.  Token tile codes as fl_gemm_tc takes them: 6
 of the weights (larger than L2 together).
 
     python tests/data/measure_gemm_candidates.py OUT.jsonl [token counts, comma separated]
+    python tests/data/measure_gemm_candidates.py --planned     # the planned products against cuBLAS, as a table
 
 gemm_candidates_b200.jsonl beside this file is its output on one B200 for the token counts 80, 128, 192, 256,
 384, 512, 768 and 96, 160, 320, 448, 640, 1024; tests/test_bench_and_loading.py holds the plan against it, and
@@ -40,7 +41,34 @@ def timed(fn, reps=10):
     return start.elapsed_time(end) * 1000 / reps
 
 
+def planned_against_cublas():
+    """o, down and q|k|v of DeepSeek-LLM-7B at 128, 256 and 512 tokens: cuBLAS (torch.matmul), the planned product
+    with its reduce kernel, and the planned product whose partial sums are left to the consumer; microseconds
+    (best of three replays of 20 launches) and the ratio to cuBLAS."""
+    dev = torch.device("cuda:0")
+    print("| product | tokens | cuBLAS us | plan: us (x cuBLAS) | plan with sums left to the consumer: us (x cuBLAS) |")
+    print("|---|---|---|---|---|")
+    for name, (n, k) in (("o", (4096, 4096)), ("down", (4096, 11008)), ("q|k|v", (12288, 4096))):
+        copies = max(2, int(600e6 // (n * k * 2)) + 1)
+        row_major = [torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.05 for _ in range(copies)]
+        packed = [gemm_tc.PackedWeight(w) for w in row_major]
+        for m in (128, 256, 512):
+            a = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+            out = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+            best = lambda fn: min(timed(fn, 20) for _ in range(3))
+            cublas = best(lambda i: torch.matmul(a, row_major[i % copies].t(), out=out))
+            t = best(lambda i: gemm_tc.gemm(a, packed[i % copies], out))
+            t_deferred = best(lambda i: gemm_tc.gemm(a, packed[i % copies], out, defer=True))
+            p, pd = gemm_tc.plan(m, n, k, 148), gemm_tc.plan(m, n, k, 148, True)
+            print(f"| {name} | {m} | {cublas:.1f} | {p[0]}/{p[1]}: {t:.1f} ({t / cublas:.2f}) | "
+                  f"{pd[0]}/{pd[1]}: {t_deferred:.1f} ({t_deferred / cublas:.2f}) |", flush=True)
+        del packed, row_major
+
+
 def main():
+    if sys.argv[1] == "--planned":
+        planned_against_cublas()
+        return
     out_path = sys.argv[1]
     counts = [int(x) for x in sys.argv[2].split(",")] if len(sys.argv) > 2 else [80, 128, 192, 256, 384, 512, 768]
     dev = torch.device("cuda:0")
